@@ -1,0 +1,346 @@
+"""Benchmark of the Bi-WKV forward+backward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one Bi-WKV forward and one backward over a synthetic batch at the shape
+the headline metric is quoted on (B=64 per GPU, T=4096, C=768, fp32), plus, with more
+than one GPU, the single all-reduce of the (2, C) gw/gu buffer.  Ranks shard by batch
+(weak scaling: every GPU holds its own 64 sequences; no collective on the data path).
+
+The metric is algorithmic HBM throughput: 32 bytes per (batch, token, channel) element
+(forward reads k, v and writes y; backward reads k, v, gy and writes gk, gv) divided by
+the step time, summed over GPUs.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOAD = {"name": "biwkv_fwd_bwd", "B": 64, "T": 4096, "C": 768}
+BYTES_FWD = 12          # k, v read; y written (fp32)
+BYTES_BWD = 20          # k, v, gy read; gk, gv written
+METRIC = "biwkv_fwd_bwd_algorithmic_hbm_throughput"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while running."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        rows = [r for ts, r in self.rows if (t0 is None or ts >= t0) and (t1 is None or ts <= t1 + 0.2)]
+        if not rows:
+            rows = [r for _, r in self.rows]
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_recurrence_seconds(B, T, C, threads, repeats=1):
+    """Time the recurrence (float32 PyTorch, O(T) scans, forward + analytic backward) on
+    the host cores for a (B, T, C) sample.  Returns best-of seconds."""
+    from oracle import biwkv_oracle as O
+    torch.set_num_threads(threads)
+    w, u, k, v, gy = O.make_inputs(B, T, C, dtype=torch.float32)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.biwkv_scan_forward(w, u, k, v)
+        O.biwkv_scan_backward(w, u, k, v, gy)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def run_reference_arm(args):
+    """The reference's recurrence on the host cores (it has no CPU code of its own: this is
+    the PyTorch restatement under oracle/), on a bounded batch sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    T, C = WORKLOAD["T"], WORKLOAD["C"]
+    sample_B = 1
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt = cpu_recurrence_seconds(sample_B, T, C, threads)
+        if i >= args.warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    gbs = (BYTES_FWD + BYTES_BWD) * sample_B * T * C / sec / 1e9
+    sample = f"B={sample_B} of {WORKLOAD['B']} sequences, T={T}, C={C}, fp32, fwd+bwd scans"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"biwkv_fwd_bwd B={WORKLOAD['B']} T={T} C={C} fp32",
+                   "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=WORKLOAD["B"], help="sequences per GPU")
+    ap.add_argument("--tokens", type=int, default=WORKLOAD["T"])
+    ap.add_argument("--channels", type=int, default=WORKLOAD["C"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import __graft_entry__
+    if rank == 0:
+        __graft_entry__.build()
+    if world > 1:
+        dist.barrier()
+    from vision_rwkv_b200 import launch_count, ops
+    from vision_rwkv_b200.parallel import GradAllReducer
+    from vision_rwkv_b200.vrwkv import RUN_CUDA
+
+    B, T, C = args.batch, args.tokens, args.channels
+    E = B * T * C
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    k = torch.randn(B, T, C, device=dev, generator=gen)
+    v = torch.randn(B, T, C, device=dev, generator=gen)
+    gy = torch.randn(B, T, C, device=dev, generator=gen)
+    w = (torch.rand(C, device=dev, generator=gen) * 2 - 1) / T
+    u = (torch.rand(C, device=dev, generator=gen) * 2 - 1) / T
+    gwgu = torch.empty(2, C, device=dev)
+    reducer = GradAllReducer()
+
+    def step():
+        y = ops.biwkv_forward(w, u, k, v)
+        ops.biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu)
+        if world > 1:
+            reducer.launch(gwgu)
+            reducer.wait()
+        return y
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
+               torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    sync_all()
+    t_host0 = time.perf_counter()
+    ev[0].record()
+    for i in range(args.steps):
+        a, b, c = fwd_ev[i]
+        a.record()
+        ops.biwkv_forward(w, u, k, v)
+        b.record()
+        ops.biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu)
+        c.record()
+        if world > 1:
+            reducer.launch(gwgu)
+            reducer.wait()
+    ev[1].record()
+    sync_all()
+    t_host1 = time.perf_counter()
+    launches = launch_count() - launches0
+    elapsed_ms = ev[0].elapsed_time(ev[1])
+    fwd_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in fwd_ev)
+    bwd_ms = statistics.mean(b.elapsed_time(c) for _, b, c in fwd_ev)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = t.item()
+    clocks = sampler.stop(t_host0, t_host1) if rank == 0 else None
+    ms_per_step = elapsed_ms / args.steps
+    value = (BYTES_FWD + BYTES_BWD) * E * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public autograd surface, host buffers ------------------
+    e2e = None
+    if args.e2e_steps > 0:
+        hk, hv, hgy = (torch.empty(B, T, C, pin_memory=True).copy_(x) for x in (k, v, gy))
+        hw, hu = w.cpu().pin_memory(), u.cpu().pin_memory()
+        out_y, out_gk, out_gv = (torch.empty(B, T, C, pin_memory=True) for _ in range(3))
+        out_gwgu = torch.empty(2, C, pin_memory=True)
+
+        def e2e_step():
+            dw = hw.to(dev, non_blocking=True).requires_grad_(True)
+            du = hu.to(dev, non_blocking=True).requires_grad_(True)
+            dk = hk.to(dev, non_blocking=True).requires_grad_(True)
+            dv = hv.to(dev, non_blocking=True).requires_grad_(True)
+            dgy = hgy.to(dev, non_blocking=True)
+            y = RUN_CUDA(dw, du, dk, dv)
+            y.backward(dgy)
+            grads = torch.stack([dw.grad, du.grad])
+            if world > 1:
+                reducer.launch(grads)
+                reducer.wait()
+            out_y.copy_(y.detach(), non_blocking=True)
+            out_gk.copy_(dk.grad, non_blocking=True)
+            out_gv.copy_(dv.grad, non_blocking=True)
+            out_gwgu.copy_(grads, non_blocking=True)
+
+        e2e_step()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record()
+        sync_all()
+        e_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = t.item()
+        e_ms /= args.e2e_steps
+        e2e = {"value": (BYTES_FWD + BYTES_BWD) * E * world / (e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "ms_per_step": e_ms, "steps": args.e2e_steps,
+               "h2d_bytes_per_step": (3 * E + 2 * C) * 4 * world,
+               "d2h_bytes_per_step": (3 * E + 2 * C) * 4 * world}
+        del hk, hv, hgy, out_y, out_gk, out_gv
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    bwd_gbs = BYTES_BWD * E / (bwd_ms * 1e-3) / 1e9
+    fwd_gbs = BYTES_FWD * E / (fwd_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "biwkv backward (all launches of one backward call)",
+                "achieved": bwd_gbs, "peak": peak, "peak_source": f"{peak_kind} copy bandwidth",
+                "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": None,
+                "algorithmic_bytes_per_launch": BYTES_BWD * E, "ms_per_launch": bwd_ms,
+                "forward": {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "ms": fwd_ms,
+                            "algorithmic_bytes": BYTES_FWD * E},
+                "fwd_bwd_frac": (BYTES_FWD + BYTES_BWD) * E / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak}
+
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        threads = os.cpu_count() or 1
+        sB = 1
+        sec = cpu_recurrence_seconds(sB, T, C, threads)
+        if sec < 5:                       # grow the sample towards ~10-30 s of CPU work
+            sB = max(1, min(B, int(12 / sec)))
+            sec = cpu_recurrence_seconds(sB, T, C, threads)
+        cpu = {"value": (BYTES_FWD + BYTES_BWD) * sB * T * C / sec / 1e9, "unit": UNIT,
+               "cores": threads, "kind": "port", "seconds": sec,
+               "sample": f"B={sB} of {B} sequences, T={T}, C={C}, fp32 PyTorch scans, fwd+bwd"}
+
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"biwkv_fwd_bwd B={B}/gpu T={T} C={C} fp32",
+                   "global_batch": B * world, "parallelism": f"batch-sharded x{world}",
+                   "collective": "one all-reduce of gw|gu (2,C) per step" if world > 1 else "none",
+                   "l2": "inputs (2.4 GB per pass) exceed the 126 MB L2; no explicit flush"},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+        "clocks": clocks,
+    }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+/* vrwkv_b200 -- C ABI of the B200 (sm_100a) token-mixing kernels of Vision-RWKV.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA
+ * stream it is given (a cudaStream_t passed as void*; NULL is the legacy default
+ * stream), never synchronises, never allocates, and returns a status code
+ * (VRWKV_OK == 0).  The caller owns every buffer, including the scratch
+ * "workspace", whose size the matching *_workspace_bytes function reports.
+ * Outputs need no initialisation: every element is written.
+ *
+ * Layouts: k, v, y, gy, gk, gv, r, gr, w_raw, gw_raw are (B, T, C) row-major,
+ * channel fastest (the backbones' token-major layout).  All data are fp32, as in
+ * the reference, whose Python wrappers cast to fp32 before calling the kernels.
+ *
+ * Each declaration names the reference interface it stands in for, by path inside
+ * the OpenGVLab/Vision-RWKV tree ("CLS/" = classification/mmcls_custom/models/
+ * backbones/, "MAE/" = classification/mae/).
+ */
+#ifndef VRWKV_B200_H_
+#define VRWKV_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum vrwkv_status {
+    VRWKV_OK = 0,
+    VRWKV_ERR_SHAPE = 1,       /* a dimension is <= 0 or beyond what a launch can index   */
+    VRWKV_ERR_NULL = 2,        /* a required pointer is NULL                               */
+    VRWKV_ERR_WORKSPACE = 3,   /* workspace_bytes is smaller than *_workspace_bytes says   */
+    VRWKV_ERR_ALIGNMENT = 4,   /* a pointer is not 4-byte aligned                          */
+    VRWKV_ERR_LAUNCH = 5,      /* cudaGetLastError() reported a failure after a launch     */
+    VRWKV_ERR_DEVICE = 6,      /* driver entry point or device attribute unavailable       */
+    VRWKV_ERR_HEAD_SIZE = 7    /* WKV6: C != 64 * H                                        */
+};
+
+/* Library version, major*10000 + minor*100 + patch. */
+int vrwkv_version(void);
+/* Human-readable text for a status code (static storage). */
+const char* vrwkv_status_string(int status);
+/* Number of kernels this library has launched in the calling process so far. */
+unsigned long long vrwkv_launch_count(void);
+
+/* ---- Bi-WKV --------------------------------------------------------------------
+ * y[b,t,c] = sum_j p_tj v[b,j,c] / sum_j p_tj,  log p_tj = k[b,j,c] - w[c]|t-j| for
+ * j != t and u[c] + k[b,t,c] for j == t.  w, u: (C,).
+ *
+ * vrwkv_biwkv_forward_f32 replaces
+ *   cuda_forward(int B,int T,int C,float*w,float*u,float*k,float*v,float*y)
+ *       MAE/vrwkv/cuda/wkv_op.cpp:3,6-8  (kernel MAE/vrwkv/cuda/wkv_cuda.cu:332-338)
+ *   bi_wkv_cuda_forward(w,u,k,v) -> y
+ *       CLS/cuda_new/bi_wkv.cpp:11-15,23-33 (kernel CLS/cuda_new/bi_wkv_kernel.cu:370-399)
+ * without their T <= T_MAX, C >= 32 and B*C % 32 == 0 restrictions.
+ */
+size_t vrwkv_biwkv_forward_workspace_bytes(int B, int T, int C);
+int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
+                            const float* v, float* y, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* vrwkv_biwkv_backward_f32 replaces
+ *   cuda_backward(int B,int T,int C,float*w,float*u,float*k,float*v,float*gy,
+ *                 float*gw,float*gu,float*gk,float*gv)
+ *       MAE/vrwkv/cuda/wkv_op.cpp:4,9-11 (kernel MAE/vrwkv/cuda/wkv_cuda.cu:340-345)
+ *   bi_wkv_cuda_backward(w,u,k,v,gy) -> {gw,gu,gk,gv}
+ *       CLS/cuda_new/bi_wkv.cpp:17-21,35-47 (kernel CLS/cuda_new/bi_wkv_kernel.cu:401-443)
+ * gwgu is (2, C): row 0 = gw, row 1 = gu, already summed over batch and tokens in
+ * a fixed order (no atomics), contiguous so one all-reduce covers both.  Nothing
+ * per-token is kept from the forward: the backward recomputes from k, v, gy.
+ */
+size_t vrwkv_biwkv_backward_workspace_bytes(int B, int T, int C);
+int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
+                             const float* v, const float* gy, float* gwgu, float* gk, float* gv,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VRWKV_B200_H_ */

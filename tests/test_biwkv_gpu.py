@@ -1,0 +1,217 @@
+"""Bi-WKV on the GPU, through the C ABI, against the float64 oracle.
+
+Tolerance (fp32 kernels): max|x - ref| / max|ref| <= 1e-5 per tensor, the bar the
+north-star states for fp32 against a float64 evaluation.  Inputs with a deliberately
+huge exponent range (k scaled by 8, or |w| of order one per token) get 5e-5: there the
+float32 rounding of k itself moves the answer by more than 1e-5.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err
+from oracle import biwkv_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 1e-5
+
+
+def run_gpu(dev, w, u, k, v, gy):
+    from vision_rwkv_b200 import ops
+    f = [x.float().contiguous().to(dev) for x in (w, u, k, v, gy)]
+    y = ops.biwkv_forward(*f[:4])
+    gw, gu, gk, gv = ops.biwkv_backward(*f)
+    torch.cuda.synchronize()
+    return y, gw, gu, gk, gv
+
+
+def check(dev, w, u, k, v, gy, tol=TOL):
+    f32 = [x.float().double() for x in (w, u, k, v, gy)]
+    got = run_gpu(dev, w, u, k, v, gy)
+    ref = (O.biwkv_scan_forward(*f32[:4]),) + tuple(O.biwkv_scan_backward(*f32))
+    errs = {}
+    for name, g, r in zip(("y", "gw", "gu", "gk", "gv"), got, ref):
+        assert torch.isfinite(g).all(), name
+        if r.abs().max() == 0:
+            assert g.abs().max().item() < 1e-6, name
+            continue
+        errs[name] = rel_err(g, r)
+    assert all(e <= tol for e in errs.values()), errs
+    return errs
+
+
+SHAPES = [(2, 196, 192), (1, 1, 4), (1, 2, 3), (2, 3, 5), (1, 31, 33), (2, 32, 32), (1, 33, 130),
+          (1, 63, 7), (2, 64, 64), (1, 65, 1), (3, 197, 36), (1, 576, 100), (2, 1000, 12),
+          (1, 4200, 8)]
+
+
+@pytest.mark.parametrize("B,T,C", SHAPES)
+def test_parity_with_oracle(cuda_device, B, T, C):
+    check(cuda_device, *O.make_inputs(B, T, C, seed=B * 7 + T))
+
+
+@pytest.mark.parametrize("ws,ks,tol", [(-5.0, 1.0, TOL), (3.0, 1.0, TOL), (50.0, 1.0, 5e-5),
+                                       (1.0, 8.0, 5e-5), (-40.0, 4.0, 5e-5)])
+def test_parity_wide_exponent_range(cuda_device, ws, ks, tol):
+    w, u, k, v, gy = O.make_inputs(2, 150, 24, seed=5)
+    check(cuda_device, w * ws, u, k * ks, v, gy, tol)
+
+
+def test_parity_extreme_values_stay_finite(cuda_device):
+    w, u, k, v, gy = O.make_inputs(1, 90, 16, seed=6)
+    got = run_gpu(cuda_device, w * 90 * 3, u * 90 * 30, k * 60, v, gy)
+    assert all(torch.isfinite(g).all() for g in got)
+    ref = O.biwkv_scan_forward((w * 270).float().double(), (u * 2700).float().double(),
+                               (k * 60).float().double(), v)
+    assert rel_err(got[0], ref) < 1e-4
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "biwkv_*.npz"))))
+def test_golden_vectors(cuda_device, path):
+    z = np.load(path)
+    w, u, k, v, gy = (torch.from_numpy(z[n]) for n in ("w", "u", "k", "v", "gy"))
+    got = run_gpu(cuda_device, w, u, k, v, gy)
+    tol = 5e-5 if "strongdecay" in path else TOL
+    for g, name in zip(got, ("y", "gw", "gu", "gk", "gv")):
+        assert rel_err(g, torch.from_numpy(z[name])) <= tol, name
+
+
+def test_outputs_do_not_spill_past_their_buffers(cuda_device):
+    """Every output sits between sentinel blocks; the blocks must survive the launch."""
+    from vision_rwkv_b200 import _lib
+    lib = _lib.load()
+    B, T, C = 2, 37, 9
+    n = B * T * C
+    pad = 256
+    w, u, k, v, gy = [x.float().to(cuda_device).contiguous() for x in O.make_inputs(B, T, C)]
+    sent = 12345.0
+
+    def padded(count):
+        buf = torch.full((pad + count + pad,), sent, device=cuda_device)
+        return buf, buf[pad:pad + count]
+
+    ybuf, y = padded(n)
+    gkbuf, gk = padded(n)
+    gvbuf, gv = padded(n)
+    gbuf, gwgu = padded(2 * C)
+    nf = lib.vrwkv_biwkv_forward_workspace_bytes(B, T, C)
+    nb = lib.vrwkv_biwkv_backward_workspace_bytes(B, T, C)
+    wsbuf = torch.full((pad * 4 + max(nf, nb) + pad * 4,), 77, dtype=torch.uint8, device=cuda_device)
+    ws = wsbuf[pad * 4:pad * 4 + max(nf, nb)]
+    st = lib.vrwkv_biwkv_forward_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                     y.data_ptr(), ws.data_ptr(), nf, None)
+    assert st == 0
+    st = lib.vrwkv_biwkv_backward_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(),
+                                      v.data_ptr(), gy.data_ptr(), gwgu.data_ptr(), gk.data_ptr(),
+                                      gv.data_ptr(), ws.data_ptr(), nb, None)
+    assert st == 0
+    torch.cuda.synchronize()
+    for buf, count in ((ybuf, n), (gkbuf, n), (gvbuf, n), (gbuf, 2 * C)):
+        assert (buf[:pad] == sent).all() and (buf[pad + count:] == sent).all()
+        assert (buf[pad:pad + count] != sent).all()
+    assert (wsbuf[:pad * 4] == 77).all() and (wsbuf[pad * 4 + max(nf, nb):] == 77).all()
+
+
+def test_bitwise_reproducible(cuda_device):
+    args = O.make_inputs(4, 300, 40, seed=3)
+    a = run_gpu(cuda_device, *args)
+    b = run_gpu(cuda_device, *args)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+def test_autograd_surface_new_api(cuda_device):
+    from vision_rwkv_b200.vrwkv import RUN_CUDA, WKV
+    w, u, k, v, gy = O.make_inputs(2, 50, 8)
+    xs = [x.float().requires_grad_(True) for x in (w, u, k, v)]       # CPU tensors: RUN_CUDA moves them
+    y = RUN_CUDA(*xs)
+    assert y.is_cuda and y.dtype == torch.float32
+    y.backward(gy.float().to(cuda_device))
+    ref = O.biwkv_scan_backward(w, u, k, v, gy)
+    for x, r in zip(xs, ref):
+        assert x.grad.shape == r.shape and rel_err(x.grad, r) <= TOL
+    # dtype of the result follows w
+    for dt in (torch.half, torch.bfloat16):
+        xs = [x.to(dt).to(cuda_device).requires_grad_(True) for x in (w, u, k, v)]
+        y = WKV.apply(*xs)
+        assert y.dtype == dt
+        y.backward(gy.to(dt).to(cuda_device))
+        assert all(x.grad.dtype == dt for x in xs)
+        ref16 = O.biwkv_scan_forward(*[x.detach().double().cpu() for x in xs])
+        assert rel_err(y, ref16) <= 1e-2
+    # decay_offset = 1 is the paper's convention
+    xs = [x.float().to(cuda_device).requires_grad_(True) for x in (w, u, k, v)]
+    y1 = RUN_CUDA(*xs, decay_offset=1)
+    y1.backward(gy.float().to(cuda_device))
+    assert rel_err(y1, O.biwkv_dense(w, u, k, v, 1)) <= TOL
+    for x, r in zip(xs, O.biwkv_scan_backward(w, u, k, v, gy, 1)):
+        assert rel_err(x.grad, r) <= TOL
+
+
+def test_autograd_surface_old_api(cuda_device):
+    from vision_rwkv_b200.mae_vrwkv import RUN_CUDA
+    B, T, C = 2, 40, 16
+    w, u, k, v, gy = O.make_inputs(B, T, C)
+    xs = [x.float().to(cuda_device).requires_grad_(True) for x in (w, u, k, v)]
+    y = RUN_CUDA(B, T, C, *xs)
+    y.backward(gy.float().to(cuda_device))
+    assert rel_err(y, O.biwkv_scan_forward(w, u, k, v)) <= TOL
+    for x, r in zip(xs, O.biwkv_scan_backward(w, u, k, v, gy)):
+        assert rel_err(x.grad, r) <= TOL
+    with pytest.raises(RuntimeError):
+        RUN_CUDA(B, T + 1, C, *xs)
+
+
+def test_non_contiguous_and_cpu_inputs_are_rejected_by_ops(cuda_device):
+    from vision_rwkv_b200 import ops
+    w, u, k, v, _ = [x.float().to(cuda_device) for x in O.make_inputs(2, 8, 4)]
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ops.biwkv_forward(w, u, k.transpose(0, 1), v.transpose(0, 1))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.biwkv_forward(w.cpu(), u, k, v)
+
+
+# ---- the headline shape: properties that need no oracle, plus an oracle slice ----------
+def test_full_size_properties(cuda_device):
+    from vision_rwkv_b200 import ops
+    B, T, C = 8, 4096, 768
+    g = torch.Generator(device="cuda").manual_seed(0)
+    k = torch.randn(B, T, C, device=cuda_device, generator=g)
+    v = torch.randn(B, T, C, device=cuda_device, generator=g)
+    v2 = torch.randn(B, T, C, device=cuda_device, generator=g)
+    gy = torch.randn(B, T, C, device=cuda_device, generator=g)
+    w = (torch.rand(C, device=cuda_device, generator=g) * 2 - 1) / T
+    u = (torch.rand(C, device=cuda_device, generator=g) * 2 - 1) / T
+    y = ops.biwkv_forward(w, u, k, v)
+    # linear in v
+    y2 = ops.biwkv_forward(w, u, k, v2)
+    ylin = ops.biwkv_forward(w, u, k, 0.5 * v - 2.0 * v2)
+    assert rel_err(ylin, (0.5 * y - 2.0 * y2).cpu()) < 1e-5
+    # invariant to a constant shift of k
+    assert rel_err(ops.biwkv_forward(w, u, k + 3.0, v), y.cpu()) < 1e-5
+    # token reversal commutes with the op
+    yr = ops.biwkv_forward(w, u, k.flip(1).contiguous(), v.flip(1).contiguous())
+    assert rel_err(yr.flip(1), y.cpu()) < 1e-5
+    # convex combination of v: bounded by the extremes of v per (batch, channel)
+    assert (y <= v.amax(1, keepdim=True) + 1e-4).all() and (y >= v.amin(1, keepdim=True) - 1e-4).all()
+    gw, gu, gk, gv = ops.biwkv_backward(w, u, k, v, gy)
+    gwr, gur, gkr, gvr = ops.biwkv_backward(w, u, k.flip(1).contiguous(), v.flip(1).contiguous(),
+                                            gy.flip(1).contiguous())
+    assert rel_err(gkr.flip(1), gk.cpu()) < 1e-5 and rel_err(gvr.flip(1), gv.cpu()) < 1e-5
+    assert rel_err(gwr, gw.cpu()) < 1e-4 and rel_err(gur, gu.cpu()) < 1e-4
+    # gw, gu add over batch shards (what the data-parallel all-reduce relies on)
+    h = B // 2
+    a = ops.biwkv_backward(w, u, k[:h].contiguous(), v[:h].contiguous(), gy[:h].contiguous())
+    b = ops.biwkv_backward(w, u, k[h:].contiguous(), v[h:].contiguous(), gy[h:].contiguous())
+    assert rel_err(a[0] + b[0], gw.cpu()) < 1e-5 and rel_err(a[1] + b[1], gu.cpu()) < 1e-5
+    # sum_j gk_j = 0: y does not change when k shifts by a constant
+    assert gk.sum(1).abs().max().item() < 1e-3 * gk.abs().max().item() * (T ** 0.5)
+    # channels are independent: a channel slice of the full result equals the oracle on that slice
+    cs = slice(100, 104)
+    sl = [x.double().cpu() for x in (w[cs], u[cs], k[:1, :, cs], v[:1, :, cs], gy[:1, :, cs])]
+    assert rel_err(y[:1, :, cs], O.biwkv_scan_forward(*sl[:4])) <= TOL
+    _, _, gk_ref, gv_ref = O.biwkv_scan_backward(*sl)
+    assert rel_err(gk[:1, :, cs], gk_ref) <= TOL and rel_err(gv[:1, :, cs], gv_ref) <= TOL

@@ -1,0 +1,60 @@
+"""ctypes binding of libvrwkv_b200.so (the C ABI declared in include/vrwkv_b200.h).
+
+There is no fallback: if the library is missing or a call returns a non-zero status
+the caller gets an exception.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from ._build import LIB_PATH
+
+_c_int = ctypes.c_int
+_c_size_t = ctypes.c_size_t
+_ptr = ctypes.c_void_p
+
+# name -> (restype, argtypes); mirrors include/vrwkv_b200.h one to one
+SIGNATURES = {
+    "vrwkv_version": (_c_int, []),
+    "vrwkv_status_string": (ctypes.c_char_p, [_c_int]),
+    "vrwkv_launch_count": (ctypes.c_ulonglong, []),
+    "vrwkv_biwkv_forward_workspace_bytes": (_c_size_t, [_c_int] * 3),
+    "vrwkv_biwkv_forward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 6 + [_c_size_t, _ptr]),
+    "vrwkv_biwkv_backward_workspace_bytes": (_c_size_t, [_c_int] * 3),
+    "vrwkv_biwkv_backward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 9 + [_c_size_t, _ptr]),
+}
+
+_lib = None
+
+
+class VrwkvError(RuntimeError):
+    pass
+
+
+def load():
+    """Load the shared library once and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise VrwkvError(
+            f"{LIB_PATH} is missing: build it first (python -m vision_rwkv_b200._build). "
+            "This package has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)       # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str):
+    if status != 0:
+        msg = load().vrwkv_status_string(status).decode()
+        raise VrwkvError(f"{what} failed with status {status}: {msg}")
+
+
+def launch_count() -> int:
+    return int(load().vrwkv_launch_count())

@@ -1,0 +1,15 @@
+// Declarations shared between the C-ABI translation unit and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+
+namespace biwkv {
+// Each launcher returns the number of kernels it enqueued.
+size_t generic_forward_workspace(int B, int T, int C);
+size_t generic_backward_workspace(int B, int T, int C);
+int generic_forward(int B, int T, int C, const float* w, const float* u, const float* k,
+                    const float* v, float* y, void* workspace, cudaStream_t stream);
+int generic_backward(int B, int T, int C, const float* w, const float* u, const float* k,
+                     const float* v, const float* gy, float* gwgu, float* gk, float* gv,
+                     void* workspace, cudaStream_t stream);
+}  // namespace biwkv

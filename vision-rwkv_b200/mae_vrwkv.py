@@ -1,0 +1,50 @@
+"""Drop-in for the older Bi-WKV surface kept by the MAE pre-training code:
+`WKV` and `RUN_CUDA(B, T, C, w, u, k, v)` of classification/mae/vrwkv/vrwkv.py:30-90.
+
+Kept from that surface: the explicit B, T, C arguments (checked against the tensors),
+the three leading `None` gradients, the dtype rule keyed on `w`.  Dropped: the
+`T <= T_MAX` and `B * C % min(C, 1024) == 0` asserts (:36-37), which were limits of the
+old kernel, and the per-batch (B, C) gw/gu buffers summed in Python (:62-86) -- the
+kernel already returns (C,).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+class WKV(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, B, T, C, w, u, k, v):
+        if tuple(k.shape) != (B, T, C):
+            raise RuntimeError(f"k has shape {tuple(k.shape)}, expected {(B, T, C)}")
+        ctx.B, ctx.T, ctx.C = B, T, C
+        half_mode = (w.dtype == torch.half)
+        bf_mode = (w.dtype == torch.bfloat16)
+        ctx.save_for_backward(w, u, k, v)
+        y = ops.biwkv_forward(w.float().contiguous(), u.float().contiguous(),
+                              k.float().contiguous(), v.float().contiguous())
+        if half_mode:
+            y = y.half()
+        elif bf_mode:
+            y = y.bfloat16()
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        w, u, k, v = ctx.saved_tensors
+        half_mode = (w.dtype == torch.half)
+        bf_mode = (w.dtype == torch.bfloat16)
+        gw, gu, gk, gv = ops.biwkv_backward(w.float().contiguous(), u.float().contiguous(),
+                                            k.float().contiguous(), v.float().contiguous(),
+                                            gy.float().contiguous())
+        if half_mode:
+            return (None, None, None, gw.half(), gu.half(), gk.half(), gv.half())
+        elif bf_mode:
+            return (None, None, None, gw.bfloat16(), gu.bfloat16(), gk.bfloat16(), gv.bfloat16())
+        return (None, None, None, gw, gu, gk, gv)
+
+
+def RUN_CUDA(B, T, C, w, u, k, v):
+    return WKV.apply(B, T, C, w.cuda(), u.cuda(), k.cuda(), v.cuda())

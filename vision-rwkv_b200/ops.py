@@ -1,0 +1,96 @@
+"""Tensor-level entry points: torch tensors in, torch tensors out, no autograd.
+
+These stand where the reference's extension modules stand
+(`wkv_cuda.bi_wkv_forward(w, u, k, v)` / `bi_wkv_backward(w, u, k, v, gy)`,
+classification/mmcls_custom/models/backbones/cuda_new/bi_wkv.cpp:23-52): they check
+what that binding checks (CUDA tensors, contiguous: its CHECK_INPUT at :6-8), allocate
+outputs and scratch with torch, and call the C ABI on the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _check_inputs(named):
+    dev = None
+    for name, t in named:
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor")          # CHECK_CUDA
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")             # CHECK_CONTIGUOUS
+        if t.dtype != torch.float32:
+            raise RuntimeError(f"{name} must be float32, got {t.dtype}")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"{name} is on {t.device}, expected {dev}")
+    return dev
+
+
+def _biwkv_shapes(w, u, k, v, gy=None):
+    if k.dim() != 3:
+        raise RuntimeError(f"k must be (B, T, C), got {tuple(k.shape)}")
+    B, T, C = k.shape
+    if v.shape != k.shape or (gy is not None and gy.shape != k.shape):
+        raise RuntimeError("k, v (and gy) must have the same shape")
+    if w.numel() != C or u.numel() != C:
+        raise RuntimeError(f"w and u must hold C={C} values")
+    return B, T, C
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+
+
+def biwkv_forward(w, u, k, v):
+    """y = Bi-WKV(w, u, k, v); all float32 CUDA, k and v (B, T, C), w and u (C,)."""
+    dev = _check_inputs((("w", w), ("u", u), ("k", k), ("v", v)))
+    B, T, C = _biwkv_shapes(w, u, k, v)
+    lib = _lib.load()
+    y = torch.empty_like(k)
+    if k.numel() == 0:
+        return y
+    with torch.cuda.device(dev):
+        nbytes = lib.vrwkv_biwkv_forward_workspace_bytes(B, T, C)
+        ws = _workspace(nbytes, dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        st = lib.vrwkv_biwkv_forward_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(),
+                                         v.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(),
+                                         stream)
+    _lib.check(st, "vrwkv_biwkv_forward_f32")
+    return y
+
+
+def biwkv_backward(w, u, k, v, gy, gwgu_out=None):
+    """(gw, gu, gk, gv).  gw and gu are views of one (2, C) buffer, so a data-parallel
+    caller can all-reduce both with a single collective; pass `gwgu_out` to have them
+    written into a buffer of its own (for instance one registered with NCCL)."""
+    dev = _check_inputs((("w", w), ("u", u), ("k", k), ("v", v), ("gy", gy)))
+    B, T, C = _biwkv_shapes(w, u, k, v, gy)
+    lib = _lib.load()
+    gk = torch.empty_like(k)
+    gv = torch.empty_like(k)
+    if gwgu_out is None:
+        gwgu = torch.empty((2, C), dtype=torch.float32, device=dev)
+    else:
+        _check_inputs((("gwgu_out", gwgu_out),))
+        if gwgu_out.numel() != 2 * C:
+            raise RuntimeError("gwgu_out must hold 2*C values")
+        gwgu = gwgu_out.view(2, C)
+    if k.numel() == 0:
+        gwgu.zero_()
+        return gwgu[0], gwgu[1], gk, gv
+    with torch.cuda.device(dev):
+        nbytes = lib.vrwkv_biwkv_backward_workspace_bytes(B, T, C)
+        ws = _workspace(nbytes, dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        st = lib.vrwkv_biwkv_backward_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(),
+                                          v.data_ptr(), gy.data_ptr(), gwgu.data_ptr(),
+                                          gk.data_ptr(), gv.data_ptr(), ws.data_ptr(),
+                                          ws.numel(), stream)
+    _lib.check(st, "vrwkv_biwkv_backward_f32")
+    return gwgu[0], gwgu[1], gk, gv
