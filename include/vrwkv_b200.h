@@ -4,7 +4,8 @@
  * stream it is given (a cudaStream_t passed as void*; NULL is the legacy default
  * stream), never synchronises, never allocates, and returns a status code
  * (VRWKV_OK == 0).  The caller owns every buffer, including the scratch
- * "workspace", whose size the matching *_workspace_bytes function reports.
+ * "workspace" (256-byte aligned), whose size the matching *_workspace_bytes function
+ * reports.
  * Outputs need no initialisation: every element is written.
  *
  * Layouts: k, v, y, gy, gk, gv, r, gr, w_raw, gw_raw are (B, T, C) row-major,
@@ -29,7 +30,7 @@ enum vrwkv_status {
     VRWKV_ERR_SHAPE = 1,       /* a dimension is <= 0 or beyond what a launch can index   */
     VRWKV_ERR_NULL = 2,        /* a required pointer is NULL                               */
     VRWKV_ERR_WORKSPACE = 3,   /* workspace_bytes is smaller than *_workspace_bytes says   */
-    VRWKV_ERR_ALIGNMENT = 4,   /* a pointer is not 4-byte aligned                          */
+    VRWKV_ERR_ALIGNMENT = 4,   /* data pointer not 4-byte / workspace not 256-byte aligned */
     VRWKV_ERR_LAUNCH = 5,      /* cudaGetLastError() reported a failure after a launch     */
     VRWKV_ERR_DEVICE = 6,      /* driver entry point or device attribute unavailable       */
     VRWKV_ERR_HEAD_SIZE = 7    /* WKV6: C != 64 * H                                        */
@@ -39,8 +40,20 @@ enum vrwkv_status {
 int vrwkv_version(void);
 /* Human-readable text for a status code (static storage). */
 const char* vrwkv_status_string(int status);
+/* One line about the most recent non-zero status of this process (for instance the name of
+ * the CUDA error behind VRWKV_ERR_LAUNCH).  Static storage, not thread-safe.  Diagnostic. */
+const char* vrwkv_last_error_detail(void);
 /* Number of kernels this library has launched in the calling process so far. */
 unsigned long long vrwkv_launch_count(void);
+
+/* Kernel path selection, for tests and measurements: 0 = automatic (default), 1 = always
+ * the generic multi-launch path, 2 = same as 0.  Process-wide.  No reference counterpart. */
+int vrwkv_set_path(int path);
+/* Copies the device status word kept in the first 4 bytes of a workspace to *status_out
+ * after synchronising `stream`.  0 means no bounded device-side wait ran out; bit 0 = a
+ * tile-exchange flag never arrived, bit 1 = a TMA load never completed.  Diagnostic only;
+ * no reference counterpart (the reference never checks its launches). */
+int vrwkv_workspace_status(const void* workspace, void* stream, unsigned* status_out);
 
 /* ---- Bi-WKV --------------------------------------------------------------------
  * y[b,t,c] = sum_j p_tj v[b,j,c] / sum_j p_tj,  log p_tj = k[b,j,c] - w[c]|t-j| for

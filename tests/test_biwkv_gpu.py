@@ -22,6 +22,19 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 TOL = 1e-5
 
 
+@pytest.fixture(autouse=True, params=["auto", "generic"])
+def kernel_path(request):
+    """Every test runs twice: automatic path selection (the fused TMA kernels wherever they
+    are eligible) and the generic multi-launch kernels."""
+    from vision_rwkv_b200 import _lib, ops
+    lib = _lib.load()
+    ops.CHECK_STATUS = True
+    assert lib.vrwkv_set_path(1 if request.param == "generic" else 0) == 0
+    yield request.param
+    lib.vrwkv_set_path(0)
+    ops.CHECK_STATUS = False
+
+
 def run_gpu(dev, w, u, k, v, gy):
     from vision_rwkv_b200 import ops
     f = [x.float().contiguous().to(dev) for x in (w, u, k, v, gy)]
@@ -119,6 +132,24 @@ def test_outputs_do_not_spill_past_their_buffers(cuda_device):
         assert (buf[:pad] == sent).all() and (buf[pad + count:] == sent).all()
         assert (buf[pad:pad + count] != sent).all()
     assert (wsbuf[:pad * 4] == 77).all() and (wsbuf[pad * 4 + max(nf, nb):] == 77).all()
+
+
+def test_fused_path_is_taken_when_eligible(cuda_device, kernel_path):
+    """One launch per forward and two per backward (kernel + gw/gu reduction) on the fused
+    path; three and six on the generic one."""
+    from vision_rwkv_b200 import launch_count, ops
+    w, u, k, v, gy = [x.float().to(cuda_device).contiguous() for x in O.make_inputs(2, 300, 64)]
+    n0 = launch_count()
+    ops.biwkv_forward(w, u, k, v)
+    n1 = launch_count()
+    ops.biwkv_backward(w, u, k, v, gy)
+    n2 = launch_count()
+    assert (n1 - n0, n2 - n1) == ((3, 6) if kernel_path == "generic" else (1, 2))
+    # C not a multiple of 4 cannot be described to TMA: generic kernels serve it
+    w, u, k, v, gy = [x.float().to(cuda_device).contiguous() for x in O.make_inputs(2, 30, 6)]
+    n0 = launch_count()
+    ops.biwkv_forward(w, u, k, v)
+    assert launch_count() - n0 == 3
 
 
 def test_bitwise_reproducible(cuda_device):

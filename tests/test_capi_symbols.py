@@ -45,9 +45,9 @@ def test_version_and_status_strings(lib):
 
 
 def test_argument_validation_without_a_device(lib):
-    one = ctypes.c_void_p(16)
+    one = ctypes.c_void_p(256)
     null = ctypes.c_void_p(0)
-    odd = ctypes.c_void_p(18)
+    odd = ctypes.c_void_p(258)
     assert lib.vrwkv_biwkv_forward_workspace_bytes(2, 196, 192) > 0
     assert lib.vrwkv_biwkv_forward_workspace_bytes(0, 196, 192) == 0
     f = lib.vrwkv_biwkv_forward_f32

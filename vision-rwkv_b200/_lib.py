@@ -18,7 +18,10 @@ _ptr = ctypes.c_void_p
 SIGNATURES = {
     "vrwkv_version": (_c_int, []),
     "vrwkv_status_string": (ctypes.c_char_p, [_c_int]),
+    "vrwkv_last_error_detail": (ctypes.c_char_p, []),
     "vrwkv_launch_count": (ctypes.c_ulonglong, []),
+    "vrwkv_set_path": (_c_int, [_c_int]),
+    "vrwkv_workspace_status": (_c_int, [_ptr, _ptr, ctypes.POINTER(ctypes.c_uint)]),
     "vrwkv_biwkv_forward_workspace_bytes": (_c_size_t, [_c_int] * 3),
     "vrwkv_biwkv_forward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 6 + [_c_size_t, _ptr]),
     "vrwkv_biwkv_backward_workspace_bytes": (_c_size_t, [_c_int] * 3),
@@ -53,7 +56,8 @@ def load():
 def check(status: int, what: str):
     if status != 0:
         msg = load().vrwkv_status_string(status).decode()
-        raise VrwkvError(f"{what} failed with status {status}: {msg}")
+        detail = load().vrwkv_last_error_detail().decode()
+        raise VrwkvError(f"{what} failed with status {status}: {msg}" + (f" [{detail}]" if detail else ""))
 
 
 def launch_count() -> int:

@@ -1,0 +1,771 @@
+// Bi-WKV "fused" path: one persistent kernel per forward, one per backward, each
+// element of k, v (and gy) crossing HBM once in and each output once out.
+//
+// Work unit ("tile"): kTc = 128 consecutive tokens x kCs = 32 consecutive channels of
+// one sequence.  A CTA is 8 warps; warp s owns the sub-chunk of kL = 16 tokens
+// [16 s, 16 s + 16) of the tile, its lane c the channel; a thread walks its 16 tokens
+// sequentially out of shared memory.  Thread 0 moves tiles with TMA (tiled 3-D tensor maps
+// over (C, T, B): zero fill past T and C on load, clipping on store), double-buffered.
+//
+// The scan needs, at every token, the decayed sum over all earlier tokens of the
+// sequence and over all later ones.  Per scan level every warp
+//   1. posts its sub-chunk aggregate (both directions) to shared memory;
+//   2. sums the aggregates of the other sub-chunks of its tile that lie before / after it;
+//      warp 7 (resp. 0) thereby holds the whole tile's rightward (leftward) aggregate,
+//      writes it to the tile's global exchange record and bumps the tile's flag;
+//   3. waits (bounded spin) for the flags of the tiles j = s, s + 8, ... of the same
+//      (sequence, channel strip), reads their records back through L2 and posts the partial
+//      sum to shared memory;
+//   4. adds the eight partials and its own inside sum: the state entering its sub-chunk.
+// No tile waits for another tile's *result*, only for its aggregate, which depends on that
+// tile's own data alone, so one exchange round suffices per level (one level in the
+// forward: e^{k}[v,1]; a second in the backward: the adjoint pairs [gy/Den, gy y/Den]).
+// All sums over several (value, exponent) records take the maximum exponent first and then
+// add the rescaled values, so the exponentials are independent and pipeline.
+//
+// The kernel is launched cooperatively with one CTA per resident slot and walks the tile
+// list round-robin; consecutive tile ids are the chunks of one (sequence, strip block), so
+// the peers of a tile are in flight at the same time on other SMs.  A tile only waits for
+// tiles whose ids differ by less than the grid size, all started by resident CTAs, so the
+// wait cannot deadlock; it is bounded anyway and sets bit 0 of the workspace status word
+// instead of hanging.
+//
+// Numerics.  All hand-overs are (value, exponent) pairs as in biwkv_math.cuh.  Inside a
+// sub-chunk a thread shifts by one reference exponent (the maximum over its 16 k values
+// and the states entering it) and then runs plain decayed recurrences with lambda =
+// e^{-w}, packed two floats per instruction (numerator|denominator).  That is exact
+// enough whenever (max k - min k) + 16 |w| + |u| <= 60 inside the sub-chunk; a warp that
+// sees otherwise takes the per-token max-shifted path of biwkv_math.cuh for that tile.
+//
+// Recurrence restated: classification/mmcls_custom/models/backbones/cuda_new/
+// bi_wkv_kernel.cu:21-116 (forward), :119-367 (gradients).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <algorithm>
+#include <cstdint>
+#include <initializer_list>
+#include "biwkv_math.cuh"
+#include "sm100_async.cuh"
+#include "vrwkv_internal.h"
+
+namespace biwkv {
+namespace fused {
+
+constexpr int kL = 16;                 // tokens per thread
+constexpr int kWarps = 8;              // warps = sub-chunks per tile
+constexpr int kTc = kL * kWarps;       // tokens per tile
+constexpr int kCs = 32;                // channels per tile
+constexpr int kThreads = kWarps * 32;
+constexpr int kSlotFloats = kTc * kCs;
+constexpr int kRows = 8;               // exchange rows per channel: a,b,ma,mb,o | a,b,o
+constexpr int kRecFloats = kRows * kCs;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kFastRange = 60.f;
+constexpr uint32_t kSpinLimit = 1u << 20;   // ~0.1 s of polling
+
+struct Params {
+    int B, T, C;
+    int n_chunks;      // tiles along T
+    int n_strips;      // tiles along C
+    int interleave;    // strips whose tiles alternate in the id order (divides n_strips)
+    int n_tiles;
+    const float* w;
+    const float* u;
+    float* exch;       // [n_tiles][levels][kRows][kCs]
+    unsigned* flags;   // [n_tiles][levels], zero before launch, 2 when both halves are written
+    unsigned* status;  // device status word
+    float* partial;    // backward: [n_tiles][2][kCs]
+};
+
+struct TileCoord {
+    int b, strip, chunk;
+};
+__device__ __forceinline__ TileCoord decode_tile(const Params& p, int id) {
+    const int span = p.interleave * p.n_chunks;
+    const int block = id / span;
+    const int r = id - block * span;
+    const int chunk = r / p.interleave;
+    const int gs = block * p.interleave + (r - chunk * p.interleave);   // strip index over all sequences
+    TileCoord t;
+    t.b = gs / p.n_strips;
+    t.strip = gs - t.b * p.n_strips;
+    t.chunk = chunk;
+    return t;
+}
+
+__device__ __forceinline__ float fast_exp(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * kLog2e));
+    return y;
+}
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+
+// ---- exchange records: rec[row * kCs], rec already offset by the lane -------------------------
+__device__ __forceinline__ void post_acc4(float* rec, const Acc4& s) {
+    rec[0 * kCs] = s.a; rec[1 * kCs] = s.b; rec[2 * kCs] = s.ma; rec[3 * kCs] = s.mb; rec[4 * kCs] = s.o;
+}
+__device__ __forceinline__ void post_acc2(float* rec, const Acc2& s) {
+    rec[5 * kCs] = s.a; rec[6 * kCs] = s.b; rec[7 * kCs] = s.o;
+}
+__device__ __forceinline__ Acc4 merge4(const Acc4& x, const Acc4& y) {
+    const float no = wkv_max(x.o, y.o);
+    const float e1 = fast_exp(x.o - no), e2 = fast_exp(y.o - no);
+    return Acc4{e1 * x.a + e2 * y.a, e1 * x.b + e2 * y.b, e1 * x.ma + e2 * y.ma, e1 * x.mb + e2 * y.mb, no};
+}
+__device__ __forceinline__ Acc2 merge2(const Acc2& x, const Acc2& y) {
+    const float no = wkv_max(x.o, y.o);
+    const float e1 = fast_exp(x.o - no), e2 = fast_exp(y.o - no);
+    return Acc2{e1 * x.a + e2 * y.a, e1 * x.b + e2 * y.b, no};
+}
+
+struct Entering {
+    Acc4 left;    // state entering the sub-chunk at its first token (with first moments)
+    Acc2 right;   // state entering it at its last position
+};
+
+// One exchange level for one warp (see the file header).  own_right / own_left: this
+// sub-chunk's aggregates, relative to the position after its 16-token span / before it.
+__device__ __forceinline__ Entering exchange(const Params& p, float* sub, float* ext, int lane, int warp,
+                                             float w, int tile, int chunk, int level, int levels,
+                                             const Acc4& own_right, const Acc2& own_left) {
+    post_acc4(sub + warp * kRecFloats + lane, own_right);
+    post_acc2(sub + warp * kRecFloats + lane, own_left);
+    __syncthreads();
+    // (2) the other sub-chunks of this tile
+    Acc4 inP;
+    Acc2 inS;
+    {
+        float x4[kWarps], x2[kWarps];
+        float m4 = kMinExp, m2 = kMinExp;
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            const float* r = sub + s * kRecFloats + lane;
+            x4[s] = (s < warp) ? r[4 * kCs] - w * static_cast<float>((warp - 1 - s) * kL) : kMinExp;
+            x2[s] = (s > warp) ? r[7 * kCs] - w * static_cast<float>((s - warp - 1) * kL) : kMinExp;
+            m4 = wkv_max(m4, x4[s]);
+            m2 = wkv_max(m2, x2[s]);
+        }
+        inP = Acc4{0.f, 0.f, 0.f, 0.f, m4};
+        inS = Acc2{0.f, 0.f, m2};
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            const float* r = sub + s * kRecFloats + lane;
+            if (s < warp) {
+                const float f = fast_exp(x4[s] - m4);
+                const float d = static_cast<float>((warp - 1 - s) * kL);
+                const float a = r[0], b = r[kCs];
+                inP.a += f * a;
+                inP.b += f * b;
+                inP.ma += f * (r[2 * kCs] + d * a);
+                inP.mb += f * (r[3 * kCs] + d * b);
+            }
+            if (s > warp) {
+                const float f = fast_exp(x2[s] - m2);
+                inS.a += f * r[5 * kCs];
+                inS.b += f * r[6 * kCs];
+            }
+        }
+    }
+    // publish the tile's aggregate: rightward half by the last warp, leftward by the first
+    if (warp == kWarps - 1 || warp == 0) {
+        float* mine = p.exch + (static_cast<size_t>(tile) * levels + level) * kRecFloats + lane;
+        if (warp == kWarps - 1) {
+            Acc4 t = inP;
+            acc4_decay(t, w, static_cast<float>(kL));
+            post_acc4(mine, merge4(t, own_right));
+        }
+        if (warp == 0) {
+            Acc2 t = inS;
+            acc2_decay(t, w, static_cast<float>(kL));
+            post_acc2(mine, merge2(t, own_left));
+        }
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            atomicAdd(p.flags + static_cast<size_t>(tile) * levels + level, 1u);
+        }
+    }
+    // (3) the records of the tiles j = warp, warp + 8, ... of this (sequence, strip)
+    {
+        const int first = tile - chunk * p.interleave;
+        Acc4 P = acc4_zero();
+        Acc2 S = acc2_zero();
+        for (int j0 = warp; j0 < p.n_chunks; j0 += 4 * kWarps) {
+            bool ok = true;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                if (j < p.n_chunks && j != chunk) {
+                    const unsigned* f = p.flags + static_cast<size_t>(first + j * p.interleave) * levels + level;
+                    uint32_t spins = 0;
+                    while (sm100::flag_acquire(f) < 2u) {
+                        // give up after ~0.1 s, or at once if any wait of this launch already did
+                        if (++spins > kSpinLimit ||
+                            ((spins & 1023u) == 0u && *reinterpret_cast<volatile unsigned*>(p.status) != 0u)) {
+                            ok = false;
+                            break;
+                        }
+                        if (spins > 16) __nanosleep(64);
+                    }
+                }
+            }
+            if (!ok && lane == 0) atomicOr(p.status, 1u);
+            // all loads of the batch first, then the arithmetic
+            float r0[4], r1[4], r2[4], r3[4], x[4];
+            float mP = kMinExp, mS = kMinExp;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                r0[q] = r1[q] = r2[q] = r3[q] = 0.f;
+                x[q] = kMinExp;
+                if (j < p.n_chunks && j != chunk) {
+                    const float* rec = p.exch + (static_cast<size_t>(first + j * p.interleave) * levels + level) * kRecFloats + lane;
+                    if (j < chunk) {
+                        r0[q] = sm100::ld_cg(rec); r1[q] = sm100::ld_cg(rec + kCs);
+                        r2[q] = sm100::ld_cg(rec + 2 * kCs); r3[q] = sm100::ld_cg(rec + 3 * kCs);
+                        x[q] = sm100::ld_cg(rec + 4 * kCs);
+                    } else {
+                        r0[q] = sm100::ld_cg(rec + 5 * kCs); r1[q] = sm100::ld_cg(rec + 6 * kCs);
+                        x[q] = sm100::ld_cg(rec + 7 * kCs);
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                if (j < p.n_chunks && j != chunk) {
+                    const float d = static_cast<float>((j < chunk ? chunk - 1 - j : j - chunk - 1) * kTc);
+                    x[q] -= w * d;
+                    if (j < chunk) { r2[q] += d * r0[q]; r3[q] += d * r1[q]; mP = wkv_max(mP, x[q]); }
+                    else mS = wkv_max(mS, x[q]);
+                }
+            }
+            Acc4 bp{0.f, 0.f, 0.f, 0.f, mP};
+            Acc2 bs{0.f, 0.f, mS};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                if (j < p.n_chunks && j != chunk) {
+                    if (j < chunk) {
+                        const float f = fast_exp(x[q] - mP);
+                        bp.a += f * r0[q]; bp.b += f * r1[q]; bp.ma += f * r2[q]; bp.mb += f * r3[q];
+                    } else {
+                        const float f = fast_exp(x[q] - mS);
+                        bs.a += f * r0[q]; bs.b += f * r1[q];
+                    }
+                }
+            }
+            P = merge4(P, bp);
+            S = merge2(S, bs);
+        }
+        post_acc4(ext + warp * kRecFloats + lane, P);
+        post_acc2(ext + warp * kRecFloats + lane, S);
+    }
+    __syncthreads();
+    // (4) everything outside the tile, moved to this sub-chunk's edges, plus the inside sums
+    Entering out;
+    {
+        float m4 = kMinExp, m2 = kMinExp;
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            m4 = wkv_max(m4, ext[s * kRecFloats + 4 * kCs + lane]);
+            m2 = wkv_max(m2, ext[s * kRecFloats + 7 * kCs + lane]);
+        }
+        Acc4 P{0.f, 0.f, 0.f, 0.f, m4};
+        Acc2 S{0.f, 0.f, m2};
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            const float* r = ext + s * kRecFloats + lane;
+            const float f4 = fast_exp(r[4 * kCs] - m4), f2_ = fast_exp(r[7 * kCs] - m2);
+            P.a += f4 * r[0]; P.b += f4 * r[kCs]; P.ma += f4 * r[2 * kCs]; P.mb += f4 * r[3 * kCs];
+            S.a += f2_ * r[5 * kCs]; S.b += f2_ * r[6 * kCs];
+        }
+        acc4_decay(P, w, static_cast<float>(warp * kL));
+        acc2_decay(S, w, static_cast<float>((kWarps - 1 - warp) * kL));
+        out.left = merge4(P, inP);
+        out.right = merge2(S, inS);
+    }
+    return out;
+}
+
+// ---- per-token max-shifted path (any exponent range) -------------------------------------------
+// Handles one tile for one thread, both exchange levels, out of line so that its register
+// needs do not weigh on the packed path.  Sweeps are position-anchored (biwkv_math.cuh).
+struct ExchangeCtx {
+    float* sub;
+    float* ext;
+    int lane, warp, tile, chunk;
+};
+
+template <bool kBwd>
+__device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x, float* ks, float* vs,
+                                           float* gs, int n, float w, float u, float& gw_out, float& gu_out) {
+    constexpr int kLevels = kBwd ? 2 : 1;
+    const float last = static_cast<float>(n - 1);
+    Acc4 right = acc4_zero();
+    Acc2 left = acc2_zero();
+    for (int i = 0; i < n; ++i) acc4_absorb(right, ks[i * kCs] + w * static_cast<float>(i), vs[i * kCs], 1.f);
+    for (int i = n - 1; i >= 0; --i) acc2_add(left, ks[i * kCs] - w * static_cast<float>(i), vs[i * kCs], 1.f);
+    // a short sub-chunk still spans kL positions for its right-hand neighbours
+    right.o -= w * static_cast<float>(n);
+    acc4_decay(right, w, static_cast<float>(kL - n));
+    left.o -= w;
+    const Entering e1 = exchange(p, x.sub, x.ext, x.lane, x.warp, w, x.tile, x.chunk, 0, kLevels, right, left);
+    const Acc4 P4 = e1.left;                         // anchored at token 0
+    Acc2 S = e1.right;
+    acc2_decay(S, w, static_cast<float>(kL - n));   // given at position kL-1; anchor it at token n-1
+    Acc2 stash[kL];
+    for (int i = n - 1; i >= 0; --i) {
+        const float d = last - static_cast<float>(i);
+        stash[i] = acc2_at(S, w, d);
+        acc2_add(S, ks[i * kCs] + w * d, vs[i * kCs], 1.f);
+    }
+    if (!kBwd) {
+        Acc2 P{P4.a, P4.b, P4.o};
+        for (int i = 0; i < n; ++i) {
+            const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+            const TokenOut o = token_out(acc2_at(P, w, d), stash[i], k, v, u);
+            ks[i * kCs] = o.y;
+            acc2_add(P, k + w * d, v, 1.f);
+        }
+        return;
+    }
+    // backward: G e^{m}, H e^{m}, -m per token; gw from pairs (output later than input)
+    float gg[kL], hh[kL], xo[kL];
+    float gw = 0.f, gu = 0.f;
+    Acc4 PM = P4;   // prefix state with first moments
+    for (int i = 0; i < n; ++i) {
+        const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+        const Acc2 Pi{PM.a, PM.b, PM.o - w * d};
+        const TokenOut o = token_out(Pi, stash[i], k, v, u);
+        gg[i] = gs[i * kCs] * o.inv_den;
+        hh[i] = gg[i] * o.y;
+        xo[i] = -o.m;
+        gw -= wkv_exp(Pi.o + xo[i]) * (gg[i] * PM.ma - hh[i] * PM.mb);
+        acc4_absorb(PM, k + w * d, v, 1.f);
+    }
+    Acc4 later = acc4_zero();
+    Acc2 earlier = acc2_zero();
+    for (int i = 0; i < n; ++i) acc4_absorb(later, xo[i] + w * static_cast<float>(i), gg[i], hh[i]);
+    for (int i = n - 1; i >= 0; --i) acc2_add(earlier, xo[i] - w * static_cast<float>(i), gg[i], hh[i]);
+    later.o -= w * static_cast<float>(n);
+    acc4_decay(later, w, static_cast<float>(kL - n));
+    earlier.o -= w;
+    const Entering e2 = exchange(p, x.sub, x.ext, x.lane, x.warp, w, x.tile, x.chunk, 1, kLevels, later, earlier);
+    Acc4 R = e2.left;                                // anchored at token 0
+    Acc2 Q = e2.right;
+    acc2_decay(Q, w, static_cast<float>(kL - n));   // anchored at token n-1
+    float pk[kL], pv[kL];
+    for (int i = n - 1; i >= 0; --i) {
+        const float d = last - static_cast<float>(i);
+        const float e = wkv_exp(ks[i * kCs] + Q.o - w * d);
+        pv[i] = e * Q.a;
+        pk[i] = e * (Q.a * vs[i * kCs] - Q.b);
+        acc2_add(Q, xo[i] + w * d, gg[i], hh[i]);
+    }
+    for (int i = 0; i < n; ++i) {
+        const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+        const float e = wkv_exp(k + R.o - w * d);
+        const float es = wkv_exp(u + k + xo[i]);
+        const float self = es * (v * gg[i] - hh[i]);
+        vs[i * kCs] = pv[i] + e * R.a + es * gg[i];
+        ks[i * kCs] = pk[i] + e * (R.a * v - R.b) + self;
+        gu += self;
+        gw -= e * (R.ma * v - R.mb);
+        acc4_absorb(R, xo[i] + w * d, gg[i], hh[i]);
+    }
+    gw_out = gw;
+    gu_out = gu;
+}
+
+// ---- the kernel -----------------------------------------------------------------------------
+template <bool kBwd>
+__global__ void __launch_bounds__(kThreads, 2)
+biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const __grid_constant__ CUtensorMap map_g,     // backward: gy
+                   const __grid_constant__ CUtensorMap map_o0,    // forward: y ; backward: gk
+                   const __grid_constant__ CUtensorMap map_o1,    // backward: gv
+                   const Params p) {
+    constexpr int kSlots = kBwd ? 3 : 2;
+    constexpr int kLevels = kBwd ? 2 : 1;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    float* stage_base = reinterpret_cast<float*>(smem_raw);                         // [2][kSlots][kTc][kCs]
+    float* sub = stage_base + 2 * kSlots * kSlotFloats;                             // [kWarps][kRows][kCs]
+    float* ext = sub + kWarps * kRecFloats;                                         // [kWarps][kRows][kCs]
+    float* red = sub;                 // [kWarps][2][kCs]: gw/gu of a tile, between two barriers at its end
+    uint64_t* full = reinterpret_cast<uint64_t*>(ext + kWarps * kRecFloats);        // [2]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(&full[0], 1);
+        sm100::mbar_init(&full[1], 1);
+        sm100::mbar_init_fence();
+    }
+    __syncthreads();
+
+    constexpr uint32_t kStageBytes = kSlots * kSlotFloats * sizeof(float);
+    auto issue_loads = [&](int tile, int stage) {
+        const TileCoord tc = decode_tile(p, tile);
+        float* dst = stage_base + stage * kSlots * kSlotFloats;
+        sm100::mbar_expect_tx(&full[stage], kStageBytes);
+        sm100::tma_load_3d(dst, &map_k, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+        sm100::tma_load_3d(dst + kSlotFloats, &map_v, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+        if (kBwd)
+            sm100::tma_load_3d(dst + 2 * kSlotFloats, &map_g, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+    };
+
+    if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.n_tiles) issue_loads(blockIdx.x, 0);
+
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+        const int stage = it & 1;
+        const TileCoord tc = decode_tile(p, tile);
+        float* slot_k = stage_base + stage * kSlots * kSlotFloats;
+        float* slot_v = slot_k + kSlotFloats;
+        float* slot_g = slot_v + kSlotFloats;
+        const int c = tc.strip * kCs + lane;
+        const float w = (c < p.C) ? p.w[c] : 0.f;
+        const float u = (c < p.C) ? p.u[c] : 0.f;
+
+        if (threadIdx.x == 0) {
+            sm100::tma_store_wait_read();            // the other stage's outputs have left shared memory
+            const int next = tile + gridDim.x;
+            if (next < p.n_tiles) issue_loads(next, stage ^ 1);
+        }
+        if (!sm100::mbar_wait(&full[stage], (it >> 1) & 1, kSpinLimit)) atomicOr(p.status, 2u);
+        const int t0 = tc.chunk * kTc + warp * kL;               // first token of this sub-chunk
+        const int n = max(0, min(kL, p.T - t0));
+        float* ks = slot_k + (warp * kL) * kCs + lane;
+        float* vs = slot_v + (warp * kL) * kCs + lane;
+        float* gs = slot_g + (warp * kL) * kCs + lane;
+        float gw = 0.f, gu = 0.f;
+
+        float kk[kL], vv[kL];
+        float m = kMinExp, mn = 1e38f;
+#pragma unroll
+        for (int i = 0; i < kL; ++i) {
+            kk[i] = ks[i * kCs];
+            vv[i] = vs[i * kCs];
+            if (i < n) { m = wkv_max(m, kk[i]); mn = fminf(mn, kk[i]); }
+        }
+        const bool safe = (n == 0) || ((m - mn) + fabsf(w) * kL + fabsf(u) <= kFastRange);
+        if (!__all_sync(0xffffffffu, safe)) {
+            const ExchangeCtx xc{sub, ext, lane, warp, tile, tc.chunk};
+            rigorous_tile<kBwd>(p, xc, ks, vs, gs, n, w, u, gw, gu);
+        } else {
+            const float lam = fast_exp(-w);
+            const float2 lam2 = f2(lam, lam);
+            // ---- level 1: aggregates in scale e^{m} ----
+            Acc4 own_right;
+            Acc2 own_left;
+            {
+                float2 a = f2(0.f, 0.f), ma = f2(0.f, 0.f), a2 = f2(0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    const float e = (i < n) ? fast_exp(kk[i] - m) : 0.f;
+                    a = mul2(add2(a, f2(e * vv[i], e)), lam2);
+                    if (kBwd) ma = fma2(ma, lam2, a);
+                }
+#pragma unroll
+                for (int i = kL - 1; i >= 0; --i) {
+                    const float e = (i < n) ? fast_exp(kk[i] - m) : 0.f;
+                    a2 = mul2(add2(a2, f2(e * vv[i], e)), lam2);
+                }
+                own_right = Acc4{a.x, a.y, ma.x, ma.y, m};
+                own_left = Acc2{a2.x, a2.y, m};
+            }
+            const Entering e1 = exchange(p, sub, ext, lane, warp, w, tile, tc.chunk, 0, kLevels, own_right, own_left);
+            const Acc4 cp = e1.left;
+            const Acc2 cs = e1.right;
+            const float M = wkv_max(m, wkv_max(cp.o, cs.o));
+            const float fp = fast_exp(cp.o - M), fs = fast_exp(cs.o - M);
+            const float eu = fast_exp(u);
+            float2 pr = f2(cp.a * fp, cp.b * fp);
+            float2 sf = f2(cs.a * fs, cs.b * fs);
+            float2 stash[kL];
+#pragma unroll
+            for (int i = kL - 1; i >= 0; --i) {
+                stash[i] = sf;
+                const float e = (i < n) ? fast_exp(kk[i] - M) : 0.f;
+                sf = mul2(add2(sf, f2(e * vv[i], e)), lam2);
+            }
+            if (!kBwd) {
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    const float e = (i < n) ? fast_exp(kk[i] - M) : 0.f;
+                    const float2 x = f2(e * vv[i], e);
+                    const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
+                    ks[i * kCs] = __fdividef(nd.x, nd.y);
+                    pr = mul2(add2(pr, x), lam2);
+                }
+            } else {
+                // ---- level 1 emit: G' = gy/Den', H' = G' y (scale e^{-M}); gu; gw from pairs t > j ----
+                float2 pm = f2(cp.ma * fp, cp.mb * fp);
+                float hh[kL];
+                float2 r = f2(0.f, 0.f), mr = f2(0.f, 0.f), q = f2(0.f, 0.f);
+                float mu = lam;
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    const float e = (i < n) ? fast_exp(kk[i] - M) : 0.f;
+                    const float2 x = f2(e * vv[i], e);
+                    const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
+                    const float inv = (i < n) ? __frcp_rn(nd.y) : 0.f;
+                    const float y = nd.x * inv;
+                    const float g = gs[i * kCs] * inv;
+                    const float h = g * y;
+                    gs[i * kCs] = g;
+                    hh[i] = h;
+                    gu += eu * (x.x * g - x.y * h);
+                    gw -= g * pm.x - h * pm.y;
+                    pr = mul2(add2(pr, x), lam2);
+                    pm = fma2(pm, lam2, pr);
+                    const float2 gh = f2(g, h);
+                    r = mul2(add2(r, gh), lam2);
+                    mr = fma2(mr, lam2, r);
+                    q = fma2(gh, f2(mu, mu), q);
+                    mu *= lam;
+                }
+                const Entering e2 = exchange(p, sub, ext, lane, warp, w, tile, tc.chunk, 1, kLevels,
+                                             Acc4{r.x, r.y, mr.x, mr.y, -M}, Acc2{q.x, q.y, -M});
+                const Acc4 cr = e2.left;
+                const Acc2 cq = e2.right;
+                // adjoint values live in scale e^{N}; inputs re-enter as e^{k + N}
+                const float N = wkv_max(-M, wkv_max(cr.o, cq.o));
+                const float fl = fast_exp(-M - N), fr = fast_exp(cr.o - N), fq = fast_exp(cq.o - N);
+                float2 qq = f2(cq.a * fq, cq.b * fq);
+                float2 rr = f2(cr.a * fr, cr.b * fr);
+                float2 mrr = f2(cr.ma * fr, cr.mb * fr);
+                const float2 fl2 = f2(fl, fl);
+                float2 part[kL];
+#pragma unroll
+                for (int i = kL - 1; i >= 0; --i) {
+                    const float e = (i < n) ? fast_exp(kk[i] + N) : 0.f;
+                    part[i] = f2(e * (qq.x * vv[i] - qq.y), e * qq.x);          // (gk, gv) from later outputs
+                    qq = mul2(fma2(f2(gs[i * kCs], hh[i]), fl2, qq), lam2);
+                }
+                const float euf = eu * fl;
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    const float e = (i < n) ? fast_exp(kk[i] + N) : 0.f;
+                    const float g = gs[i * kCs], h = hh[i];
+                    const float ev = e * vv[i];
+                    const float self = euf * (ev * g - e * h);
+                    ks[i * kCs] = part[i].x + (ev * rr.x - e * rr.y) + self;
+                    vs[i * kCs] = part[i].y + e * rr.x + euf * e * g;
+                    gw -= ev * mrr.x - e * mrr.y;
+                    rr = mul2(fma2(f2(g, h), fl2, rr), lam2);
+                    mrr = fma2(mrr, lam2, rr);
+                }
+            }
+        }
+        if (kBwd) {
+            red[(warp * 2 + 0) * kCs + lane] = gw;
+            red[(warp * 2 + 1) * kCs + lane] = gu;
+            __syncthreads();
+            if (warp < 2) {
+                float acc = 0.f;
+#pragma unroll
+                for (int s = 0; s < kWarps; ++s) acc += red[(s * 2 + warp) * kCs + lane];
+                p.partial[(static_cast<size_t>(tile) * 2 + warp) * kCs + lane] = acc;
+            }
+        }
+        sm100::fence_proxy_async_smem();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            sm100::tma_store_3d(&map_o0, slot_k, tc.strip * kCs, tc.chunk * kTc, tc.b);
+            if (kBwd) sm100::tma_store_3d(&map_o1, slot_v, tc.strip * kCs, tc.chunk * kTc, tc.b);
+            sm100::tma_store_commit();
+        }
+    }
+    if (threadIdx.x == 0) sm100::tma_store_wait_all();
+}
+
+// out[j][c] = sum over the tiles of channel c's strip of partial[tile][j][c % 32]
+__global__ void __launch_bounds__(1024)
+reduce_tile_partials(Params p, float* __restrict__ out) {
+    __shared__ float red[32][33];
+    const int strip = blockIdx.x, j = blockIdx.y, lane = threadIdx.x;
+    const int c = strip * kCs + lane;
+    const int rows = p.B * p.n_chunks;
+    float acc = 0.f;
+    for (int r = threadIdx.y; r < rows; r += 32) {
+        const int b = r / p.n_chunks, chunk = r - b * p.n_chunks;
+        const int gs = b * p.n_strips + strip;
+        const int block = gs / p.interleave, si = gs - block * p.interleave;
+        const int tile = block * p.interleave * p.n_chunks + chunk * p.interleave + si;
+        acc += p.partial[(static_cast<size_t>(tile) * 2 + j) * kCs + lane];
+    }
+    red[threadIdx.y][lane] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < p.C) {
+        float total = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) total += red[r][lane];
+        out[static_cast<size_t>(j) * p.C + c] = total;
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+static bool make_map(CUtensorMap* map, const float* base, int B, int T, int C) {
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 4, static_cast<cuuint64_t>(T) * C * 4};
+    const cuuint32_t box[3] = {kCs, kTc, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box,
+                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    int resident[2] = {0, 0};   // CTAs per SM, forward / backward
+    bool ok = false;
+};
+
+template <bool kBwd>
+static constexpr size_t smem_bytes() {
+    return (2 * (kBwd ? 3 : 2) * kSlotFloats + 2 * kWarps * kRecFloats) * sizeof(float) + 64;
+}
+
+static const DeviceInfo& device_info() {
+    static DeviceInfo infos[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    DeviceInfo& d = infos[dev & 63];
+    if (d.ok) return d;
+    cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+    bool good = encode_fn() != nullptr;
+    good = good && cudaFuncSetAttribute(biwkv_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem_bytes<false>())) == cudaSuccess;
+    good = good && cudaFuncSetAttribute(biwkv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem_bytes<true>())) == cudaSuccess;
+    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[0], biwkv_fused_kernel<false>,
+                                                                 kThreads, smem_bytes<false>()) == cudaSuccess;
+    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[1], biwkv_fused_kernel<true>,
+                                                                 kThreads, smem_bytes<true>()) == cudaSuccess;
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    d.ok = good && coop && d.sms > 0 && d.resident[0] > 0 && d.resident[1] > 0;
+    if (!d.ok) cudaGetLastError();
+    return d;
+}
+
+static int pick_interleave(int n_strips) {
+    for (int i : {4, 2}) if (n_strips % i == 0) return i;
+    return 1;
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct Layout {
+    Params p;
+    size_t off_status, off_flags, off_exch, off_partial, total;
+};
+
+static Layout make_layout(int B, int T, int C, bool bwd) {
+    Layout l{};
+    Params& p = l.p;
+    p.B = B; p.T = T; p.C = C;
+    p.n_chunks = (T + kTc - 1) / kTc;
+    p.n_strips = (C + kCs - 1) / kCs;
+    p.interleave = pick_interleave(p.n_strips);
+    p.n_tiles = B * p.n_strips * p.n_chunks;
+    const int levels = bwd ? 2 : 1;
+    l.off_status = 0;
+    l.off_flags = 256;
+    l.off_exch = align_up(l.off_flags + static_cast<size_t>(p.n_tiles) * levels * 4, 256);
+    l.off_partial = align_up(l.off_exch + static_cast<size_t>(p.n_tiles) * levels * kRows * kCs * 4, 256);
+    l.total = l.off_partial + (bwd ? static_cast<size_t>(p.n_tiles) * 2 * kCs * 4 : 0);
+    return l;
+}
+
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs) {
+    if (C % 4 != 0) return false;                                  // TMA row pitch must be 16-byte
+    for (const void* q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) & 15u) return false;    // TMA base alignment
+    const DeviceInfo& d = device_info();
+    if (!d.ok) return false;
+    const long long tiles = static_cast<long long>(B) * ((C + kCs - 1) / kCs) * ((T + kTc - 1) / kTc);
+    if (tiles > (1LL << 30)) return false;
+    // every peer of a tile must be reachable inside one sweep of the resident grid
+    const int n_chunks = (T + kTc - 1) / kTc;
+    const int grid = d.sms * std::min(d.resident[0], d.resident[1]);
+    return static_cast<long long>(n_chunks) * pick_interleave((C + kCs - 1) / kCs) < grid;
+}
+
+size_t workspace_bytes(int B, int T, int C, bool bwd) { return make_layout(B, T, C, bwd).total; }
+
+template <bool kBwd>
+static int launch(Layout& l, const float* w, const float* u, const float* k, const float* v, const float* gy,
+                  float* o0, float* o1, float* gwgu, void* workspace, cudaStream_t stream) {
+    Params& p = l.p;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    p.w = w; p.u = u;
+    p.status = reinterpret_cast<unsigned*>(ws + l.off_status);
+    p.flags = reinterpret_cast<unsigned*>(ws + l.off_flags);
+    p.exch = reinterpret_cast<float*>(ws + l.off_exch);
+    p.partial = reinterpret_cast<float*>(ws + l.off_partial);
+    cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
+    CUtensorMap mk, mv, mg, m0, m1;
+    bool ok = make_map(&mk, k, p.B, p.T, p.C) && make_map(&mv, v, p.B, p.T, p.C) &&
+              make_map(&m0, o0, p.B, p.T, p.C);
+    ok = ok && make_map(&mg, kBwd ? gy : k, p.B, p.T, p.C) && make_map(&m1, kBwd ? o1 : o0, p.B, p.T, p.C);
+    if (!ok) {
+        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) fp32 tensor map");
+        return -1;
+    }
+    // status word + flags start at zero
+    cudaMemsetAsync(ws, 0, l.off_exch, stream);
+    const DeviceInfo& d = device_info();
+    const int grid = std::min(p.n_tiles, d.sms * d.resident[kBwd ? 1 : 0]);
+    void* args[] = {&mk, &mv, &mg, &m0, &m1, &p};
+    const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_fused_kernel<kBwd>),
+                                                        dim3(grid), dim3(kThreads), args, smem_bytes<kBwd>(), stream);
+    if (err != cudaSuccess) {
+        set_error_detail(cudaGetErrorName(err));
+        return -1;
+    }
+    int launched = 1;
+    if (kBwd) {
+        reduce_tile_partials<<<dim3(p.n_strips, 2), dim3(32, 32), 0, stream>>>(p, gwgu);
+        ++launched;
+    }
+    return launched;
+}
+
+int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
+            void* workspace, cudaStream_t stream) {
+    Layout l = make_layout(B, T, C, false);
+    return launch<false>(l, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
+}
+
+int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+             const float* gy, float* gwgu, float* gk, float* gv, void* workspace, cudaStream_t stream) {
+    Layout l = make_layout(B, T, C, true);
+    return launch<true>(l, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+}
+
+}  // namespace fused
+}  // namespace biwkv

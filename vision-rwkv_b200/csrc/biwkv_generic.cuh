@@ -80,38 +80,41 @@ WKV_HD void fwd_aggregate_thread(const GenericShape& s, const float* w_, const f
     Acc2 right = acc2_zero();   // what this sub-chunk adds to the prefix state of the token after it
 #pragma unroll
     for (int i = 0; i < L; ++i)
-        if (i < n) { acc2_add(right, kk[i], vv[i], 1.f); acc2_decay(right, w, 1.f); }
+        if (i < n) acc2_add(right, kk[i] + w * static_cast<float>(i), vv[i], 1.f);     // anchor: token 0
+    acc2_decay(right, w, static_cast<float>(n));
     Acc2 left = acc2_zero();    // what it adds to the suffix state of the token before it
 #pragma unroll
     for (int i = L - 1; i >= 0; --i)
-        if (i < n) { acc2_add(left, kk[i], vv[i], 1.f); acc2_decay(left, w, 1.f); }
+        if (i < n) acc2_add(left, kk[i] - w * static_cast<float>(i), vv[i], 1.f);      // anchor: token 0, leftwards
+    acc2_decay(left, w, 1.f);
     float* base = carry + scratch_index(s, kFwdRows, b, sc, 0, c);
     store_acc2(base, s.C, right);
     store_acc2(base + 3 * static_cast<size_t>(s.C), s.C, left);
 }
 
 // ---- step 2: aggregates -> entering states, in place -------------------------------
+// The running exponent of the walk is kept in double: it is decremented once per sub-chunk,
+// hundreds of times along a long sequence, and in float those roundings add up to ~1e-5.
 WKV_HD void fwd_carry_thread(const GenericShape& s, const float* w_, float* carry, int b, int c) {
-    const float w = w_[c];
-    Acc2 run = acc2_zero();
-    for (int sc = 0; sc < s.NS; ++sc) {
-        float* base = carry + scratch_index(s, kFwdRows, b, sc, 0, c);
-        const Acc2 agg = load_acc2(base, s.C);
-        store_acc2(base, s.C, run);
-        const int t0 = sc * s.L;
-        const int n = (s.T - t0 < s.L) ? (s.T - t0) : s.L;
-        acc2_decay(run, w, static_cast<float>(n));
-        run = acc2_merge(run, agg);
-    }
-    run = acc2_zero();
-    for (int sc = s.NS - 1; sc >= 0; --sc) {
-        float* base = carry + scratch_index(s, kFwdRows, b, sc, 3, c);
-        const Acc2 agg = load_acc2(base, s.C);
-        store_acc2(base, s.C, run);
-        const int t0 = sc * s.L;
-        const int n = (s.T - t0 < s.L) ? (s.T - t0) : s.L;
-        acc2_decay(run, w, static_cast<float>(n));
-        run = acc2_merge(run, agg);
+    const double w = w_[c];
+    for (int dir = 0; dir < 2; ++dir) {
+        float a = 0.f, bb = 0.f;
+        double o = kMinExp;
+        for (int q = 0; q < s.NS; ++q) {
+            const int sc = dir == 0 ? q : s.NS - 1 - q;
+            float* base = carry + scratch_index(s, kFwdRows, b, sc, dir * 3, c);
+            const Acc2 agg = load_acc2(base, s.C);
+            store_acc2(base, s.C, Acc2{a, bb, static_cast<float>(o)});
+            const int t0 = sc * s.L;
+            const int n = (s.T - t0 < s.L) ? (s.T - t0) : s.L;
+            o -= w * n;
+            const double no = o > agg.o ? o : static_cast<double>(agg.o);
+            const float e1 = wkv_exp(static_cast<float>(o - no));
+            const float e2 = wkv_exp(static_cast<float>(agg.o - no));
+            a = e1 * a + e2 * agg.a;
+            bb = e1 * bb + e2 * agg.b;
+            o = no;
+        }
     }
 }
 
@@ -120,21 +123,23 @@ WKV_HD void fwd_carry_thread(const GenericShape& s, const float* w_, float* carr
 template <int L, typename Sink>
 WKV_HD void fwd_recompute(const float (&kk)[L], const float (&vv)[L], int n, float w, float u,
                           Acc2 P, Acc2 S, Sink&& sink) {
+    // S enters at the last valid token, P at token 0; both sweeps are anchored there.
     Acc2 stash[L];
+    const float last = static_cast<float>(n - 1);
 #pragma unroll
     for (int i = L - 1; i >= 0; --i) {
         if (i < n) {
-            stash[i] = S;
-            acc2_add(S, kk[i], vv[i], 1.f);
-            acc2_decay(S, w, 1.f);
+            const float d = last - static_cast<float>(i);
+            stash[i] = acc2_at(S, w, d);
+            acc2_add(S, kk[i] + w * d, vv[i], 1.f);
         }
     }
 #pragma unroll
     for (int i = 0; i < L; ++i) {
         if (i < n) {
-            sink(i, token_out(P, stash[i], kk[i], vv[i], u));
-            acc2_add(P, kk[i], vv[i], 1.f);
-            acc2_decay(P, w, 1.f);
+            const float d = static_cast<float>(i);
+            sink(i, token_out(acc2_at(P, w, d), stash[i], kk[i], vv[i], u));
+            acc2_add(P, kk[i] + w * d, vv[i], 1.f);
         }
     }
 }
@@ -199,37 +204,42 @@ WKV_HD void bwd_aggregate_thread(const GenericShape& s, const float* w_, const f
     Acc4 later = acc4_zero();     // what the outputs of this sub-chunk send to later inputs
 #pragma unroll
     for (int i = 0; i < L; ++i)
-        if (i < n) acc4_step(later, xo[i], gg[i], hh[i], w);
+        if (i < n) acc4_absorb(later, xo[i] + w * static_cast<float>(i), gg[i], hh[i]);
+    later.o -= w * static_cast<float>(n);
     Acc4 earlier = acc4_zero();   // ... and to earlier inputs
 #pragma unroll
     for (int i = L - 1; i >= 0; --i)
-        if (i < n) acc4_step(earlier, xo[i], gg[i], hh[i], w);
+        if (i < n) acc4_absorb(earlier, xo[i] - w * static_cast<float>(i), gg[i], hh[i]);
+    earlier.o -= w;
     float* out = adj + scratch_index(s, kAdjRows, b, sc, 0, c);
     store_acc4(out, s.C, later);
     store_acc4(out + 5 * static_cast<size_t>(s.C), s.C, earlier);
 }
 
 WKV_HD void bwd_carry_thread(const GenericShape& s, const float* w_, float* adj, int b, int c) {
-    const float w = w_[c];
-    Acc4 run = acc4_zero();
-    for (int sc = 0; sc < s.NS; ++sc) {
-        float* base = adj + scratch_index(s, kAdjRows, b, sc, 0, c);
-        const Acc4 agg = load_acc4(base, s.C);
-        store_acc4(base, s.C, run);
-        const int t0 = sc * s.L;
-        const int n = (s.T - t0 < s.L) ? (s.T - t0) : s.L;
-        acc4_decay(run, w, static_cast<float>(n));
-        run = acc4_merge(run, agg);
-    }
-    run = acc4_zero();
-    for (int sc = s.NS - 1; sc >= 0; --sc) {
-        float* base = adj + scratch_index(s, kAdjRows, b, sc, 5, c);
-        const Acc4 agg = load_acc4(base, s.C);
-        store_acc4(base, s.C, run);
-        const int t0 = sc * s.L;
-        const int n = (s.T - t0 < s.L) ? (s.T - t0) : s.L;
-        acc4_decay(run, w, static_cast<float>(n));
-        run = acc4_merge(run, agg);
+    const double w = w_[c];
+    for (int dir = 0; dir < 2; ++dir) {
+        float a = 0.f, bb = 0.f, ma = 0.f, mb = 0.f;
+        double o = kMinExp;
+        for (int q = 0; q < s.NS; ++q) {
+            const int sc = dir == 0 ? q : s.NS - 1 - q;
+            float* base = adj + scratch_index(s, kAdjRows, b, sc, dir * 5, c);
+            const Acc4 agg = load_acc4(base, s.C);
+            store_acc4(base, s.C, Acc4{a, bb, ma, mb, static_cast<float>(o)});
+            const int t0 = sc * s.L;
+            const int n = (s.T - t0 < s.L) ? (s.T - t0) : s.L;
+            ma += n * a;
+            mb += n * bb;
+            o -= w * n;
+            const double no = o > agg.o ? o : static_cast<double>(agg.o);
+            const float e1 = wkv_exp(static_cast<float>(o - no));
+            const float e2 = wkv_exp(static_cast<float>(agg.o - no));
+            a = e1 * a + e2 * agg.a;
+            bb = e1 * bb + e2 * agg.b;
+            ma = e1 * ma + e2 * agg.ma;
+            mb = e1 * mb + e2 * agg.mb;
+            o = no;
+        }
     }
 }
 
@@ -268,14 +278,16 @@ WKV_HD void bwd_emit_thread(const GenericShape& s, const float* w_, const float*
     Acc4 Q = load_acc4(abase + 5 * static_cast<size_t>(s.C), s.C);       // from outputs after the sub-chunk
     float gw = 0.f, gu = 0.f;
     float pk[L], pv[L];
+    const float last = static_cast<float>(n - 1);
 #pragma unroll
     for (int i = L - 1; i >= 0; --i) {
         if (i < n) {
-            const float e = wkv_exp(kk[i] + Q.o);
+            const float d = last - static_cast<float>(i);     // Q is anchored at the last valid token
+            const float e = wkv_exp(kk[i] + Q.o - w * d);
             pv[i] = e * Q.a;
             pk[i] = e * (Q.a * vv[i] - Q.b);
             gw -= e * (Q.ma * vv[i] - Q.mb);
-            acc4_step(Q, xo[i], gg[i], hh[i], w);
+            acc4_absorb(Q, xo[i] + w * d, gg[i], hh[i]);
         }
     }
     float* gk = gk_ + token_index(s, b, t0, c);
@@ -284,14 +296,15 @@ WKV_HD void bwd_emit_thread(const GenericShape& s, const float* w_, const float*
 #pragma unroll
     for (int i = 0; i < L; ++i) {
         if (i < n) {
-            const float e = wkv_exp(kk[i] + R.o);
+            const float d = static_cast<float>(i);            // R is anchored at token 0
+            const float e = wkv_exp(kk[i] + R.o - w * d);
             const float es = wkv_exp(u + kk[i] + xo[i]);
             const float self = es * (vv[i] * gg[i] - hh[i]);   // e^{u+k}(v - y) G
             gv[i * C] = pv[i] + e * R.a + es * gg[i];
             gk[i * C] = pk[i] + e * (R.a * vv[i] - R.b) + self;
             gu += self;
             gw -= e * (R.ma * vv[i] - R.mb);
-            acc4_step(R, xo[i], gg[i], hh[i], w);
+            acc4_absorb(R, xo[i] + w * d, gg[i], hh[i]);
         }
     }
     gw_out = gw;

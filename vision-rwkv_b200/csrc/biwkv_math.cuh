@@ -24,9 +24,11 @@ namespace biwkv {
 
 constexpr float kMinExp = -1e38f;
 
+// Full-accuracy exponential: this header serves the paths that must hold 1e-5 over
+// thousands of tokens for any exponent range; the packed fast path has its own ex2.
 WKV_HD float wkv_exp(float x) {
 #if defined(__CUDA_ARCH__)
-    return __expf(x);
+    return expf(x);
 #else
     return std::exp(x);
 #endif
@@ -74,6 +76,18 @@ WKV_HD void acc4_step(Acc4& s, float x, float p, float q, float w) {
     s.mb = e1 * s.mb + s.b;
     s.o = no - w;
 }
+// absorb X = e^{x}[p, q] and count one more unit of distance for everything held so far,
+// without moving the exponent: for sweeps that fold the position into x (see below)
+WKV_HD void acc4_absorb(Acc4& s, float x, float p, float q) {
+    const float no = wkv_max(s.o, x);
+    const float e1 = wkv_exp(s.o - no);
+    const float e2 = wkv_exp(x - no);
+    s.a = e1 * s.a + e2 * p;
+    s.b = e1 * s.b + e2 * q;
+    s.ma = e1 * s.ma + s.a;
+    s.mb = e1 * s.mb + s.b;
+    s.o = no;
+}
 // every term moves n tokens further away
 WKV_HD void acc4_decay(Acc4& s, float w, float n) {
     s.ma += n * s.a;
@@ -87,6 +101,15 @@ WKV_HD Acc4 acc4_merge(const Acc4& x, const Acc4& y) {
     return Acc4{e1 * x.a + e2 * y.a, e1 * x.b + e2 * y.b, e1 * x.ma + e2 * y.ma,
                 e1 * x.mb + e2 * y.mb, no};
 }
+
+// Position-anchored sweeps.  Subtracting w from the exponent once per token would add one
+// rounding of the exponent per token, a random walk that reaches 1e-5 after a few
+// thousand tokens.  The per-token loops therefore keep the state's exponent relative to a
+// fixed anchor position: a term of token i enters with exponent x_i + w * (its distance
+// from the anchor, counted against the sweep direction), and the state seen at distance d
+// from the anchor is [a, b] e^{o - w d}.  Only the hand-over between sub-chunks moves an
+// exponent, once per sub-chunk.
+WKV_HD Acc2 acc2_at(const Acc2& s, float w, float d) { return Acc2{s.a, s.b, s.o - w * d}; }
 
 // One token's output from its prefix state P, suffix state S and own term:
 //   y = (P + S + e^{u+k}[v,1]) ratio.  Also returns 1/den' and the shift m with

@@ -1,12 +1,17 @@
 // C ABI of the library: argument validation, path selection, launch accounting.
 // The contract of every function is stated in include/vrwkv_b200.h.
+#include <algorithm>
 #include <atomic>
 #include <cstdint>
+#include <cstring>
 #include "vrwkv_b200.h"
 #include "vrwkv_internal.h"
 
 namespace {
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_path{0};   // 0 auto, 1 generic only, 2 fused whenever eligible
+
+char g_detail[256] = "";
 
 inline bool misaligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) != 0; }
 
@@ -18,14 +23,25 @@ int check_shape(int B, int T, int C) {
 }
 
 int finish(int launched) {
+    if (launched < 0) { cudaGetLastError(); return VRWKV_ERR_DEVICE; }
     g_launches.fetch_add(static_cast<unsigned long long>(launched), std::memory_order_relaxed);
-    return cudaGetLastError() == cudaSuccess ? VRWKV_OK : VRWKV_ERR_LAUNCH;
+    const cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) return VRWKV_OK;
+    set_error_detail(cudaGetErrorName(err));
+    return VRWKV_ERR_LAUNCH;
 }
 }  // namespace
+
+void set_error_detail(const char* text) {
+    std::strncpy(g_detail, text ? text : "", sizeof(g_detail) - 1);
+    g_detail[sizeof(g_detail) - 1] = 0;
+}
 
 extern "C" {
 
 int vrwkv_version(void) { return 100; }
+
+const char* vrwkv_last_error_detail(void) { return g_detail; }
 
 const char* vrwkv_status_string(int status) {
     switch (status) {
@@ -33,7 +49,7 @@ const char* vrwkv_status_string(int status) {
         case VRWKV_ERR_SHAPE: return "bad shape: B, T, C must be positive, B <= 65535, T <= 4000000";
         case VRWKV_ERR_NULL: return "null pointer argument";
         case VRWKV_ERR_WORKSPACE: return "workspace smaller than the *_workspace_bytes value";
-        case VRWKV_ERR_ALIGNMENT: return "pointer not aligned to 4 bytes";
+        case VRWKV_ERR_ALIGNMENT: return "data pointer not aligned to 4 bytes, or workspace not aligned to 256 bytes";
         case VRWKV_ERR_LAUNCH: return "CUDA reported an error after a kernel launch";
         case VRWKV_ERR_DEVICE: return "required driver entry point or device attribute unavailable";
         case VRWKV_ERR_HEAD_SIZE: return "WKV6 requires C == 64 * H";
@@ -43,9 +59,27 @@ const char* vrwkv_status_string(int status) {
 
 unsigned long long vrwkv_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int vrwkv_set_path(int path) {
+    if (path < 0 || path > 2) return VRWKV_ERR_SHAPE;
+    g_path.store(path);
+    return VRWKV_OK;
+}
+
+int vrwkv_workspace_status(const void* workspace, void* stream, unsigned* status_out) {
+    if (!workspace || !status_out) return VRWKV_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(status_out, workspace, sizeof(unsigned), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        cudaGetLastError();
+        return VRWKV_ERR_LAUNCH;
+    }
+    return VRWKV_OK;
+}
+
 size_t vrwkv_biwkv_forward_workspace_bytes(int B, int T, int C) {
     if (check_shape(B, T, C) != VRWKV_OK) return 0;
-    return biwkv::generic_forward_workspace(B, T, C);
+    return std::max(biwkv::generic_forward_workspace(B, T, C) + 256,
+                    biwkv::fused::workspace_bytes(B, T, C, false));
 }
 
 int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
@@ -54,16 +88,21 @@ int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u,
     if (int st = check_shape(B, T, C)) return st;
     if (!w || !u || !k || !v || !y || !workspace) return VRWKV_ERR_NULL;
     if (misaligned4(w) || misaligned4(u) || misaligned4(k) || misaligned4(v) || misaligned4(y) ||
-        misaligned4(workspace))
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_forward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
-    return finish(biwkv::generic_forward(B, T, C, w, u, k, v, y, workspace,
-                                         static_cast<cudaStream_t>(stream)));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (g_path.load() != 1 && biwkv::fused::eligible(B, T, C, {k, v, y}))
+        return finish(biwkv::fused::forward(B, T, C, w, u, k, v, y, workspace, s));
+    // generic path: status word (first 256 bytes) is cleared, scratch follows
+    cudaMemsetAsync(workspace, 0, 256, s);
+    return finish(biwkv::generic_forward(B, T, C, w, u, k, v, y, static_cast<char*>(workspace) + 256, s));
 }
 
 size_t vrwkv_biwkv_backward_workspace_bytes(int B, int T, int C) {
     if (check_shape(B, T, C) != VRWKV_OK) return 0;
-    return biwkv::generic_backward_workspace(B, T, C);
+    return std::max(biwkv::generic_backward_workspace(B, T, C) + 256,
+                    biwkv::fused::workspace_bytes(B, T, C, true));
 }
 
 int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
@@ -72,11 +111,15 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
     if (int st = check_shape(B, T, C)) return st;
     if (!w || !u || !k || !v || !gy || !gwgu || !gk || !gv || !workspace) return VRWKV_ERR_NULL;
     if (misaligned4(w) || misaligned4(u) || misaligned4(k) || misaligned4(v) || misaligned4(gy) ||
-        misaligned4(gwgu) || misaligned4(gk) || misaligned4(gv) || misaligned4(workspace))
+        misaligned4(gwgu) || misaligned4(gk) || misaligned4(gv) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_backward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
-    return finish(biwkv::generic_backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace,
-                                          static_cast<cudaStream_t>(stream)));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (g_path.load() != 1 && biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}))
+        return finish(biwkv::fused::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s));
+    cudaMemsetAsync(workspace, 0, 256, s);
+    return finish(biwkv::generic_backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv,
+                                          static_cast<char*>(workspace) + 256, s));
 }
 
 }  // extern "C"

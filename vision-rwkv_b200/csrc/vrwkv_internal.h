@@ -2,6 +2,10 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cstddef>
+#include <initializer_list>
+
+// Remember a one-line explanation of the most recent failure (read by vrwkv_last_error_detail).
+void set_error_detail(const char* text);
 
 namespace biwkv {
 // Each launcher returns the number of kernels it enqueued.
@@ -12,4 +16,14 @@ int generic_forward(int B, int T, int C, const float* w, const float* u, const f
 int generic_backward(int B, int T, int C, const float* w, const float* u, const float* k,
                      const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                      void* workspace, cudaStream_t stream);
+namespace fused {
+// True when the fused TMA path can serve this call on the current device.
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs);
+size_t workspace_bytes(int B, int T, int C, bool bwd);
+int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+            float* y, void* workspace, cudaStream_t stream);
+int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+             const float* gy, float* gwgu, float* gk, float* gv, void* workspace,
+             cudaStream_t stream);
+}  // namespace fused
 }  // namespace biwkv

@@ -10,7 +10,24 @@ from __future__ import annotations
 
 import torch
 
+import ctypes
+
 from . import _lib
+
+# When true, every call synchronises and raises if a bounded device-side wait ran out
+# (the kernels then return garbage instead of hanging).  Off by default: it costs a sync.
+CHECK_STATUS = False
+
+
+def _check_status(lib, ws, what):
+    if not CHECK_STATUS:
+        return
+    word = ctypes.c_uint(0)
+    st = lib.vrwkv_workspace_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream,
+                                    ctypes.byref(word))
+    _lib.check(st, "vrwkv_workspace_status")
+    if word.value:
+        raise _lib.VrwkvError(f"{what}: device status word {word.value:#x} (a bounded wait ran out)")
 
 
 def _check_inputs(named):
@@ -61,7 +78,8 @@ def biwkv_forward(w, u, k, v):
         st = lib.vrwkv_biwkv_forward_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(),
                                          v.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(),
                                          stream)
-    _lib.check(st, "vrwkv_biwkv_forward_f32")
+        _lib.check(st, "vrwkv_biwkv_forward_f32")
+        _check_status(lib, ws, "vrwkv_biwkv_forward_f32")
     return y
 
 
@@ -92,5 +110,6 @@ def biwkv_backward(w, u, k, v, gy, gwgu_out=None):
                                           v.data_ptr(), gy.data_ptr(), gwgu.data_ptr(),
                                           gk.data_ptr(), gv.data_ptr(), ws.data_ptr(),
                                           ws.numel(), stream)
-    _lib.check(st, "vrwkv_biwkv_backward_f32")
+        _lib.check(st, "vrwkv_biwkv_backward_f32")
+        _check_status(lib, ws, "vrwkv_biwkv_backward_f32")
     return gwgu[0], gwgu[1], gk, gv
