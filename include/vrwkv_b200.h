@@ -86,6 +86,36 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
                              const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                              void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- WKV6 (bidirectional, head size 64) ---------------------------------------------
+ * Per (batch, head), state S in R^{64x64} [key][value], d_t = exp(-exp(w_raw_t)):
+ *   S>_{t+1} = diag(d_t) S>_t + k_t v_t^T,  S<_{t-1} = diag(d_t) S<_t + k_t v_t^T
+ *   y_t = r_t^T (S>_t + diag(u) k_t v_t^T) + r_t^T S<_t
+ * r, k, v, w_raw, y, gy and the gradients are (B, T, C) with C = 64 H; u and gu are (H, 64).
+ * Inputs must be 16-byte aligned.
+ *
+ * vrwkv_wkv6_forward_f32 replaces
+ *   cuda_forward(int B,int T,int C,int H,float*r,float*k,float*v,float*w,float*u,float*y)
+ *       CLS/cuda_v6/wkv6_op.cpp:4,7-9 (kernel CLS/cuda_v6/wkv6_cuda.cu:6-97,348-353)
+ * It takes the raw decay input and forms -exp(w_raw) itself, where the reference's Python
+ * wrapper does that in a separate pass (CLS/vrwkv6.py:48).
+ */
+int vrwkv_wkv6_forward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                           const float* w_raw, const float* u, float* y, void* stream);
+
+/* vrwkv_wkv6_backward_f32 replaces
+ *   cuda_backward(int B,int T,int C,int H,float*r,...,float*gy,float*gr,float*gk,float*gv,
+ *                 float*gw,float*gu)
+ *       CLS/cuda_v6/wkv6_op.cpp:5,10-12 (kernels CLS/cuda_v6/wkv6_cuda.cu:99-346,355-362)
+ * without its T <= 256 limit.  gw is the gradient w.r.t. w_raw (as in the reference, whose
+ * kernels multiply by -exp(w_raw)); gu is already summed over batch (the reference returns
+ * (B, C) and sums in Python, CLS/vrwkv6.py:69).
+ */
+size_t vrwkv_wkv6_backward_workspace_bytes(int B, int T, int C, int H);
+int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                            const float* w_raw, const float* u, const float* gy, float* gr, float* gk,
+                            float* gv, float* gw, float* gu, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,133 @@
+"""WKV6 on the GPU, through the C ABI, against the float64 oracle.
+
+Tolerance: max|x - ref| / max|ref| <= 1e-5 per tensor for float32 inputs; 1e-2 when the
+caller hands bfloat16 tensors (the oracle then sees the same bf16-rounded values).
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err
+from oracle import wkv6_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 1e-5
+NAMES = ("y", "gr", "gk", "gv", "gw", "gu")
+
+
+def run_gpu(dev, r, k, v, w, u, gy, H):
+    from vision_rwkv_b200 import ops
+    f = [x.float().contiguous().to(dev) for x in (r, k, v, w, u, gy)]
+    y = ops.wkv6_forward(*f[:5], H)
+    grads = ops.wkv6_backward(*f, H)
+    torch.cuda.synchronize()
+    return (y,) + tuple(grads)
+
+
+def reference(r, k, v, w, u, gy, H):
+    d = [x.float().double() for x in (r, k, v, w, u, gy)]
+    return (O.wkv6_forward(*d[:5], H),) + tuple(O.wkv6_backward(*d, H))
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 1, 1), (2, 2, 1), (1, 3, 2), (2, 15, 1), (1, 16, 3), (1, 17, 2),
+                                   (2, 37, 2), (1, 70, 1), (1, 196, 2), (1, 300, 1)])
+def test_parity_with_oracle(cuda_device, B, T, H):
+    args = O.make_inputs(B, T, 64 * H, H, seed=T)
+    got = run_gpu(cuda_device, *args, H)
+    ref = reference(*args, H)
+    errs = {}
+    scale = max(float(rf.abs().max()) for rf in ref)
+    for name, g, rf in zip(NAMES, got, ref):
+        assert torch.isfinite(g).all(), name
+        if rf.abs().max() == 0:
+            # e.g. gw for T <= 2: a difference of two equal sums, zero only up to rounding
+            assert g.abs().max().item() <= TOL * scale, name
+            continue
+        errs[name] = rel_err(g.reshape(rf.shape), rf)
+    assert all(e <= TOL for e in errs.values()), errs
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "wkv6_*.npz"))))
+def test_golden_vectors(cuda_device, path):
+    z = np.load(path)
+    H = int(z["H"])
+    args = [torch.from_numpy(z[n]) for n in ("r", "k", "v", "w", "u", "gy")]
+    got = run_gpu(cuda_device, *args, H)
+    for g, name in zip(got, NAMES):
+        rf = torch.from_numpy(z[name])
+        assert rel_err(g.reshape(rf.shape), rf) <= TOL, name
+
+
+def test_long_sequence_forward_and_backward_slice(cuda_device):
+    """T = 4096 forward against the oracle for one head, and T = 1024 backward (beyond the
+    reference's own T <= 256 limit)."""
+    H = 1
+    r, k, v, w, u, gy = O.make_inputs(1, 4096, 64, H, seed=9)
+    from vision_rwkv_b200 import ops
+    f = [x.float().contiguous().to(cuda_device) for x in (r, k, v, w, u)]
+    y = ops.wkv6_forward(*f, H)
+    with torch.no_grad():
+        ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
+    assert rel_err(y, ref) <= TOL
+    args = O.make_inputs(1, 1024, 64, H, seed=10)
+    got = run_gpu(cuda_device, *args, H)
+    for g, rf, name in zip(got, reference(*args, H), NAMES):
+        assert rel_err(g.reshape(rf.shape), rf) <= (3e-5 if name == "gw" else TOL), name
+
+
+def test_heads_and_batches_are_independent(cuda_device):
+    B, T, H = 3, 50, 4
+    args = O.make_inputs(B, T, 64 * H, H, seed=4)
+    full = run_gpu(cuda_device, *args, H)
+    r, k, v, w, u, gy = args
+    b, h = 2, 1
+    sl = slice(64 * h, 64 * h + 64)
+    one = run_gpu(cuda_device, r[b:b + 1, :, sl], k[b:b + 1, :, sl], v[b:b + 1, :, sl], w[b:b + 1, :, sl],
+                  u[h:h + 1], gy[b:b + 1, :, sl], 1)
+    for name, f, o in zip(NAMES[:5], full[:5], one[:5]):
+        assert torch.equal(f[b:b + 1, :, sl], o), name
+
+
+def test_bitwise_reproducible(cuda_device):
+    args = O.make_inputs(2, 90, 128, 2, seed=5)
+    a = run_gpu(cuda_device, *args, 2)
+    b = run_gpu(cuda_device, *args, 2)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+def test_autograd_surface(cuda_device):
+    from vision_rwkv_b200.vrwkv6 import RUN_CUDA_RWKV6
+    B, T, H = 2, 40, 2
+    C = 64 * H
+    r, k, v, w, u, gy = O.make_inputs(B, T, C, H, seed=6)
+    xs = [x.float().to(cuda_device).requires_grad_(True) for x in (r, k, v, w, u)]
+    y = RUN_CUDA_RWKV6(B, T, C, H, *xs)
+    assert y.dtype == torch.float32 and y.shape == (B, T, C)
+    y.backward(gy.float().to(cuda_device))
+    ref = reference(r, k, v, w, u, gy, H)
+    assert rel_err(y, ref[0]) <= TOL
+    for x, rf in zip(xs, ref[1:]):
+        assert x.grad.shape == rf.shape and rel_err(x.grad, rf) <= TOL
+    with pytest.raises(AssertionError):
+        RUN_CUDA_RWKV6(B, T, C, H + 1, *xs)
+    with pytest.raises(AssertionError):
+        RUN_CUDA_RWKV6(B, T, C, H, xs[0].transpose(0, 1), *xs[1:])
+
+
+def test_bf16_inputs(cuda_device):
+    from vision_rwkv_b200.vrwkv6 import RUN_CUDA_RWKV6
+    B, T, H = 2, 196, 2
+    C = 64 * H
+    r, k, v, w, u, gy = O.make_inputs(B, T, C, H, seed=7, round_to=torch.bfloat16)
+    xs = [x.to(torch.bfloat16).to(cuda_device).requires_grad_(True) for x in (r, k, v)]
+    xs += [w.float().to(cuda_device).requires_grad_(True), u.float().to(cuda_device).requires_grad_(True)]
+    y = RUN_CUDA_RWKV6(B, T, C, H, *xs)
+    y.backward(gy.float().to(cuda_device))
+    ref = reference(r, k, v, w, u, gy, H)
+    assert rel_err(y, ref[0]) <= 1e-2
+    for x, rf in zip(xs, ref[1:]):
+        assert rel_err(x.grad.float(), rf) <= 1e-2

@@ -49,7 +49,7 @@ const char* vrwkv_status_string(int status) {
         case VRWKV_ERR_SHAPE: return "bad shape: B, T, C must be positive, B <= 65535, T <= 4000000";
         case VRWKV_ERR_NULL: return "null pointer argument";
         case VRWKV_ERR_WORKSPACE: return "workspace smaller than the *_workspace_bytes value";
-        case VRWKV_ERR_ALIGNMENT: return "data pointer not aligned to 4 bytes, or workspace not aligned to 256 bytes";
+        case VRWKV_ERR_ALIGNMENT: return "pointer alignment: data 4 bytes (WKV6 inputs 16 bytes), workspace 256 bytes";
         case VRWKV_ERR_LAUNCH: return "CUDA reported an error after a kernel launch";
         case VRWKV_ERR_DEVICE: return "required driver entry point or device attribute unavailable";
         case VRWKV_ERR_HEAD_SIZE: return "WKV6 requires C == 64 * H";
@@ -120,6 +120,46 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
     cudaMemsetAsync(workspace, 0, 256, s);
     return finish(biwkv::generic_backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv,
                                           static_cast<char*>(workspace) + 256, s));
+}
+
+// ---- WKV6 ---------------------------------------------------------------------------------------
+static int check_wkv6(int B, int T, int C, int H) {
+    if (B <= 0 || T <= 0 || C <= 0 || H <= 0) return VRWKV_ERR_SHAPE;
+    if (C != 64 * H) return VRWKV_ERR_HEAD_SIZE;
+    if (static_cast<long long>(B) * H > 2000000000LL || T > 4000000) return VRWKV_ERR_SHAPE;
+    return VRWKV_OK;
+}
+static inline bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+size_t vrwkv_wkv6_backward_workspace_bytes(int B, int T, int C, int H) {
+    if (check_wkv6(B, T, C, H) != VRWKV_OK) return 0;
+    return wkv6::backward_workspace(B, T, H);
+}
+
+int vrwkv_wkv6_forward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                           const float* w_raw, const float* u, float* y, void* stream) {
+    if (int st = check_wkv6(B, T, C, H)) return st;
+    if (!r || !k || !v || !w_raw || !u || !y) return VRWKV_ERR_NULL;
+    if (misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(w_raw) || misaligned4(u) ||
+        misaligned4(y))
+        return VRWKV_ERR_ALIGNMENT;
+    return finish(wkv6::forward(B, T, H, r, k, v, w_raw, u, y, static_cast<cudaStream_t>(stream)));
+}
+
+int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                            const float* w_raw, const float* u, const float* gy, float* gr, float* gk,
+                            float* gv, float* gw, float* gu, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+    if (int st = check_wkv6(B, T, C, H)) return st;
+    if (!r || !k || !v || !w_raw || !u || !gy || !gr || !gk || !gv || !gw || !gu || !workspace)
+        return VRWKV_ERR_NULL;
+    if (misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(w_raw) || misaligned16(gy) ||
+        misaligned4(u) || misaligned4(gr) || misaligned4(gk) || misaligned4(gv) || misaligned4(gw) ||
+        misaligned4(gu) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return VRWKV_ERR_ALIGNMENT;
+    if (workspace_bytes < wkv6::backward_workspace(B, T, H)) return VRWKV_ERR_WORKSPACE;
+    return finish(wkv6::backward(B, T, H, r, k, v, w_raw, u, gy, gr, gk, gv, gw, gu, workspace,
+                                 static_cast<cudaStream_t>(stream)));
 }
 
 }  // extern "C"

@@ -27,3 +27,12 @@ int backward(int B, int T, int C, const float* w, const float* u, const float* k
              cudaStream_t stream);
 }  // namespace fused
 }  // namespace biwkv
+
+namespace wkv6 {
+size_t backward_workspace(int B, int T, int H);
+int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw,
+            const float* u, float* y, cudaStream_t stream);
+int backward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw,
+             const float* u, const float* gy, float* gr, float* gk, float* gv, float* gw, float* gu,
+             void* workspace, cudaStream_t stream);
+}  // namespace wkv6

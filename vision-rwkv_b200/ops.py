@@ -113,3 +113,53 @@ def biwkv_backward(w, u, k, v, gy, gwgu_out=None):
         _lib.check(st, "vrwkv_biwkv_backward_f32")
         _check_status(lib, ws, "vrwkv_biwkv_backward_f32")
     return gwgu[0], gwgu[1], gk, gv
+
+
+def _wkv6_shapes(r, k, v, w, u, H, gy=None):
+    if r.dim() != 3:
+        raise RuntimeError(f"r must be (B, T, C), got {tuple(r.shape)}")
+    B, T, C = r.shape
+    for name, t in (("k", k), ("v", v), ("w", w)) + ((("gy", gy),) if gy is not None else ()):
+        if t.shape != r.shape:
+            raise RuntimeError(f"{name} must have the shape of r")
+    if C != 64 * H:
+        raise RuntimeError(f"head size must be 64: C={C}, H={H}")
+    if u.numel() != C:
+        raise RuntimeError(f"u must hold C={C} values")
+    return B, T, C
+
+
+def wkv6_forward(r, k, v, w, u, H):
+    """y (float32) of the bidirectional WKV6; w is the raw decay input (decay = exp(-exp(w)))."""
+    dev = _check_inputs((("r", r), ("k", k), ("v", v), ("w", w), ("u", u)))
+    B, T, C = _wkv6_shapes(r, k, v, w, u, H)
+    lib = _lib.load()
+    y = torch.empty((B, T, C), device=dev, dtype=torch.float32)
+    if y.numel() == 0:
+        return y
+    with torch.cuda.device(dev):
+        st = lib.vrwkv_wkv6_forward_f32(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                        w.data_ptr(), u.data_ptr(), y.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_wkv6_forward_f32")
+    return y
+
+
+def wkv6_backward(r, k, v, w, u, gy, H):
+    """(gr, gk, gv, gw, gu); gw w.r.t. the raw decay input, gu of shape (H, 64)."""
+    dev = _check_inputs((("r", r), ("k", k), ("v", v), ("w", w), ("u", u), ("gy", gy)))
+    B, T, C = _wkv6_shapes(r, k, v, w, u, H, gy)
+    lib = _lib.load()
+    gr, gk, gv, gw = (torch.empty((B, T, C), device=dev, dtype=torch.float32) for _ in range(4))
+    gu = torch.empty((H, C // H), device=dev, dtype=torch.float32)
+    if gr.numel() == 0:
+        return gr, gk, gv, gw, gu.zero_()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_wkv6_backward_workspace_bytes(B, T, C, H), dev)
+        st = lib.vrwkv_wkv6_backward_f32(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                         w.data_ptr(), u.data_ptr(), gy.data_ptr(), gr.data_ptr(),
+                                         gk.data_ptr(), gv.data_ptr(), gw.data_ptr(), gu.data_ptr(),
+                                         ws.data_ptr(), ws.numel(),
+                                         torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_wkv6_backward_f32")
+    return gr, gk, gv, gw, gu

@@ -1,0 +1,51 @@
+"""Drop-in for the WKV6 autograd surface of VRWKV6:
+`WKV_6` and `RUN_CUDA_RWKV6(B, T, C, H, r, k, v, w, u)` of
+classification/mmcls_custom/models/backbones/vrwkv6.py:22-73.
+
+Kept: the argument list, `HEAD_SIZE == C // H` and the contiguity asserts (:38-46, :61), a
+float32 `y`, gradients `(None, None, None, None, gr, gk, gv, gw, gu)` with `gw` taken w.r.t.
+the raw `w` and `gu` of shape (H, C // H) (:69-70).  Dropped: `T_MAX = 256`, a limit of the
+reference's backward kernels only.  The reference's extension reads every tensor as float32;
+here half / bfloat16 inputs are accepted too and cast up for the kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+HEAD_SIZE = 64
+
+
+def _f32(x):
+    return x if x.dtype == torch.float32 else x.float()
+
+
+class WKV_6(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, B, T, C, H, r, k, v, w, u):
+        with torch.no_grad():
+            assert HEAD_SIZE == C // H
+            ctx.B, ctx.T, ctx.C, ctx.H = B, T, C, H
+            assert r.is_contiguous()
+            assert k.is_contiguous()
+            assert v.is_contiguous()
+            assert w.is_contiguous()
+            assert u.is_contiguous()
+            if tuple(r.shape) != (B, T, C):
+                raise RuntimeError(f"r has shape {tuple(r.shape)}, expected {(B, T, C)}")
+            ctx.save_for_backward(r, k, v, w, u)
+            return ops.wkv6_forward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), H)
+
+    @staticmethod
+    def backward(ctx, gy):
+        with torch.no_grad():
+            assert gy.is_contiguous()
+            r, k, v, w, u = ctx.saved_tensors
+            gr, gk, gv, gw, gu = ops.wkv6_backward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u),
+                                                   _f32(gy), ctx.H)
+            return (None, None, None, None, gr, gk, gv, gw, gu.view(ctx.H, ctx.C // ctx.H))
+
+
+def RUN_CUDA_RWKV6(B, T, C, H, r, k, v, w, u):
+    return WKV_6.apply(B, T, C, H, r, k, v, w, u)
