@@ -86,6 +86,22 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
                              const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                              void* workspace, size_t workspace_bytes, void* stream);
 
+/* vrwkv_biwkv_forward_f32_noalloc has no counterpart in the reference.  It is
+ * vrwkv_biwkv_forward_f32 for callers that cannot allocate device memory and so have no
+ * workspace to pass (a host that owns all device memory and lends only inputs and outputs,
+ * a loop running under a frozen memory plan, code inside a region where allocation is
+ * forbidden).  Its scratch is a 16 MiB array built into the library's device image, present
+ * once on every GPU that loads the library until the process exits.
+ *   - A shape is accepted when B * ceil(T / 16) * 24 * C bytes fit in 16 MiB (for example
+ *     B=2, T=196, C=192, or B=4, T=1024, C=768); larger shapes return VRWKV_ERR_WORKSPACE.
+ *   - The first call on a device also looks up the array's device address; make that call
+ *     before starting any stream capture.  No call allocates or frees.
+ *   - All calls on a device share the array: two calls that can overlap on the GPU (different
+ *     streams with no ordering between them) race; calls on one stream do not.
+ * Results equal vrwkv_biwkv_forward_f32's generic path bit for bit. */
+int vrwkv_biwkv_forward_f32_noalloc(int B, int T, int C, const float* w, const float* u,
+                                    const float* k, const float* v, float* y, void* stream);
+
 /* ---- WKV6 (bidirectional, head size 64) ---------------------------------------------
  * Per (batch, head), state S in R^{64x64} [key][value], d_t = exp(-exp(w_raw_t)):
  *   S>_{t+1} = diag(d_t) S>_t + k_t v_t^T,  S<_{t-1} = diag(d_t) S<_t + k_t v_t^T

@@ -37,6 +37,8 @@ void set_error_detail(const char* text) {
     g_detail[sizeof(g_detail) - 1] = 0;
 }
 
+int record_launches(int launched) { return finish(launched); }
+
 extern "C" {
 
 int vrwkv_version(void) { return 100; }

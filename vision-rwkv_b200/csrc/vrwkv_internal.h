@@ -6,6 +6,8 @@
 
 // Remember a one-line explanation of the most recent failure (read by vrwkv_last_error_detail).
 void set_error_detail(const char* text);
+// Add `launched` kernels to the process-wide count and turn the CUDA error state into a status.
+int record_launches(int launched);
 
 namespace biwkv {
 // Each launcher returns the number of kernels it enqueued.
