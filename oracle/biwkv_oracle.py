@@ -4,10 +4,14 @@ Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark
 may import this module; the product path (the CUDA library and its Python
 wrappers) never does.
 
-PARITY UNPINNED: the reference repository holds no test, golden vector or CPU
-implementation for this operator, and its CUDA kernels cannot run where this
-file was written (no GPU).  The functions below restate the *recurrence* those
-kernels evaluate, following
+PARITY PIN: the reference repository holds no test, golden vector or CPU
+implementation for this operator.  What pins this oracle is the reference's own
+CUDA kernel, compiled in place into oracle/_ref/ (build_ref.py) and run on the GPU
+by tests/test_reference_kernels_gpu.py: for T <= 32 its output and its gw/gu equal
+`biwkv_scan_forward/backward` to float32 accuracy; for T > 32 it equals
+`biwkv_reference_quirk_forward` (the closed form of its in-segment deviation, ~1e-3
+away from the recurrence) and its gk/gv carry an extra e^{w} on the cross terms.
+The functions below restate the *recurrence* those kernels evaluate, following
 
   classification/mmcls_custom/models/backbones/cuda_new/bi_wkv_kernel.cu:21-116
       (forward: per (batch, channel) prefix and suffix sums of e^{k_j - w*dist}

@@ -3,8 +3,11 @@
 Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark
 may import this module; the product path never does.
 
-PARITY UNPINNED: the reference holds no test or golden vector for this operator
-and its kernels are CUDA-only.  This file restates the recurrence of
+PARITY PIN: the reference holds no test or golden vector for this operator.  What
+pins this oracle is the reference's own CUDA kernels, compiled in place into
+oracle/_ref/ (build_ref.py) and run on the GPU by tests/test_reference_kernels_gpu.py:
+forward and all five gradients agree with the functions below to float32 accuracy
+for T up to the reference's limit of 256.  This file restates the recurrence of
 
   classification/mmcls_custom/models/backbones/cuda_v6/wkv6_cuda.cu:6-97
       (forward: a reverse sweep without bonus, :23-57, then a forward sweep with
