@@ -24,8 +24,8 @@
 // add the rescaled values, so the exponentials are independent and pipeline.
 //
 // The kernel is launched cooperatively with one CTA per resident slot and walks the tile
-// list round-robin; consecutive tile ids are the chunks of one (sequence, strip block), so
-// the peers of a tile are in flight at the same time on other SMs.  A tile only waits for
+// list round-robin; consecutive tile ids are the chunks of one (sequence, strip), so the
+// peers of a tile are in flight at the same time on neighbouring CTAs.  A tile only waits for
 // tiles whose ids differ by less than the grid size, all started by resident CTAs, so the
 // wait cannot deadlock; it is bounded anyway and sets bit 0 of the workspace status word
 // instead of hanging.
@@ -672,10 +672,10 @@ static const DeviceInfo& device_info() {
     return d;
 }
 
-static int pick_interleave(int n_strips) {
-    for (int i : {4, 2}) if (n_strips % i == 0) return i;
-    return 1;
-}
+// Strips whose tiles alternate in the id order.  Measured on B200 (B=64, T=4096, C=768):
+// 1 -> 1.21 / 2.74 ms (forward / backward), 2 -> 1.43 / 3.28, 4 -> 1.39 / 3.29, 8 -> 1.58 / 3.45:
+// keeping the peers of a tile on adjacent CTAs matters more than sharing DRAM pages.
+static int pick_interleave(int /*n_strips*/) { return 1; }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
