@@ -132,6 +132,28 @@ int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const fl
                             float* gv, float* gw, float* gu, void* workspace, size_t workspace_bytes,
                             void* stream);
 
+/* ---- Q-Shift + token-mix interpolation (the step in front of the K/V/R projections) ----
+ * x is (B, H*W, C), tokens in raster order.  xx = x with channel group g (`group` channels
+ * each, group = int(C * channel_gamma)) moved by `shift` pixels: g=0 right, g=1 left, g=2 down,
+ * g=3 up, zero fill at the image border, channels beyond 4*group copied.  Outputs
+ * out[m] = x * mix[m] + xx * (1 - mix[m]), m < n_out (1..3), mix[m] of shape (C,).
+ * `mix`, `out`, `gout`, `gmix` are host arrays of n_out device pointers.
+ *
+ * Replaces the tensor-op sequence q_shift(...) followed by the n_out lerps of
+ *   VRWKV_SpatialMix.jit_func   CLS/vrwkv.py:156-164  (n_out = 3: xk, xv, xr)
+ *   VRWKV_ChannelMix.forward    CLS/vrwkv.py:247-250  (n_out = 2: xk, xr)
+ *   q_shift                     CLS/vrwkv.py:68-79
+ * The backward returns gx and gmix[m] (C,), the latter summed over batch and tokens in a
+ * fixed order. */
+int vrwkv_qshift_mix_forward_f32(int B, int H, int W, int C, int group, int shift, int n_out,
+                                 const float* x, const float* const* mix, float* const* out,
+                                 void* stream);
+size_t vrwkv_qshift_mix_backward_workspace_bytes(int B, int H, int W, int C, int n_out);
+int vrwkv_qshift_mix_backward_f32(int B, int H, int W, int C, int group, int shift, int n_out,
+                                  const float* x, const float* const* mix, const float* const* gout,
+                                  float* gx, float* const* gmix, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,34 @@
+"""CPU oracle for Q-Shift and the token-mix interpolation.  TEST INFRASTRUCTURE ONLY.
+
+Restates, with index arithmetic instead of slice assignments,
+classification/mmcls_custom/models/backbones/vrwkv.py:68-79 (`q_shift`: four channel groups of
+int(C * gamma) channels moved by `shift_pixel` pixels right, left, down, up on the H x W token
+grid with zero fill; remaining channels copied) and :156-164 (out = x * mix + xx * (1 - mix)).
+Pinned by construction: it is a permutation with zero fill, checked in the tests against an
+independent formulation by padded 2-D shifts and by torch.autograd for the gradients.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def q_shift(x, resolution, shift_pixel=1, gamma=0.25):
+    B, T, C = x.shape
+    H, W = resolution
+    g = int(C * gamma)
+    grid = x.reshape(B, H, W, C)
+    out = torch.zeros_like(grid)
+    s = shift_pixel
+    if s < W:
+        out[:, :, s:, 0:g] = grid[:, :, :W - s, 0:g]
+        out[:, :, :W - s, g:2 * g] = grid[:, :, s:, g:2 * g]
+    if s < H:
+        out[:, s:, :, 2 * g:3 * g] = grid[:, :H - s, :, 2 * g:3 * g]
+        out[:, :H - s, :, 3 * g:4 * g] = grid[:, s:, :, 3 * g:4 * g]
+    out[..., 4 * g:] = grid[..., 4 * g:]
+    return out.reshape(B, T, C)
+
+
+def qshift_mix(x, mixes, resolution, shift_pixel=1, gamma=0.25):
+    xx = q_shift(x, resolution, shift_pixel, gamma)
+    return [x * m + xx * (1 - m) for m in mixes]

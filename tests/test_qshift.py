@@ -1,0 +1,55 @@
+"""Q-Shift + mix: the oracle against an independent formulation (CPU), and the fused CUDA
+kernels against the oracle (GPU, bit-exact forward: it is one fma per output)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from conftest import rel_err
+from oracle import qshift_oracle as O
+
+
+def shift_by_padding(x, resolution, s, gamma):
+    B, T, C = x.shape
+    H, W = resolution
+    g = int(C * gamma)
+    img = x.transpose(1, 2).reshape(B, C, H, W)
+    out = img.clone()
+    out[:, 0:g] = F.pad(img[:, 0:g], (s, 0, 0, 0))[..., :W]
+    out[:, g:2 * g] = F.pad(img[:, g:2 * g], (0, s, 0, 0))[..., s:]
+    out[:, 2 * g:3 * g] = F.pad(img[:, 2 * g:3 * g], (0, 0, s, 0))[:, :, :H]
+    out[:, 3 * g:4 * g] = F.pad(img[:, 3 * g:4 * g], (0, 0, 0, s))[:, :, s:]
+    return out.flatten(2).transpose(1, 2)
+
+
+@pytest.mark.parametrize("B,H,W,C,s,gamma", [(2, 5, 7, 16, 1, 0.25), (1, 14, 14, 36, 1, 0.25),
+                                             (1, 4, 3, 10, 2, 0.2), (1, 1, 6, 8, 1, 0.25)])
+def test_oracle_matches_padded_shift(B, H, W, C, s, gamma):
+    x = torch.randn(B, H * W, C, dtype=torch.float64)
+    assert torch.equal(O.q_shift(x, (H, W), s, gamma), shift_by_padding(x, (H, W), s, gamma))
+
+
+CASES = [(2, 14, 14, 192, 1, 0.25, 3), (1, 5, 7, 16, 1, 0.25, 2), (2, 3, 4, 10, 1, 0.2, 3),
+         (1, 50, 84, 768, 1, 0.25, 3), (1, 6, 6, 36, 2, 0.25, 1), (3, 1, 9, 8, 1, 0.25, 2)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,H,W,C,s,gamma,n", CASES)
+def test_fused_kernel_matches_oracle(cuda_device, B, H, W, C, s, gamma, n):
+    from vision_rwkv_b200.qshift import qshift_mix
+    g = torch.Generator().manual_seed(B * 100 + C)
+    x = torch.randn(B, H * W, C, generator=g)
+    mixes = [torch.rand(1, 1, C, generator=g) for _ in range(n)]
+    gouts = [torch.randn(B, H * W, C, generator=g) for _ in range(n)]
+    xr = x.double().requires_grad_(True)
+    mr = [m.double().requires_grad_(True) for m in mixes]
+    ref = O.qshift_mix(xr, mr, (H, W), s, gamma)
+    torch.autograd.backward(ref, [go.double() for go in gouts])
+    xd = x.to(cuda_device).requires_grad_(True)
+    md = [m.to(cuda_device).requires_grad_(True) for m in mixes]
+    outs = qshift_mix(xd, md, (H, W), s, gamma)
+    torch.autograd.backward(outs, [go.to(cuda_device) for go in gouts])
+    for o, r in zip(outs, ref):
+        assert rel_err(o, r.detach()) < 1e-6
+    assert rel_err(xd.grad, xr.grad) < 1e-6
+    for a, b in zip(md, mr):
+        assert a.grad.shape == b.grad.shape and rel_err(a.grad, b.grad) < 1e-5

@@ -163,3 +163,66 @@ def wkv6_backward(r, k, v, w, u, gy, H):
                                          torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_wkv6_backward_f32")
     return gr, gk, gv, gw, gu
+
+
+def _ptr_array(tensors):
+    arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    return arr
+
+
+def _qshift_args(x, mixes, resolution, shift_pixel, gamma):
+    if x.dim() != 3:
+        raise RuntimeError(f"x must be (B, T, C), got {tuple(x.shape)}")
+    B, T, C = x.shape
+    H, W = resolution
+    if H * W != T:
+        raise RuntimeError(f"patch resolution {H}x{W} does not match T={T}")
+    if not 1 <= len(mixes) <= 3:
+        raise RuntimeError("between one and three mix vectors")
+    if gamma > 0.25:
+        raise RuntimeError("channel_gamma must be <= 1/4")            # the reference asserts the same
+    group = int(C * gamma)
+    if group <= 0:
+        raise RuntimeError(f"int(C * gamma) = 0 for C={C}")
+    for m in mixes:
+        if m.numel() != C:
+            raise RuntimeError(f"mix vectors must hold C={C} values")
+    return B, H, W, C, group
+
+
+def qshift_mix_forward(x, mixes, resolution, shift_pixel=1, gamma=0.25):
+    """[x * mix + q_shift(x) * (1 - mix) for mix in mixes], one fused pass."""
+    dev = _check_inputs([("x", x)] + [(f"mix{i}", m) for i, m in enumerate(mixes)])
+    B, H, W, C, group = _qshift_args(x, mixes, resolution, shift_pixel, gamma)
+    lib = _lib.load()
+    outs = [torch.empty_like(x) for _ in mixes]
+    if x.numel() == 0:
+        return outs
+    with torch.cuda.device(dev):
+        st = lib.vrwkv_qshift_mix_forward_f32(B, H, W, C, group, shift_pixel, len(mixes), x.data_ptr(),
+                                              _ptr_array(mixes), _ptr_array(outs),
+                                              torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_qshift_mix_forward_f32")
+    return outs
+
+
+def qshift_mix_backward(x, mixes, gouts, resolution, shift_pixel=1, gamma=0.25):
+    """(gx, [gmix...]) for `qshift_mix_forward`."""
+    dev = _check_inputs([("x", x)] + [(f"mix{i}", m) for i, m in enumerate(mixes)]
+                        + [(f"gout{i}", g) for i, g in enumerate(gouts)])
+    B, H, W, C, group = _qshift_args(x, mixes, resolution, shift_pixel, gamma)
+    if len(gouts) != len(mixes) or any(g.shape != x.shape for g in gouts):
+        raise RuntimeError("one output gradient of the shape of x per mix vector")
+    lib = _lib.load()
+    gx = torch.empty_like(x)
+    gmix = [torch.empty(C, dtype=torch.float32, device=dev) for _ in mixes]
+    if x.numel() == 0:
+        return gx, [g.zero_() for g in gmix]
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_qshift_mix_backward_workspace_bytes(B, H, W, C, len(mixes)), dev)
+        st = lib.vrwkv_qshift_mix_backward_f32(B, H, W, C, group, shift_pixel, len(mixes), x.data_ptr(),
+                                               _ptr_array(mixes), _ptr_array(gouts), gx.data_ptr(),
+                                               _ptr_array(gmix), ws.data_ptr(), ws.numel(),
+                                               torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_qshift_mix_backward_f32")
+    return gx, gmix
