@@ -149,6 +149,73 @@ def run_reference_arm(args):
     }))
 
 
+def _timed(fn, dev, world, dist, iters, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    return ms / iters
+
+
+def side_measurements(dev, world, dist):
+    """Model-level and second-operator figures, per-GPU work fixed, summed over ranks."""
+    from vision_rwkv_b200 import ops
+    from vision_rwkv_b200.backbone import build
+    out = {}
+    # VRWKV-B (embed 768, 12 blocks, patch 16) inference on 224x224 synthetic images, batch-sharded,
+    # bf16 autocast for the linear layers, fp32 Bi-WKV: no collective
+    B = 64
+    model = build("vrwkv_b").to(dev).eval()
+    img = torch.randn(B, 3, 224, 224, device=dev)
+
+    def infer():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            model(img)
+
+    ms = _timed(infer, dev, world, dist, iters=5)
+    out["vrwkv_b_inference"] = {"img_per_s": B * world / (ms * 1e-3), "ms_per_batch": ms,
+                                "batch_per_gpu": B, "resolution": 224, "n_gpus": world,
+                                "gemm_dtype": "bf16 autocast", "wkv_dtype": "f32"}
+    del model, img
+    # WKV6 operator as in VRWKV6-B: C=768, 12 heads, B=32 per GPU, T=196, fwd+bwd (exact fp32 sweeps)
+    Bw, T, H = 32, 196, 12
+    C = 64 * H
+    g = torch.Generator(device=dev).manual_seed(7)
+    r, k6, v6, gy6 = (torch.randn(Bw, T, C, device=dev, generator=g) for _ in range(4))
+    w6 = torch.randn(Bw, T, C, device=dev, generator=g) * 0.5 - 0.6
+    u6 = torch.randn(H, 64, device=dev, generator=g) * 0.1
+
+    def wkv6_step():
+        ops.wkv6_forward(r, k6, v6, w6, u6, H)
+        ops.wkv6_backward(r, k6, v6, w6, u6, gy6, H)
+
+    ms = _timed(wkv6_step, dev, world, dist, iters=5)
+    out["wkv6_fwd_bwd"] = {"ms": ms, "B_per_gpu": Bw, "T": T, "C": C, "H": H, "dtype": "f32",
+                           "elements_per_s": Bw * T * C * world / (ms * 1e-3)}
+    # fused Q-Shift + 3 interpolations, forward: 16 bytes per element
+    Bq, Hh, Ww, Cq = 64, 64, 64, 768
+    x = torch.randn(Bq, Hh * Ww, Cq, device=dev, generator=g)
+    mixes = [torch.rand(Cq, device=dev, generator=g) for _ in range(3)]
+    ms = _timed(lambda: ops.qshift_mix_forward(x, mixes, (Hh, Ww)), dev, world, dist, iters=10)
+    gbs = 16 * x.numel() / (ms * 1e-3) / 1e9
+    peak, _ = measured_peak()
+    out["qshift_mix_forward"] = {"ms": ms, "algorithmic_GBps": gbs, "frac_of_hbm_peak": gbs / peak,
+                                 "shape": [Bq, Hh * Ww, Cq], "outputs": 3}
+    return out
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -161,6 +228,8 @@ def main():
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"], help="sequences per GPU")
     ap.add_argument("--tokens", type=int, default=WORKLOAD["T"])
     ap.add_argument("--channels", type=int, default=WORKLOAD["C"])
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the model-level and WKV6 side measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -297,6 +366,13 @@ def main():
                "d2h_bytes_per_step": (3 * E + 2 * C) * 4 * world}
         del hk, hv, hgy, out_y, out_gk, out_gv
 
+    # ---- side measurements (not the headline): VRWKV-B inference img/s, WKV6 op, Q-Shift ----
+    secondary = None
+    if not args.no_secondary:
+        del k, v, gy
+        torch.cuda.empty_cache()
+        secondary = side_measurements(dev, world, dist if world > 1 else None)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -335,7 +411,7 @@ def main():
                    "collective": "one all-reduce of gw|gu (2,C) per step" if world > 1 else "none",
                    "l2": "inputs (2.4 GB per pass) exceed the 126 MB L2; no explicit flush"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
-        "clocks": clocks,
+        "clocks": clocks, "secondary": secondary,
     }))
     if world > 1:
         dist.barrier()
