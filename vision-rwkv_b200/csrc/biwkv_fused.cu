@@ -126,11 +126,17 @@ struct Entering {
     Acc2 right;   // state entering it at its last position
 };
 
-// One exchange level for one warp (see the file header).  own_right / own_left: this
-// sub-chunk's aggregates, relative to the position after its 16-token span / before it.
-__device__ __forceinline__ Entering exchange(const Params& p, float* sub, float* ext, int lane, int warp,
-                                             float w, int tile, int chunk, int level, int levels,
-                                             const Acc4& own_right, const Acc2& own_left) {
+struct Inside {
+    Acc4 inP;     // what the earlier sub-chunks of the same tile send to this one
+    Acc2 inS;     // ... and the later ones
+};
+
+// First half of an exchange level for one warp (steps 1-2 of the file header): post, sum the
+// rest of the tile, publish the tile aggregate.  own_right / own_left: this sub-chunk's
+// aggregates, relative to the position after its 16-token span / before it.
+__device__ __forceinline__ Inside exchange_publish(const Params& p, float* sub, int lane, int warp, float w,
+                                                   int tile, int level, int levels, const Acc4& own_right,
+                                                   const Acc2& own_left) {
     post_acc4(sub + warp * kRecFloats + lane, own_right);
     post_acc2(sub + warp * kRecFloats + lane, own_left);
     __syncthreads();
@@ -188,6 +194,15 @@ __device__ __forceinline__ Entering exchange(const Params& p, float* sub, float*
             atomicAdd(p.flags + static_cast<size_t>(tile) * levels + level, 1u);
         }
     }
+    return Inside{inP, inS};
+}
+
+// Second half (steps 3-4): collect the other tiles' aggregates and form the entering states.
+__device__ __forceinline__ Entering exchange_collect(const Params& p, float* ext, int lane, int warp, float w,
+                                                     int tile, int chunk, int level, int levels,
+                                                     const Inside& in) {
+    const Acc4 inP = in.inP;
+    const Acc2 inS = in.inS;
     // (3) the records of the tiles j = warp, warp + 8, ... of this (sequence, strip)
     {
         const int first = tile - chunk * p.interleave;
@@ -289,6 +304,14 @@ __device__ __forceinline__ Entering exchange(const Params& p, float* sub, float*
         out.right = merge2(S, inS);
     }
     return out;
+}
+
+// A whole exchange level, for kernels that hold the tile while the peers publish.
+__device__ __forceinline__ Entering exchange(const Params& p, float* sub, float* ext, int lane, int warp,
+                                             float w, int tile, int chunk, int level, int levels,
+                                             const Acc4& own_right, const Acc2& own_left) {
+    const Inside in = exchange_publish(p, sub, lane, warp, w, tile, level, levels, own_right, own_left);
+    return exchange_collect(p, ext, lane, warp, w, tile, chunk, level, levels, in);
 }
 
 // ---- per-token max-shifted path (any exponent range) -------------------------------------------
@@ -585,6 +608,195 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     if (threadIdx.x == 0) sm100::tma_store_wait_all();
 }
 
+// ---- forward, pipelined ---------------------------------------------------------------------------
+// The forward needs one exchange level only, and its tile is small enough (32 KB) to keep three
+// of them per CTA.  That allows the two halves of the exchange to be pulled apart in time: in
+// iteration n a CTA first *publishes* tile n (aggregates, inside sums, tile record + flag), then
+// *finishes* tile n-1 (collect the peers' records, emit y, store), and the third stage receives
+// tile n+1 meanwhile.  The peers of tile n-1 published a whole iteration ago, so the collect step
+// finds their flags set instead of waiting for the slowest of them.  Between the two halves a
+// thread carries only its eight inside sums in registers.  Deadlock freedom is unchanged: a
+// CTA publishes tile n before it may wait for anything belonging to tile n-1.
+constexpr int kFwdStages = 3;
+
+// per-token max-shifted path, split in the same two halves (forward only)
+__device__ __noinline__ void rigorous_aggregates(const float* ks, const float* vs, int n, float w, Acc4& right,
+                                                 Acc2& left) {
+    right = acc4_zero();
+    left = acc2_zero();
+    for (int i = 0; i < n; ++i) acc4_absorb(right, ks[i * kCs] + w * static_cast<float>(i), vs[i * kCs], 1.f);
+    for (int i = n - 1; i >= 0; --i) acc2_add(left, ks[i * kCs] - w * static_cast<float>(i), vs[i * kCs], 1.f);
+    right.o -= w * static_cast<float>(n);
+    acc4_decay(right, w, static_cast<float>(kL - n));
+    left.o -= w;
+}
+__device__ __noinline__ void rigorous_emit_forward(float* ks, const float* vs, int n, float w, float u,
+                                                   const Entering& e) {
+    const float last = static_cast<float>(n - 1);
+    Acc2 S = e.right;
+    acc2_decay(S, w, static_cast<float>(kL - n));
+    Acc2 stash[kL];
+    for (int i = n - 1; i >= 0; --i) {
+        const float d = last - static_cast<float>(i);
+        stash[i] = acc2_at(S, w, d);
+        acc2_add(S, ks[i * kCs] + w * d, vs[i * kCs], 1.f);
+    }
+    Acc2 P{e.left.a, e.left.b, e.left.o};
+    for (int i = 0; i < n; ++i) {
+        const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+        const TokenOut o = token_out(acc2_at(P, w, d), stash[i], k, v, u);
+        ks[i * kCs] = o.y;
+        acc2_add(P, k + w * d, v, 1.f);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                               const __grid_constant__ CUtensorMap map_y, const Params p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    float* stage_base = reinterpret_cast<float*>(smem_raw);                         // [3][2][kTc][kCs]
+    float* sub = stage_base + kFwdStages * 2 * kSlotFloats;                         // [kWarps][kRows][kCs]
+    float* ext = sub + kWarps * kRecFloats;                                         // [kWarps][kRows][kCs]
+    uint64_t* full = reinterpret_cast<uint64_t*>(ext + kWarps * kRecFloats);        // [3]
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kFwdStages; ++s) sm100::mbar_init(&full[s], 1);
+        sm100::mbar_init_fence();
+    }
+    __syncthreads();
+
+    const int G = static_cast<int>(gridDim.x);
+    const int first = static_cast<int>(blockIdx.x);
+    const int mine = first < p.n_tiles ? (p.n_tiles - first + G - 1) / G : 0;      // tiles of this CTA
+    auto issue_loads = [&](int n) {
+        const int stage = n % kFwdStages;
+        const TileCoord tc = decode_tile(p, first + n * G);
+        float* dst = stage_base + stage * 2 * kSlotFloats;
+        sm100::mbar_expect_tx(&full[stage], 2u * kSlotFloats * sizeof(float));
+        sm100::tma_load_3d(dst, &map_k, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+        sm100::tma_load_3d(dst + kSlotFloats, &map_v, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+    };
+    if (threadIdx.x == 0)
+        for (int n = 0; n < kFwdStages && n < mine; ++n) issue_loads(n);
+
+    Inside prev_in{acc4_zero(), acc2_zero()};
+    bool prev_safe = true;
+    for (int n = 0; n <= mine; ++n) {
+        Inside cur_in{acc4_zero(), acc2_zero()};
+        bool cur_safe = true;
+        if (n < mine) {
+            // ---- publish tile n ----
+            const int tile = first + n * G;
+            const int stage = n % kFwdStages;
+            const TileCoord tc = decode_tile(p, tile);
+            const int c = tc.strip * kCs + lane;
+            const float w = (c < p.C) ? p.w[c] : 0.f;
+            const float u = (c < p.C) ? p.u[c] : 0.f;
+            if (!sm100::mbar_wait(&full[stage], (n / kFwdStages) & 1, kSpinLimit)) atomicOr(p.status, 2u);
+            const int nv = max(0, min(kL, p.T - (tc.chunk * kTc + warp * kL)));
+            const float* ks = stage_base + stage * 2 * kSlotFloats + (warp * kL) * kCs + lane;
+            const float* vs = ks + kSlotFloats;
+            float kk[kL], vv[kL];
+            float m = kMinExp, mn = 1e38f;
+#pragma unroll
+            for (int i = 0; i < kL; ++i) {
+                kk[i] = ks[i * kCs];
+                vv[i] = vs[i * kCs];
+                if (i < nv) { m = wkv_max(m, kk[i]); mn = fminf(mn, kk[i]); }
+            }
+            const bool safe = (nv == 0) || ((m - mn) + fabsf(w) * kL + fabsf(u) <= kFastRange);
+            cur_safe = __all_sync(0xffffffffu, safe);
+            Acc4 own_right;
+            Acc2 own_left;
+            if (!cur_safe) {
+                rigorous_aggregates(ks, vs, nv, w, own_right, own_left);
+            } else {
+                const float lam = fast_exp(-w);
+                const float2 lam2 = f2(lam, lam);
+                float2 a = f2(0.f, 0.f), a2 = f2(0.f, 0.f);
+                float mu = lam;
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    const float e = (i < nv) ? fast_exp(kk[i] - m) : 0.f;
+                    const float2 x = f2(e * vv[i], e);
+                    a = mul2(add2(a, x), lam2);                 // rightward: relative to the span's end
+                    a2 = fma2(x, f2(mu, mu), a2);               // leftward: weight lambda^{i+1}
+                    mu *= lam;
+                }
+                own_right = Acc4{a.x, a.y, 0.f, 0.f, m};
+                own_left = Acc2{a2.x, a2.y, m};
+            }
+            cur_in = exchange_publish(p, sub, lane, warp, w, tile, 0, 1, own_right, own_left);
+            // the stage that tile n-2 left gets tile n+1 (its store was issued an iteration ago)
+            if (threadIdx.x == 0 && n >= 2 && n + 1 < mine) {
+                sm100::tma_store_wait_read();
+                issue_loads(n + 1);
+            }
+        }
+        if (n >= 1) {
+            // ---- finish tile n-1 ----
+            const int tile = first + (n - 1) * G;
+            const int stage = (n - 1) % kFwdStages;
+            const TileCoord tc = decode_tile(p, tile);
+            const int c = tc.strip * kCs + lane;
+            const float w = (c < p.C) ? p.w[c] : 0.f;
+            const float u = (c < p.C) ? p.u[c] : 0.f;
+            const int nv = max(0, min(kL, p.T - (tc.chunk * kTc + warp * kL)));
+            float* slot_k = stage_base + stage * 2 * kSlotFloats;
+            float* ks = slot_k + (warp * kL) * kCs + lane;
+            const float* vs = ks + kSlotFloats;
+            const Entering e1 = exchange_collect(p, ext, lane, warp, w, tile, tc.chunk, 0, 1, prev_in);
+            if (!prev_safe) {
+                rigorous_emit_forward(ks, vs, nv, w, u, e1);
+            } else {
+                float kk[kL], vv[kL];
+                float m = kMinExp;
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    kk[i] = ks[i * kCs];
+                    vv[i] = vs[i * kCs];
+                    if (i < nv) m = wkv_max(m, kk[i]);
+                }
+                const float lam = fast_exp(-w);
+                const float2 lam2 = f2(lam, lam);
+                const Acc4 cp = e1.left;
+                const Acc2 cs = e1.right;
+                const float M = wkv_max(m, wkv_max(cp.o, cs.o));
+                const float fp = fast_exp(cp.o - M), fs = fast_exp(cs.o - M);
+                const float eu = fast_exp(u);
+                float2 pr = f2(cp.a * fp, cp.b * fp);
+                float2 sf = f2(cs.a * fs, cs.b * fs);
+                float2 stash[kL];
+#pragma unroll
+                for (int i = kL - 1; i >= 0; --i) {
+                    stash[i] = sf;
+                    const float e = (i < nv) ? fast_exp(kk[i] - M) : 0.f;
+                    kk[i] = e;                                   // reused by the emit sweep
+                    sf = mul2(add2(sf, f2(e * vv[i], e)), lam2);
+                }
+#pragma unroll
+                for (int i = 0; i < kL; ++i) {
+                    const float2 x = f2(kk[i] * vv[i], kk[i]);
+                    const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
+                    ks[i * kCs] = __fdividef(nd.x, nd.y);
+                    pr = mul2(add2(pr, x), lam2);
+                }
+            }
+            sm100::fence_proxy_async_smem();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                sm100::tma_store_3d(&map_y, slot_k, tc.strip * kCs, tc.chunk * kTc, tc.b);
+                sm100::tma_store_commit();
+            }
+        }
+        prev_in = cur_in;
+        prev_safe = cur_safe;
+    }
+    if (threadIdx.x == 0) sm100::tma_store_wait_all();
+}
+
 // out[j][c] = sum over the tiles of channel c's strip of partial[tile][j][c % 32]
 __global__ void __launch_bounds__(1024)
 reduce_tile_partials(Params p, float* __restrict__ out) {
@@ -638,6 +850,10 @@ static bool make_map(CUtensorMap* map, const float* base, int B, int T, int C) {
                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static constexpr size_t fwd_pipelined_smem_bytes() {
+    return (kFwdStages * 2 * kSlotFloats + 2 * kWarps * kRecFloats) * sizeof(float) + 64;
+}
+
 struct DeviceInfo {
     int sms = 0;
     int resident[2] = {0, 0};   // CTAs per SM, forward / backward
@@ -661,8 +877,10 @@ static const DeviceInfo& device_info() {
                                         static_cast<int>(smem_bytes<false>())) == cudaSuccess;
     good = good && cudaFuncSetAttribute(biwkv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem_bytes<true>())) == cudaSuccess;
-    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[0], biwkv_fused_kernel<false>,
-                                                                 kThreads, smem_bytes<false>()) == cudaSuccess;
+    good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(fwd_pipelined_smem_bytes())) == cudaSuccess;
+    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[0], biwkv_forward_pipelined_kernel,
+                                                                 kThreads, fwd_pipelined_smem_bytes()) == cudaSuccess;
     good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[1], biwkv_fused_kernel<true>,
                                                                  kThreads, smem_bytes<true>()) == cudaSuccess;
     int coop = 0;
@@ -741,8 +959,12 @@ static int launch(Layout& l, const float* w, const float* u, const float* k, con
     const DeviceInfo& d = device_info();
     const int grid = std::min(p.n_tiles, d.sms * d.resident[kBwd ? 1 : 0]);
     void* args[] = {&mk, &mv, &mg, &m0, &m1, &p};
-    const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_fused_kernel<kBwd>),
-                                                        dim3(grid), dim3(kThreads), args, smem_bytes<kBwd>(), stream);
+    void* fwd_args[] = {&mk, &mv, &m0, &p};
+    const cudaError_t err =
+        kBwd ? cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_fused_kernel<true>), dim3(grid),
+                                           dim3(kThreads), args, smem_bytes<true>(), stream)
+             : cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_forward_pipelined_kernel), dim3(grid),
+                                           dim3(kThreads), fwd_args, fwd_pipelined_smem_bytes(), stream);
     if (err != cudaSuccess) {
         set_error_detail(cudaGetErrorName(err));
         return -1;
@@ -769,3 +991,4 @@ int backward(int B, int T, int C, const float* w, const float* u, const float* k
 
 }  // namespace fused
 }  // namespace biwkv
+
