@@ -209,24 +209,37 @@ __device__ __forceinline__ Entering exchange_collect(const Params& p, float* ext
         Acc4 P = acc4_zero();
         Acc2 S = acc2_zero();
         for (int j0 = warp; j0 < p.n_chunks; j0 += 4 * kWarps) {
+            // Poll the (up to four) flags of the batch together: independent relaxed loads, one
+            // round trip through L2 for all of them.  The record loads below take their address
+            // from the polled values (`dep`, always zero, but only known once the flags have come
+            // back), so they cannot be issued before the flags were seen set; the publisher put a
+            // fence between its record and its flag, and both sides go through L2 (ld.cg), so a
+            // set flag implies a visible record without an acquire fence in every warp.
             bool ok = true;
+            const unsigned* fl[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int j = j0 + q * kWarps;
-                if (j < p.n_chunks && j != chunk) {
-                    const unsigned* f = p.flags + static_cast<size_t>(first + j * p.interleave) * levels + level;
-                    uint32_t spins = 0;
-                    while (sm100::flag_acquire(f) < 2u) {
-                        // give up after ~0.1 s, or at once if any wait of this launch already did
-                        if (++spins > kSpinLimit ||
-                            ((spins & 1023u) == 0u && *reinterpret_cast<volatile unsigned*>(p.status) != 0u)) {
-                            ok = false;
-                            break;
-                        }
-                        if (spins > 16) __nanosleep(64);
-                    }
-                }
+                fl[q] = (j < p.n_chunks && j != chunk)
+                            ? p.flags + static_cast<size_t>(first + j * p.interleave) * levels + level
+                            : nullptr;
             }
+            unsigned seen[4] = {0u, 0u, 0u, 0u};
+            for (uint32_t spins = 0;; ++spins) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (seen[q] < 2u) seen[q] = fl[q] ? sm100::flag_relaxed(fl[q]) : 2u;   // only what is still missing
+                if (seen[0] >= 2u && seen[1] >= 2u && seen[2] >= 2u && seen[3] >= 2u) break;
+                // give up after ~0.1 s, or at once if any wait of this launch already did
+                if (spins > kSpinLimit ||
+                    ((spins & 1023u) == 1023u && *reinterpret_cast<volatile unsigned*>(p.status) != 0u)) {
+                    ok = false;
+                    break;
+                }
+                __nanosleep(spins < 8 ? 32 : 128);
+            }
+            const unsigned seen_all = seen[0] | seen[1] | seen[2] | seen[3];
+            const size_t dep = seen_all >> 31;
             if (!ok && lane == 0) atomicOr(p.status, 1u);
             // all loads of the batch first, then the arithmetic
             float r0[4], r1[4], r2[4], r3[4], x[4];
@@ -237,7 +250,7 @@ __device__ __forceinline__ Entering exchange_collect(const Params& p, float* ext
                 r0[q] = r1[q] = r2[q] = r3[q] = 0.f;
                 x[q] = kMinExp;
                 if (j < p.n_chunks && j != chunk) {
-                    const float* rec = p.exch + (static_cast<size_t>(first + j * p.interleave) * levels + level) * kRecFloats + lane;
+                    const float* rec = p.exch + (static_cast<size_t>(first + j * p.interleave) * levels + level) * kRecFloats + lane + dep;
                     if (j < chunk) {
                         r0[q] = sm100::ld_cg(rec); r1[q] = sm100::ld_cg(rec + kCs);
                         r2[q] = sm100::ld_cg(rec + 2 * kCs); r3[q] = sm100::ld_cg(rec + 3 * kCs);

@@ -95,6 +95,11 @@ __device__ __forceinline__ unsigned flag_acquire(const unsigned* flag) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned flag_relaxed(const unsigned* flag) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    return v;
+}
 // load that bypasses L1 (data another SM wrote during this kernel)
 __device__ __forceinline__ float ld_cg(const float* p) { return __ldcg(p); }
 
