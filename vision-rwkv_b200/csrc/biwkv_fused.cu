@@ -1,5 +1,6 @@
-// Bi-WKV "fused" path: one persistent kernel per forward, one per backward, each
-// element of k, v (and gy) crossing HBM once in and each output once out.
+// Bi-WKV "fused" path: one persistent kernel per forward (biwkv_forward_pipelined_kernel), one
+// per backward (biwkv_fused_kernel<true>), each element of k, v (and gy) crossing HBM once in
+// and each output once out.
 //
 // Work unit ("tile"): kTc = 128 consecutive tokens x kCs = 32 consecutive channels of
 // one sequence.  A CTA is 8 warps; warp s owns the sub-chunk of kL = 16 tokens
@@ -886,8 +887,6 @@ static const DeviceInfo& device_info() {
     if (d.ok) return d;
     cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
     bool good = encode_fn() != nullptr;
-    good = good && cudaFuncSetAttribute(biwkv_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(smem_bytes<false>())) == cudaSuccess;
     good = good && cudaFuncSetAttribute(biwkv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem_bytes<true>())) == cudaSuccess;
     good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
