@@ -118,6 +118,16 @@ int vrwkv_biwkv_forward_f32_noalloc(int B, int T, int C, const float* w, const f
 int vrwkv_wkv6_forward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
                            const float* w_raw, const float* u, float* y, void* stream);
 
+/* vrwkv_wkv6_forward_tc_f32: the same forward on the tensor cores (tcgen05, state in tensor
+ * memory): r, k, v and the state copy enter the matrix products rounded to bfloat16, sums are
+ * fp32.  Results agree with vrwkv_wkv6_forward_f32 to about 1e-2 of max|y|: meant for callers
+ * whose r, k, v are bfloat16 already.  `workspace`: 256 bytes, 256-byte aligned; its first word is
+ * a status word as in vrwkv_workspace_status.  Stands in for the same reference entry point as
+ * vrwkv_wkv6_forward_f32. */
+int vrwkv_wkv6_forward_tc_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                              const float* w_raw, const float* u, float* y, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
 /* vrwkv_wkv6_backward_f32 replaces
  *   cuda_backward(int B,int T,int C,int H,float*r,...,float*gy,float*gr,float*gk,float*gv,
  *                 float*gw,float*gu)

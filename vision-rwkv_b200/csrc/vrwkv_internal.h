@@ -38,3 +38,9 @@ int backward(int B, int T, int H, const float* r, const float* k, const float* v
              const float* u, const float* gy, float* gr, float* gk, float* gv, float* gw, float* gu,
              void* workspace, cudaStream_t stream);
 }  // namespace wkv6
+
+namespace wkv6tc {
+// Tensor-core forward (bf16 operands, fp32 state).  `status` points at 4 writable device bytes.
+int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw,
+            const float* u, float* y, unsigned* status, cudaStream_t stream);
+}  // namespace wkv6tc
