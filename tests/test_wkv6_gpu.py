@@ -131,3 +131,99 @@ def test_bf16_inputs(cuda_device):
     assert rel_err(y, ref[0]) <= 1e-2
     for x, rf in zip(xs, ref[1:]):
         assert rel_err(x.grad.float(), rf) <= 1e-2
+
+
+# ---- tensor-core forward (tcgen05, bf16 operands): tolerance 1e-2 of max|y| -------------------
+TC_TOL = 1e-2
+
+
+def run_tc(dev, r, k, v, w, u, H):
+    from vision_rwkv_b200 import ops
+    f = [x.float().contiguous().to(dev) for x in (r, k, v, w, u)]
+    y = ops.wkv6_forward(*f, H, tensor_cores=True)     # raises if the kernel's status word is set
+    torch.cuda.synchronize()
+    return y
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 1, 1), (2, 2, 1), (1, 3, 2), (2, 15, 1), (1, 16, 3), (1, 17, 2), (1, 31, 1),
+                                   (2, 37, 2), (1, 64, 1), (1, 70, 1), (3, 196, 2), (1, 300, 1), (1, 1024, 1)])
+def test_tensor_core_forward_parity(cuda_device, B, T, H):
+    r, k, v, w, u, _ = O.make_inputs(B, T, 64 * H, H, seed=T, round_to=torch.bfloat16)
+    y = run_tc(cuda_device, r, k, v, w, u, H)
+    ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
+    assert torch.isfinite(y).all()
+    assert rel_err(y, ref) <= TC_TOL
+
+
+@pytest.mark.parametrize("shift", [1.0, 1.7, 2.6, 4.0])
+def test_tensor_core_forward_strong_decay(cuda_device, shift):
+    """A block whose accumulated log-decay passes 80 in some channel scores pairwise on the CUDA cores; the
+    shifts cover none / some / all blocks taking that path, and one head only."""
+    B, T, H = 2, 100, 2
+    r, k, v, w, u, _ = O.make_inputs(B, T, 64 * H, H, seed=11, round_to=torch.bfloat16)
+    w = w.clone()
+    w[..., :64] += shift            # head 0 decays fast, head 1 stays mild
+    y = run_tc(cuda_device, r, k, v, w, u, H)
+    ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
+    assert torch.isfinite(y).all()
+    assert rel_err(y, ref) <= TC_TOL
+    # per head too: the mild head must not be hurt by its neighbour
+    assert rel_err(y[..., 64:], ref[..., 64:]) <= TC_TOL
+
+
+def test_tensor_core_forward_matches_exact_sweeps_at_scale(cuda_device):
+    """Full-size check without the oracle: both kernels on the same inputs, T = 4096."""
+    from vision_rwkv_b200 import ops
+    B, T, H = 2, 4096, 3
+    C = 64 * H
+    g = torch.Generator(device="cpu").manual_seed(3)
+    r, k, v = [torch.randn(B, T, C, generator=g).to(cuda_device) for _ in range(3)]
+    w = (torch.randn(B, T, C, generator=g) * 0.5 - 0.6).to(cuda_device)
+    u = (torch.randn(H, 64, generator=g) * 0.1).to(cuda_device)
+    y_tc = ops.wkv6_forward(r, k, v, w, u, H, tensor_cores=True)
+    y_ex = ops.wkv6_forward(r, k, v, w, u, H)
+    assert rel_err(y_tc, y_ex.double().cpu()) <= TC_TOL
+
+
+def test_tensor_core_forward_reproducible_and_independent(cuda_device):
+    r, k, v, w, u, _ = O.make_inputs(2, 90, 128, 2, seed=5, round_to=torch.bfloat16)
+    a = run_tc(cuda_device, r, k, v, w, u, 2)
+    b = run_tc(cuda_device, r, k, v, w, u, 2)
+    assert torch.equal(a, b)
+    one = run_tc(cuda_device, r[1:], k[1:], v[1:], w[1:], u, 2)
+    assert torch.equal(one[0], a[1])
+
+
+def test_tensor_core_forward_c_abi_errors(cuda_device):
+    """Direct C-ABI calls: alignment and workspace checks come back as status codes, nothing launches."""
+    from vision_rwkv_b200 import _lib
+    lib = _lib.load()
+    B, T, H = 1, 32, 1
+    C = 64
+    x = torch.zeros(B * T * C + 4, device=cuda_device)
+    out = torch.empty(B * T * C + 4, device=cuda_device)
+    u = torch.zeros(C, device=cuda_device)
+    ws = torch.zeros(512, dtype=torch.uint8, device=cuda_device)
+    p, y = x.data_ptr(), out.data_ptr()
+    ok = lib.vrwkv_wkv6_forward_tc_f32(B, T, C, H, p, p, p, p, u.data_ptr(), y, ws.data_ptr(), 256, 0)
+    torch.cuda.synchronize()
+    assert ok == 0
+    assert lib.vrwkv_wkv6_forward_tc_f32(B, T, C, H, p, p, p, p, u.data_ptr(), y + 4, ws.data_ptr(), 256, 0) == 4
+    assert lib.vrwkv_wkv6_forward_tc_f32(B, T, C, H, p, p, p, p, u.data_ptr(), y, ws.data_ptr(), 8, 0) == 3
+    assert lib.vrwkv_wkv6_forward_tc_f32(B, T, C + 1, H, p, p, p, p, u.data_ptr(), y, ws.data_ptr(), 256, 0) == 7
+    assert lib.vrwkv_wkv6_forward_tc_f32(B, T, C, H, p, p, 0, p, u.data_ptr(), y, ws.data_ptr(), 256, 0) == 2
+
+
+def test_autograd_picks_tensor_cores_for_half_inputs(cuda_device, monkeypatch):
+    from vision_rwkv_b200 import ops, vrwkv6
+    seen = []
+    real = ops.wkv6_forward
+    monkeypatch.setattr(ops, "wkv6_forward", lambda *a, **kw: (seen.append(kw.get("tensor_cores")), real(*a, **kw))[1])
+    B, T, H = 1, 48, 1
+    r, k, v, w, u, _ = O.make_inputs(B, T, 64, H, seed=2, round_to=torch.bfloat16)
+    dev = cuda_device
+    vrwkv6.RUN_CUDA_RWKV6(B, T, 64, H, *[x.float().to(dev) for x in (r, k, v, w, u)])
+    vrwkv6.RUN_CUDA_RWKV6(B, T, 64, H, *[x.bfloat16().to(dev) for x in (r, k, v)], w.float().to(dev), u.float().to(dev))
+    monkeypatch.setattr(vrwkv6, "FORWARD_PATH", "exact")
+    vrwkv6.RUN_CUDA_RWKV6(B, T, 64, H, *[x.bfloat16().to(dev) for x in (r, k, v)], w.float().to(dev), u.float().to(dev))
+    assert seen == [False, True, False]

@@ -47,6 +47,7 @@
 #include <initializer_list>
 #include "biwkv_math.cuh"
 #include "sm100_async.cuh"
+#include "tensor_map.h"
 #include "vrwkv_internal.h"
 
 namespace biwkv {
@@ -837,31 +838,8 @@ reduce_tile_partials(Params p, float* __restrict__ out) {
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(ptr);
-    }();
-    return fn;
-}
-
 static bool make_map(CUtensorMap* map, const float* base, int B, int T, int C) {
-    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 4, static_cast<cuuint64_t>(T) * C * 4};
-    const cuuint32_t box[3] = {kCs, kTc, 1};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box,
-                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return tensor_map::make_btc_f32(map, base, B, T, C, kCs, kTc);
 }
 
 static constexpr size_t fwd_pipelined_smem_bytes() {
@@ -886,7 +864,7 @@ static const DeviceInfo& device_info() {
     DeviceInfo& d = infos[dev & 63];
     if (d.ok) return d;
     cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
-    bool good = encode_fn() != nullptr;
+    bool good = tensor_map::encode_fn() != nullptr;
     good = good && cudaFuncSetAttribute(biwkv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem_bytes<true>())) == cudaSuccess;
     good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

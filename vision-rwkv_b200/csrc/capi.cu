@@ -154,7 +154,7 @@ int vrwkv_wkv6_forward_tc_f32(int B, int T, int C, int H, const float* r, const 
     if (int st = check_wkv6(B, T, C, H)) return st;
     if (!r || !k || !v || !w_raw || !u || !y || !workspace) return VRWKV_ERR_NULL;
     if (misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(w_raw) || misaligned4(u) ||
-        misaligned4(y) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        misaligned16(y) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < 256) return VRWKV_ERR_WORKSPACE;
     return finish(wkv6tc::forward(B, T, H, r, k, v, w_raw, u, y, static_cast<unsigned*>(workspace),

@@ -5,21 +5,25 @@
 // at a time; for every 16-token block, with a_t = sum of log-decays of the block's tokens
 // before t and A = a_16, all matrix work runs as UMMA instructions (M = 128, fp32 accumulate):
 //
-//   P^T (16 x 16)  = Kb (16 x 64) . Rs^T        Kb[s][i] = k_s[i] e^{-a_{s+1}[i]},  Rs[t][i] = r_t[i] e^{a_t[i]}
+//   P (16 x 16)    = Rs (16 x 64) . Kb^T        Rs[t][i] = r_t[i] e^{a_t[i]},  Kb[s][i] = k_s[i] e^{-a_{s+1}[i]}
 //                    masked to s < t, the diagonal replaced by the bonus  sum_i r_t[i] u[i] k_t[i]
 //   y^T (64 x 16)  = S^T (64 x 64, bf16 copy) . Rs^T  +  V^T (64 x 16) . P^T
 //   S^T (64 x 64) += V^T (64 x 16) . Ks         Ks[t][i] = k_t[i] e^{A[i] - a_{t+1}[i]}
 //                    after S^T was scaled by e^{A[i]} per key column on its way through registers
 //
-// The rows of Kb sit in rows 64..79 of the state operand, so the score product is the same
+// The rows of Rs also sit in rows 64..79 of the state operand, so the score product is the same
 // instruction shape as the read-out and lands in TMEM lanes 64..79, which an otherwise idle warp
 // owns.  e^{-a_{s+1}} grows with the decay; a block whose accumulated log-decay exceeds 80 in any
 // channel evaluates its 16 x 16 scores pairwise on the CUDA cores instead (every exponent <= 0
 // there), so nothing overflows however strong the decay is.  The leftward direction is the same
 // walk over the reversed sequence without the bonus; one CTA runs both and adds the second into
 // the first.  The state never leaves the SM: per block it makes one round trip TMEM -> registers
-// -> TMEM (decay) and leaves a bf16 copy in shared memory as the next A operand.  The next
-// block's r, k, v, w are fetched into registers while the current block is processed.
+// -> TMEM (decay) and leaves a bf16 copy in shared memory as the next A operand.
+//
+// Data movement: r, k, v, w tiles (16 tokens x 64 channels) arrive by TMA, the next block's while
+// the current one is on the tensor core; y tiles leave by TMA store (rightward) and TMA reduce-add
+// (leftward).  All bf16 operand writes are 16-byte shared stores (2-byte shared stores measured
+// two orders of magnitude slower here), which fixes the thread-to-element maps of the operand phase.
 //
 // Accuracy is that of bf16 operands with fp32 accumulation (about 1e-2 of max|y|); the exact fp32
 // sweeps of wkv6_sweeps.cu remain the default for float32 callers.
@@ -28,6 +32,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include "sm100_async.cuh"
+#include "tensor_map.h"
 #include "vrwkv_internal.h"
 
 namespace wkv6tc {
@@ -52,21 +58,26 @@ struct Args {
 };
 
 struct __align__(1024) Smem {
-    __nv_bfloat16 opS[128 * 64];      // A: rows 0..63 = S^T (value x key), rows 64..79 = Kb (token x key)
+    __nv_bfloat16 opS[128 * 64];      // A: rows 0..63 = S^T (value x key), rows 64..79 = Rs (token x key)
     __nv_bfloat16 opV[128 * 16];      // A of the update and of the in-block part: V^T, rows = value, K = token
     __nv_bfloat16 opR[16 * 64];       // B of the read-out and of the scores: rows = token, K = key
     __nv_bfloat16 opK[64 * 16];       // B of the update: rows = key, K = token
     __nv_bfloat16 opP[16 * 16];       // B of the in-block part: rows = token t, K = token s
-    float raw[4][SC][N];              // r, k, v, w of the block (fp32)
-    float acum[SC + 1][N];            // a_0 .. a_16 per key channel (pairwise score path only)
+    __nv_bfloat16 opKb[16 * 64];      // B of the scores: rows = token s, K = key
+    float raw[4][SC][N];              // r, k, v, w of the block as the copy engine delivers them (memory order)
+    float ytile[SC][N];               // this block's output on its way to global memory (memory order)
+    float acum[SC + 1][N];            // running log-decay sums: rows 0..8 from the block start, rows 9..16 from token 8
+    float diag[SC];                   // bonus terms  sum_i r_t[i] u[i] k_t[i]
     float dtot[N];
     float u[N];
     uint64_t bar_main;
     uint64_t bar_score;
+    uint64_t bar_load;
     uint32_t tmem_base;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+using sm100::smem_u32;
+
 
 // canonical K-major, no swizzle: element (row, k) of a [rows x K] bf16 operand
 __device__ __forceinline__ int op_index(int rows, int row, int k) { return (k >> 3) * (rows * 8) + row * 8 + (k & 7); }
@@ -113,53 +124,18 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// Bounded wait on an mbarrier phase; false if it ran out.
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0,1,0,p;\n\t}"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (i > 64) __nanosleep(32);
-    }
-    return false;
+// y tile += shared tile (fp32), through the copy engine
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::
+                     "l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
 }
 
-// The 8 float4 of one 16-token block that a thread stages: 4 arrays x 16 tokens x 16 float4.
-struct Prefetch {
-    float4 q[8];
-};
-__device__ __forceinline__ void fetch_block(Prefetch& p, const Args& a, size_t base, int C, int T, int step,
-                                            int n_blocks, int tid) {
-    const bool rightward = step < n_blocks;
-    const int blk = rightward ? step : step - n_blocks;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int i = tid + j * kThreads;
-        const int which = i >> 8, row = (i >> 4) & 15, c4 = (i & 15) * 4;
-        const int t_seq = blk * SC + row;
-        const int tg = rightward ? t_seq : T - 1 - t_seq;
-        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t_seq < T) {
-            const float* src = which == 0 ? a.r : which == 1 ? a.k : which == 2 ? a.v : a.w;
-            val = __ldg(reinterpret_cast<const float4*>(src + base + static_cast<size_t>(tg) * C + c4));
-        }
-        p.q[j] = val;
-    }
-}
-__device__ __forceinline__ void stage_block(Smem& s, const Prefetch& p, int tid) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int i = tid + j * kThreads;
-        const int which = i >> 8, row = (i >> 4) & 15, c4 = (i & 15) * 4;
-        *reinterpret_cast<float4*>(&s.raw[which][row][c4]) = p.q[j];
-    }
-}
-
-__global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args a) {
+__global__ void __launch_bounds__(kThreads, 4)
+wkv6_tc_forward_kernel(const Args a, const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
+                       const __grid_constant__ CUtensorMap map_y) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     Smem& s = *reinterpret_cast<Smem*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -169,13 +145,23 @@ __global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args
     const int n_blocks = (T + SC - 1) / SC;
     const int n_steps = 2 * n_blocks;
 
-    Prefetch pre;
-    fetch_block(pre, a, base, C, T, 0, n_blocks, tid);
+    // first token (memory order) of the 16-row tile that holds block `step`; negative for a ragged last leftward block
+    auto tile_start = [&](int step) { return step < n_blocks ? step * SC : T - SC * (step - n_blocks + 1); };
+    auto issue_loads = [&](int step) {
+        const int y0 = tile_start(step);
+        sm100::mbar_expect_tx(&s.bar_load, 4 * SC * N * sizeof(float));
+        sm100::tma_load_3d(&s.raw[0][0][0], &map_r, &s.bar_load, h * N, y0, b);
+        sm100::tma_load_3d(&s.raw[1][0][0], &map_k, &s.bar_load, h * N, y0, b);
+        sm100::tma_load_3d(&s.raw[2][0][0], &map_v, &s.bar_load, h * N, y0, b);
+        sm100::tma_load_3d(&s.raw[3][0][0], &map_w, &s.bar_load, h * N, y0, b);
+    };
 
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s.bar_main)) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s.bar_score)) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (tid == kIssuer) {
+        sm100::mbar_init(&s.bar_main, 1);
+        sm100::mbar_init(&s.bar_score, 1);
+        sm100::mbar_init(&s.bar_load, 1);
+        sm100::mbar_init_fence();
+        issue_loads(0);
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)),
@@ -186,52 +172,98 @@ __global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args
     // rows of the A operands that carry no data are still read by the tensor core: keep them finite
     for (int i = tid; i < 128 * 64; i += kThreads) s.opS[i] = __float2bfloat16(0.f);
     for (int i = tid; i < 128 * 16; i += kThreads) s.opV[i] = __float2bfloat16(0.f);
-    stage_block(s, pre, tid);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s.tmem_base;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's 32 TMEM lanes
 
-    uint32_t phase_main = 0, phase_score = 0;
+    uint32_t phase_main = 0, phase_score = 0, phase_load = 0;
     bool failed = false;
+    auto wait_on = [&](uint64_t* bar, uint32_t parity) {
+        if (!failed && !sm100::mbar_wait(bar, parity, kWaitLimit)) { failed = true; atomicExch(a.status, 1u); }
+    };
+
     for (int step = 0; step < n_steps; ++step) {
         const bool rightward = step < n_blocks;
         const int blk = rightward ? step : step - n_blocks;
-        if (step + 1 < n_steps) fetch_block(pre, a, base, C, T, step + 1, n_blocks, tid);   // lands during this block
+        auto row_of = [&](int t) { return rightward ? t : SC - 1 - t; };   // block order -> tile row
 
-        // ---- per key channel: cumulative log-decays and the scaled bf16 operands (two threads per channel) ----
-        bool big;
+        wait_on(&s.bar_load, phase_load);
+        phase_load ^= 1u;
+        if (tid == 0) sm100::tma_store_wait_read();        // the previous y tile has left shared memory
+
+        // ---- phase A: log-decays and their running sums; thread = (key channel, half of the block) ----
         {
             const int c = tid & 63, half = tid >> 6;
-            float ld[SC];
-            float A = 0.f, a_half = 0.f;
+            float wv[8];
 #pragma unroll
-            for (int t = 0; t < SC; ++t) {
-                ld[t] = (blk * SC + t < T) ? -__expf(s.raw[3][t][c]) : 0.f;
-                if (t == SC / 2) a_half = A;
-                A += ld[t];
-            }
-            big = A < -kMaxLogDecay;
-            const float dt = __expf(A);
-            if (half == 0) { s.dtot[c] = dt; s.acum[0][c] = 0.f; }
-            float at = half ? a_half : 0.f;
-            float kh[8], vv[8];
+            for (int j = 0; j < 8; ++j) wv[j] = s.raw[3][row_of(half * 8 + j)][c];    // all loads before the first store
+            float run = 0.f;
+            if (half == 0) s.acum[0][c] = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int t = half * 8 + j;
-                const float ldt = half ? ld[8 + j] : ld[j];
-                const float rs = s.raw[0][t][c] * __expf(at);
-                at += ldt;                                                      // a_{t+1}
-                s.acum[t + 1][c] = at;
-                const float kv = s.raw[1][t][c];
-                float kb;
-                if (!big) { kb = kv * __expf(-at); kh[j] = kb * dt; }
-                else      { kb = 0.f;              kh[j] = kv * __expf(A - at); }
-                vv[j] = s.raw[2][t][c];
-                s.opR[op_index(16, t, c)] = __float2bfloat16(rs);
-                s.opS[op_index(128, 64 + t, c)] = __float2bfloat16(kb);
+                run += (blk * SC + t < T) ? -__expf(wv[j]) : 0.f;
+                s.acum[t + 1][c] = run;
             }
+        }
+        __syncthreads();
+        // a_t[c] = acum[t][c] (+ acum[8][c] for t > 8);  A[c] = a_16[c]
+        // ---- phase B, job 1: thread = (token t, 8 key channels): Rs (twice), Kb, bonus; 16-byte stores only ----
+        {
+            const int t = tid >> 3, c0 = (tid & 7) * 8, row = row_of(t);
+            float rv[8], kv[8], at[8], at1[8], a8[8], a16[8];
+            *reinterpret_cast<float4*>(&rv[0]) = *reinterpret_cast<const float4*>(&s.raw[0][row][c0]);
+            *reinterpret_cast<float4*>(&rv[4]) = *reinterpret_cast<const float4*>(&s.raw[0][row][c0 + 4]);
+            *reinterpret_cast<float4*>(&kv[0]) = *reinterpret_cast<const float4*>(&s.raw[1][row][c0]);
+            *reinterpret_cast<float4*>(&kv[4]) = *reinterpret_cast<const float4*>(&s.raw[1][row][c0 + 4]);
+            *reinterpret_cast<float4*>(&at[0]) = *reinterpret_cast<const float4*>(&s.acum[t][c0]);
+            *reinterpret_cast<float4*>(&at[4]) = *reinterpret_cast<const float4*>(&s.acum[t][c0 + 4]);
+            *reinterpret_cast<float4*>(&at1[0]) = *reinterpret_cast<const float4*>(&s.acum[t + 1][c0]);
+            *reinterpret_cast<float4*>(&at1[4]) = *reinterpret_cast<const float4*>(&s.acum[t + 1][c0 + 4]);
+            *reinterpret_cast<float4*>(&a8[0]) = *reinterpret_cast<const float4*>(&s.acum[8][c0]);
+            *reinterpret_cast<float4*>(&a8[4]) = *reinterpret_cast<const float4*>(&s.acum[8][c0 + 4]);
+            *reinterpret_cast<float4*>(&a16[0]) = *reinterpret_cast<const float4*>(&s.acum[16][c0]);
+            *reinterpret_cast<float4*>(&a16[4]) = *reinterpret_cast<const float4*>(&s.acum[16][c0 + 4]);
+            float rs[8], kb[8], bonus = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float a_t = at[i] + (t > 8 ? a8[i] : 0.f);
+                const float a_t1 = at1[i] + (t + 1 > 8 ? a8[i] : 0.f);
+                rs[i] = rv[i] * __expf(a_t);
+                kb[i] = (a16[i] + a8[i] < -kMaxLogDecay) ? 0.f : kv[i] * __expf(-a_t1);
+                bonus += rv[i] * s.u[c0 + i] * kv[i];
+            }
+            const uint4 rs_packed = make_uint4(pack_bf16(rs[0], rs[1]), pack_bf16(rs[2], rs[3]), pack_bf16(rs[4], rs[5]),
+                                               pack_bf16(rs[6], rs[7]));
+            *reinterpret_cast<uint4*>(&s.opR[op_index(16, t, c0)]) = rs_packed;
+            *reinterpret_cast<uint4*>(&s.opS[op_index(128, 64 + t, c0)]) = rs_packed;
+            *reinterpret_cast<uint4*>(&s.opKb[op_index(16, t, c0)]) =
+                make_uint4(pack_bf16(kb[0], kb[1]), pack_bf16(kb[2], kb[3]), pack_bf16(kb[4], kb[5]), pack_bf16(kb[6], kb[7]));
+            bonus += __shfl_xor_sync(0xffffffffu, bonus, 1);
+            bonus += __shfl_xor_sync(0xffffffffu, bonus, 2);
+            bonus += __shfl_xor_sync(0xffffffffu, bonus, 4);
+            if ((tid & 7) == 0) s.diag[t] = rightward ? bonus : 0.f;
+        }
+        // ---- phase B, job 2: thread = (key channel, half of the block): Ks, V^T, e^A ----
+        bool big;
+        {
+            const int c = tid & 63, half = tid >> 6;
+            const float a8 = s.acum[8][c];
+            const float A = s.acum[16][c] + a8;
+            big = A < -kMaxLogDecay;
+            float kh[8], vv[8], a1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = half * 8 + j, row = row_of(t);
+                a1[j] = s.acum[t + 1][c];
+                kh[j] = s.raw[1][row][c];
+                vv[j] = s.raw[2][row][c];
+            }
+            if (half == 0) s.dtot[c] = __expf(A);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) kh[j] *= __expf(A - (a1[j] + (half * 8 + j + 1 > 8 ? a8 : 0.f)));
             *reinterpret_cast<uint4*>(&s.opK[op_index(64, c, half * 8)]) =
                 make_uint4(pack_bf16(kh[0], kh[1]), pack_bf16(kh[2], kh[3]), pack_bf16(kh[4], kh[5]), pack_bf16(kh[6], kh[7]));
             *reinterpret_cast<uint4*>(&s.opV[op_index(128, c, half * 8)]) =
@@ -242,15 +274,16 @@ __global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args
         const bool pairwise = __syncthreads_or(big) != 0;      // CTA-uniform
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-        // ---- scores on the tensor core: rows 64..79 of (opS . opR^T) ----
+        // ---- scores on the tensor core: rows 64..79 of (opS . opKb^T), lane 64 + t <- score[t][.] ----
         if (!pairwise && tid == kIssuer) {
 #pragma unroll
             for (int ks = 0; ks < N / 16; ++ks) {
                 const uint64_t da = make_desc(smem_u32(s.opS) + ks * 2 * (128 * 16), 128 * 16, 128);
-                const uint64_t db = make_desc(smem_u32(s.opR) + ks * 2 * (16 * 16), 16 * 16, 128);
+                const uint64_t db = make_desc(smem_u32(s.opKb) + ks * 2 * (16 * 16), 16 * 16, 128);
                 umma_bf16(tmem + 80, da, db, instr_desc(128, 16), ks > 0 ? 1u : 0u);
             }
             tc_commit(&s.bar_score);
+            if (step + 1 < n_steps) issue_loads(step + 1);     // the staging arrays were last read before the barrier
         }
         // ---- state round trip (warps 0, 1): bf16 copy for the read-out, decay in place ----
         if (tid < N) {
@@ -281,44 +314,42 @@ __global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
         if (!pairwise) {
-            // ---- warp 2 owns TMEM lanes 64..79: mask the scores, put the bonus on the diagonal ----
             if (warp == 2) {
-                float diag = 0.f;
-                if (rightward) {
-                    const int t = lane & 15, i0 = (lane >> 4) * 32;
-#pragma unroll 8
-                    for (int ii = 0; ii < 32; ++ii) {
-                        const int i = i0 + ((ii + t) & 31);                     // rotate: lanes of one half hit distinct banks
-                        diag += s.raw[0][t][i] * s.u[i] * s.raw[1][t][i];
-                    }
-                    diag += __shfl_xor_sync(0xffffffffu, diag, 16);
-                }
-                if (!failed && !bar_wait(&s.bar_score, phase_score)) { failed = true; atomicExch(a.status, 1u); }
+                // ---- warp 2 owns TMEM lanes 64..79: row t of the scores, masked to s < t, bonus on the diagonal ----
+                wait_on(&s.bar_score, phase_score);
+                phase_score ^= 1u;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 uint32_t x[16];
                 tmem_ld16_issue(lane_addr + 80, x);
                 tmem_ld_wait();
                 if (lane < 16) {
+                    float pr[16];
+                    const float dg = s.diag[lane];
 #pragma unroll
-                    for (int t = 0; t < SC; ++t) {
-                        const float val = t > lane ? __uint_as_float(x[t]) : (t == lane ? diag : 0.f);
-                        s.opP[op_index(16, t, lane)] = __float2bfloat16(val);
-                    }
+                    for (int q = 0; q < SC; ++q) pr[q] = q < lane ? __uint_as_float(x[q]) : (q == lane ? dg : 0.f);
+                    *reinterpret_cast<uint4*>(&s.opP[op_index(16, lane, 0)]) =
+                        make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
+                    *reinterpret_cast<uint4*>(&s.opP[op_index(16, lane, 8)]) =
+                        make_uint4(pack_bf16(pr[8], pr[9]), pack_bf16(pr[10], pr[11]), pack_bf16(pr[12], pr[13]), pack_bf16(pr[14], pr[15]));
                 }
             }
-            phase_score ^= 1u;
         } else {
             // ---- strong decay: the 16 x 16 scores pairwise in fp32, every exponent <= 0 ----
             for (int idx = tid; idx < SC * SC; idx += kThreads) {
                 const int t = idx >> 4, sidx = idx & 15;
+                const float* rt = s.raw[0][row_of(t)];
+                const float* ks = s.raw[1][row_of(sidx)];
                 float acc = 0.f;
                 if (sidx < t) {
+                    const bool t_hi = t > 8, s_hi = sidx + 1 > 8;     // running sums restart at token 8
 #pragma unroll 8
-                    for (int i = 0; i < N; ++i)
-                        acc += s.raw[0][t][i] * s.raw[1][sidx][i] * __expf(s.acum[t][i] - s.acum[sidx + 1][i]);
-                } else if (sidx == t && rightward) {
-#pragma unroll 8
-                    for (int i = 0; i < N; ++i) acc += s.raw[0][t][i] * s.u[i] * s.raw[1][t][i];
+                    for (int i = 0; i < N; ++i) {
+                        const float a8 = s.acum[8][i];
+                        const float e = (s.acum[t][i] + (t_hi ? a8 : 0.f)) - (s.acum[sidx + 1][i] + (s_hi ? a8 : 0.f));
+                        acc += rt[i] * ks[i] * __expf(e);
+                    }
+                } else if (sidx == t) {
+                    acc = s.diag[t];
                 }
                 s.opP[op_index(16, t, sidx)] = __float2bfloat16(acc);
             }
@@ -326,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        // ---- tensor core: read-out against the old state, in-block part, state update ----
+        // ---- tensor core: read-out against the old state, in-block part, state update; then the next block's loads ----
         if (tid == kIssuer) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -339,32 +370,46 @@ __global__ void __launch_bounds__(kThreads, 4) wkv6_tc_forward_kernel(const Args
             umma_bf16(tmem + 64, dv, make_desc(smem_u32(s.opP), 16 * 16, 128), instr_desc(128, 16), 1u);
             umma_bf16(tmem, dv, make_desc(smem_u32(s.opK), 64 * 16, 128), instr_desc(128, 64), 1u);
             tc_commit(&s.bar_main);
+            if (pairwise && step + 1 < n_steps) issue_loads(step + 1);   // the pairwise scores read the staging arrays too
         }
-        // the staging arrays are free now: park the next block
-        if (step + 1 < n_steps) stage_block(s, pre, tid);
-        // ---- warps 0, 1: wait for the tensor core (bounded), write this block's y ----
+        // ---- everyone waits for the tensor core (the operands are rewritten next); warps 0, 1 send this block's y ----
+        wait_on(&s.bar_main, phase_main);
+        phase_main ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (tid < N) {
-            if (!failed && !bar_wait(&s.bar_main, phase_main)) { failed = true; if (lane == 0) atomicExch(a.status, 1u); }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t yt[16];
             tmem_ld16_issue(lane_addr + 64, yt);
             tmem_ld_wait();
+            const int y0 = tile_start(step);
+            if (y0 >= 0) {
 #pragma unroll
-            for (int t = 0; t < SC; ++t) {
-                const int t_seq = blk * SC + t;
-                if (t_seq < T) {
-                    const int tg = rightward ? t_seq : T - 1 - t_seq;
-                    float* dst = a.y + base + static_cast<size_t>(tg) * C + tid;
-                    if (rightward) *dst = __uint_as_float(yt[t]);
-                    else atomicAdd(dst, __uint_as_float(yt[t]));      // second of exactly two addends: order-free
+                for (int t = 0; t < SC; ++t) s.ytile[row_of(t)][tid] = __uint_as_float(yt[t]);
+                sm100::fence_proxy_async_smem();
+                sm100::named_bar_sync(1, N);
+                if (tid == 0) {
+                    if (rightward) {
+                        sm100::tma_store_3d(&map_y, &s.ytile[0][0], h * N, y0, b);        // rows past T are clipped
+                    } else {
+                        if (blk == 0) sm100::tma_store_wait_all();                        // every rightward store has landed
+                        tma_reduce_add_3d(&map_y, &s.ytile[0][0], h * N, y0, b);
+                    }
+                    sm100::tma_store_commit();
+                }
+            } else {
+                // ragged last block of the leftward walk: its tile would start before token 0
+                if (tid == 0) sm100::tma_store_wait_all();
+                sm100::named_bar_sync(1, N);
+#pragma unroll
+                for (int t = 0; t < SC; ++t) {
+                    const int t_seq = blk * SC + t;
+                    if (t_seq < T) atomicAdd(a.y + base + static_cast<size_t>(T - 1 - t_seq) * C + tid, __uint_as_float(yt[t]));
                 }
             }
         }
-        phase_main ^= 1u;
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+    if (tid == 0) sm100::tma_store_wait_all();
+    __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
 }
 
@@ -377,9 +422,18 @@ int forward(int B, int T, int H, const float* r, const float* k, const float* v,
             return -1;
         configured = true;
     }
+    cudaFree(nullptr);   // descriptors are encoded against the current context; a fresh thread may not have one bound
+    const int C = H * N;
+    CUtensorMap mr, mk, mv, mw, my;
+    if (!(tensor_map::make_btc_f32(&mr, r, B, T, C, N, SC) && tensor_map::make_btc_f32(&mk, k, B, T, C, N, SC) &&
+          tensor_map::make_btc_f32(&mv, v, B, T, C, N, SC) && tensor_map::make_btc_f32(&mw, w_raw, B, T, C, N, SC) &&
+          tensor_map::make_btc_f32(&my, y, B, T, C, N, SC))) {
+        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) fp32 tensor map");
+        return -1;
+    }
     Args a{B, T, H, r, k, v, w_raw, u, y, status};
     cudaMemsetAsync(status, 0, sizeof(unsigned), stream);
-    wkv6_tc_forward_kernel<<<B * H, kThreads, sizeof(Smem), stream>>>(a);
+    wkv6_tc_forward_kernel<<<B * H, kThreads, sizeof(Smem), stream>>>(a, mr, mk, mv, mw, my);
     return 1;
 }
 

@@ -7,14 +7,34 @@ float32 `y`, gradients `(None, None, None, None, gr, gk, gv, gw, gu)` with `gw` 
 the raw `w` and `gu` of shape (H, C // H) (:69-70).  Dropped: `T_MAX = 256`, a limit of the
 reference's backward kernels only.  The reference's extension reads every tensor as float32;
 here half / bfloat16 inputs are accepted too and cast up for the kernel.
+
+Two forward kernels sit behind this surface: exact fp32 state sweeps, and a tcgen05 kernel that
+keeps the state in tensor memory and rounds its matrix operands to bfloat16 (about 1e-2 of
+max|y|, 2-3x faster).  `FORWARD_PATH` picks: "auto" (default) takes the tensor-core kernel when
+r, k and v arrive in half / bfloat16 - their own rounding is already of that size - and the exact
+sweeps for float32 callers; "exact" and "tensor_cores" force one.  The backward always
+recomputes from the saved inputs in fp32 and does not depend on the choice.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
 from . import ops
 
 HEAD_SIZE = 64
+FORWARD_PATH = os.environ.get("VRWKV6_FORWARD_PATH", "auto")
+
+
+def _use_tensor_cores(r, k, v):
+    if FORWARD_PATH == "tensor_cores":
+        return True
+    if FORWARD_PATH == "exact":
+        return False
+    if FORWARD_PATH != "auto":
+        raise ValueError(f"FORWARD_PATH must be auto, exact or tensor_cores, not {FORWARD_PATH!r}")
+    return all(x.dtype in (torch.float16, torch.bfloat16) for x in (r, k, v))
 
 
 def _f32(x):
@@ -35,7 +55,8 @@ class WKV_6(torch.autograd.Function):
             if tuple(r.shape) != (B, T, C):
                 raise RuntimeError(f"r has shape {tuple(r.shape)}, expected {(B, T, C)}")
             ctx.save_for_backward(r, k, v, w, u)
-            return ops.wkv6_forward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), H)
+            return ops.wkv6_forward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), H,
+                                    tensor_cores=_use_tensor_cores(r, k, v))
 
     @staticmethod
     def backward(ctx, gy):
