@@ -204,6 +204,16 @@ def side_measurements(dev, world, dist):
     ms = _timed(wkv6_step, dev, world, dist, iters=5)
     out["wkv6_fwd_bwd"] = {"ms": ms, "B_per_gpu": Bw, "T": T, "C": C, "H": H, "dtype": "f32",
                            "elements_per_s": Bw * T * C * world / (ms * 1e-3)}
+    del r, k6, v6, gy6, w6
+    # WKV6 forward at a dense-prediction length (T=4096): exact fp32 sweeps against the tcgen05 kernel
+    T = 4096
+    r, k6, v6 = (torch.randn(Bw, T, C, device=dev, generator=g) for _ in range(3))
+    w6 = torch.randn(Bw, T, C, device=dev, generator=g) * 0.5 - 0.6
+    ms_exact = _timed(lambda: ops.wkv6_forward(r, k6, v6, w6, u6, H), dev, world, dist, iters=5)
+    ms_tc = _timed(lambda: ops.wkv6_forward(r, k6, v6, w6, u6, H, tensor_cores=True), dev, world, dist, iters=5)
+    out["wkv6_forward_t4096"] = {"ms_exact_f32": ms_exact, "ms_tensor_cores": ms_tc, "B_per_gpu": Bw, "T": T,
+                                 "C": C, "H": H, "algorithmic_GBps_tensor_cores": 20 * Bw * T * C / (ms_tc * 1e-3) / 1e9}
+    del r, k6, v6, w6
     # fused Q-Shift + 3 interpolations, forward: 16 bytes per element
     Bq, Hh, Ww, Cq = 64, 64, 64, 768
     x = torch.randn(Bq, Hh * Ww, Cq, device=dev, generator=g)
