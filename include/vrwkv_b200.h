@@ -20,6 +20,7 @@
 #define VRWKV_B200_H_
 
 #include <stddef.h>
+#include <stdint.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -33,7 +34,9 @@ enum vrwkv_status {
     VRWKV_ERR_ALIGNMENT = 4,   /* data pointer not 4-byte / workspace not 256-byte aligned */
     VRWKV_ERR_LAUNCH = 5,      /* cudaGetLastError() reported a failure after a launch     */
     VRWKV_ERR_DEVICE = 6,      /* driver entry point or device attribute unavailable       */
-    VRWKV_ERR_HEAD_SIZE = 7    /* WKV6: C != 64 * H                                        */
+    VRWKV_ERR_HEAD_SIZE = 7,   /* WKV6: C != 64 * H                                        */
+    VRWKV_ERR_UNSUPPORTED = 8  /* bf16 entry points: shape or alignment outside what their
+                                  kernels cover; nothing ran, use the f32 entry points       */
 };
 
 /* Library version, major*10000 + minor*100 + patch. */
@@ -85,6 +88,22 @@ size_t vrwkv_biwkv_backward_workspace_bytes(int B, int T, int C);
 int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
                              const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* bfloat16 activations: k, v, y, gy, gk, gv are bfloat16 bit patterns (uint16_t), w, u and
+ * gwgu stay float, arithmetic is the f32 kernels' (inputs widened in shared memory, results
+ * rounded to nearest-even on the way out).  They replace the float casts around the extension
+ * calls in WKV.forward / WKV.backward (CLS/vrwkv.py:34-37, 51-55: `k.float().contiguous()` ...)
+ * together with the calls themselves.  Workspace sizes are those of the f32 entry points.
+ * Served by the single-pass TMA kernels only: C % 8 == 0, 16-byte aligned tensors and
+ * ceil(T / 128) below the number of resident thread blocks (about T < 37 000); anything else
+ * returns VRWKV_ERR_UNSUPPORTED before launching, and the caller casts and uses the f32 calls.
+ */
+int vrwkv_biwkv_forward_bf16(int B, int T, int C, const float* w, const float* u, const uint16_t* k,
+                             const uint16_t* v, uint16_t* y, void* workspace, size_t workspace_bytes,
+                             void* stream);
+int vrwkv_biwkv_backward_bf16(int B, int T, int C, const float* w, const float* u, const uint16_t* k,
+                              const uint16_t* v, const uint16_t* gy, float* gwgu, uint16_t* gk,
+                              uint16_t* gv, void* workspace, size_t workspace_bytes, void* stream);
 
 /* vrwkv_biwkv_forward_f32_noalloc has no counterpart in the reference.  It is
  * vrwkv_biwkv_forward_f32 for callers that cannot allocate device memory and so have no

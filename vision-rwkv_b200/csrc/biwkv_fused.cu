@@ -41,10 +41,12 @@
 // Recurrence restated: classification/mmcls_custom/models/backbones/cuda_new/
 // bi_wkv_kernel.cu:21-116 (forward), :119-367 (gradients).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdint>
 #include <initializer_list>
+#include <type_traits>
 #include "biwkv_math.cuh"
 #include "sm100_async.cuh"
 #include "tensor_map.h"
@@ -104,6 +106,41 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+
+// One thread's column of a tile in shared memory: element i = token i of the warp's sub-chunk,
+// channel = lane.  float tiles are read and written in place.  bfloat16 tiles are read as the
+// 32-bit word that holds a lane pair and written by the even lane after a shuffle, because 2-byte
+// shared accesses are slow on this part; st() must therefore be reached by all 32 lanes together.
+template <typename E>
+struct Col;
+template <>
+struct Col<float> {
+    float* p;
+    __device__ __forceinline__ Col(void* slot, int warp, int lane)
+        : p(static_cast<float*>(slot) + (warp * kL) * kCs + lane) {}
+    __device__ __forceinline__ float ld(int i) const { return p[i * kCs]; }
+    __device__ __forceinline__ void st(int i, float x) const { p[i * kCs] = x; }
+};
+template <>
+struct Col<__nv_bfloat16> {
+    uint32_t* p;
+    bool hi;
+    __device__ __forceinline__ Col(void* slot, int warp, int lane)
+        : p(static_cast<uint32_t*>(slot) + (warp * kL) * (kCs / 2) + (lane >> 1)), hi(lane & 1) {}
+    __device__ __forceinline__ float ld(int i) const {
+        const uint32_t word = p[i * (kCs / 2)];
+        return __uint_as_float(hi ? (word & 0xffff0000u) : (word << 16));
+    }
+    __device__ __forceinline__ void st(int i, float x) const {
+        const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+        if (!hi) {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(x, other);
+            p[i * (kCs / 2)] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+    }
+};
+template <typename E>
+constexpr uint32_t kSlotBytes = kTc * kCs * sizeof(E);
 
 // ---- exchange records: rec[row * kCs], rec already offset by the lane -------------------------
 __device__ __forceinline__ void post_acc4(float* rec, const Acc4& s) {
@@ -338,15 +375,15 @@ struct ExchangeCtx {
     int lane, warp, tile, chunk;
 };
 
-template <bool kBwd>
-__device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x, float* ks, float* vs,
-                                           float* gs, int n, float w, float u, float& gw_out, float& gu_out) {
+template <bool kBwd, typename E>
+__device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x, const Col<E> ks, const Col<E> vs,
+                                           const Col<E> gs, int n, float w, float u, float& gw_out, float& gu_out) {
     constexpr int kLevels = kBwd ? 2 : 1;
     const float last = static_cast<float>(n - 1);
     Acc4 right = acc4_zero();
     Acc2 left = acc2_zero();
-    for (int i = 0; i < n; ++i) acc4_absorb(right, ks[i * kCs] + w * static_cast<float>(i), vs[i * kCs], 1.f);
-    for (int i = n - 1; i >= 0; --i) acc2_add(left, ks[i * kCs] - w * static_cast<float>(i), vs[i * kCs], 1.f);
+    for (int i = 0; i < n; ++i) acc4_absorb(right, ks.ld(i) + w * static_cast<float>(i), vs.ld(i), 1.f);
+    for (int i = n - 1; i >= 0; --i) acc2_add(left, ks.ld(i) - w * static_cast<float>(i), vs.ld(i), 1.f);
     // a short sub-chunk still spans kL positions for its right-hand neighbours
     right.o -= w * static_cast<float>(n);
     acc4_decay(right, w, static_cast<float>(kL - n));
@@ -359,14 +396,14 @@ __device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x
     for (int i = n - 1; i >= 0; --i) {
         const float d = last - static_cast<float>(i);
         stash[i] = acc2_at(S, w, d);
-        acc2_add(S, ks[i * kCs] + w * d, vs[i * kCs], 1.f);
+        acc2_add(S, ks.ld(i) + w * d, vs.ld(i), 1.f);
     }
     if (!kBwd) {
         Acc2 P{P4.a, P4.b, P4.o};
         for (int i = 0; i < n; ++i) {
-            const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+            const float k = ks.ld(i), v = vs.ld(i), d = static_cast<float>(i);
             const TokenOut o = token_out(acc2_at(P, w, d), stash[i], k, v, u);
-            ks[i * kCs] = o.y;
+            ks.st(i, o.y);
             acc2_add(P, k + w * d, v, 1.f);
         }
         return;
@@ -376,10 +413,10 @@ __device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x
     float gw = 0.f, gu = 0.f;
     Acc4 PM = P4;   // prefix state with first moments
     for (int i = 0; i < n; ++i) {
-        const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+        const float k = ks.ld(i), v = vs.ld(i), d = static_cast<float>(i);
         const Acc2 Pi{PM.a, PM.b, PM.o - w * d};
         const TokenOut o = token_out(Pi, stash[i], k, v, u);
-        gg[i] = gs[i * kCs] * o.inv_den;
+        gg[i] = gs.ld(i) * o.inv_den;
         hh[i] = gg[i] * o.y;
         xo[i] = -o.m;
         gw -= wkv_exp(Pi.o + xo[i]) * (gg[i] * PM.ma - hh[i] * PM.mb);
@@ -399,18 +436,18 @@ __device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x
     float pk[kL], pv[kL];
     for (int i = n - 1; i >= 0; --i) {
         const float d = last - static_cast<float>(i);
-        const float e = wkv_exp(ks[i * kCs] + Q.o - w * d);
+        const float e = wkv_exp(ks.ld(i) + Q.o - w * d);
         pv[i] = e * Q.a;
-        pk[i] = e * (Q.a * vs[i * kCs] - Q.b);
+        pk[i] = e * (Q.a * vs.ld(i) - Q.b);
         acc2_add(Q, xo[i] + w * d, gg[i], hh[i]);
     }
     for (int i = 0; i < n; ++i) {
-        const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+        const float k = ks.ld(i), v = vs.ld(i), d = static_cast<float>(i);
         const float e = wkv_exp(k + R.o - w * d);
         const float es = wkv_exp(u + k + xo[i]);
         const float self = es * (v * gg[i] - hh[i]);
-        vs[i * kCs] = pv[i] + e * R.a + es * gg[i];
-        ks[i * kCs] = pk[i] + e * (R.a * v - R.b) + self;
+        vs.st(i, pv[i] + e * R.a + es * gg[i]);
+        ks.st(i, pk[i] + e * (R.a * v - R.b) + self);
         gu += self;
         gw -= e * (R.ma * v - R.mb);
         acc4_absorb(R, xo[i] + w * d, gg[i], hh[i]);
@@ -420,7 +457,7 @@ __device__ __noinline__ void rigorous_tile(const Params& p, const ExchangeCtx& x
 }
 
 // ---- the kernel -----------------------------------------------------------------------------
-template <bool kBwd>
+template <bool kBwd, typename E>
 __global__ void __launch_bounds__(kThreads, 2)
 biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __grid_constant__ CUtensorMap map_g,     // backward: gy
@@ -429,9 +466,13 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    const Params p) {
     constexpr int kSlots = kBwd ? 3 : 2;
     constexpr int kLevels = kBwd ? 2 : 1;
+    constexpr bool kHalf = !std::is_same<E, float>::value;
+    constexpr uint32_t kStageBytes = kSlots * kSlotBytes<E>;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    float* stage_base = reinterpret_cast<float*>(smem_raw);                         // [2][kSlots][kTc][kCs]
-    float* sub = stage_base + 2 * kSlots * kSlotFloats;                             // [kWarps][kRows][kCs]
+    unsigned char* stage_base = smem_raw;                                           // [2][kSlots][kTc][kCs] of E
+    // bfloat16 tiles: the scaled output gradients of the tile in flight stay in fp32 in a region of their own
+    float* gscratch = reinterpret_cast<float*>(stage_base + 2 * kStageBytes);       // [kTc][kCs], kBwd && kHalf only
+    float* sub = gscratch + ((kBwd && kHalf) ? kSlotFloats : 0);                    // [kWarps][kRows][kCs]
     float* ext = sub + kWarps * kRecFloats;                                         // [kWarps][kRows][kCs]
     float* red = sub;                 // [kWarps][2][kCs]: gw/gu of a tile, between two barriers at its end
     uint64_t* full = reinterpret_cast<uint64_t*>(ext + kWarps * kRecFloats);        // [2]
@@ -446,15 +487,14 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     }
     __syncthreads();
 
-    constexpr uint32_t kStageBytes = kSlots * kSlotFloats * sizeof(float);
     auto issue_loads = [&](int tile, int stage) {
         const TileCoord tc = decode_tile(p, tile);
-        float* dst = stage_base + stage * kSlots * kSlotFloats;
+        unsigned char* dst = stage_base + stage * kStageBytes;
         sm100::mbar_expect_tx(&full[stage], kStageBytes);
         sm100::tma_load_3d(dst, &map_k, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
-        sm100::tma_load_3d(dst + kSlotFloats, &map_v, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+        sm100::tma_load_3d(dst + kSlotBytes<E>, &map_v, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
         if (kBwd)
-            sm100::tma_load_3d(dst + 2 * kSlotFloats, &map_g, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+            sm100::tma_load_3d(dst + 2 * kSlotBytes<E>, &map_g, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
     };
 
     if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.n_tiles) issue_loads(blockIdx.x, 0);
@@ -463,9 +503,9 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
         const int stage = it & 1;
         const TileCoord tc = decode_tile(p, tile);
-        float* slot_k = stage_base + stage * kSlots * kSlotFloats;
-        float* slot_v = slot_k + kSlotFloats;
-        float* slot_g = slot_v + kSlotFloats;
+        unsigned char* slot_k = stage_base + stage * kStageBytes;
+        unsigned char* slot_v = slot_k + kSlotBytes<E>;
+        unsigned char* slot_g = slot_v + kSlotBytes<E>;
         const int c = tc.strip * kCs + lane;
         const float w = (c < p.C) ? p.w[c] : 0.f;
         const float u = (c < p.C) ? p.u[c] : 0.f;
@@ -478,23 +518,23 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         if (!sm100::mbar_wait(&full[stage], (it >> 1) & 1, kSpinLimit)) atomicOr(p.status, 2u);
         const int t0 = tc.chunk * kTc + warp * kL;               // first token of this sub-chunk
         const int n = max(0, min(kL, p.T - t0));
-        float* ks = slot_k + (warp * kL) * kCs + lane;
-        float* vs = slot_v + (warp * kL) * kCs + lane;
-        float* gs = slot_g + (warp * kL) * kCs + lane;
+        const Col<E> ks(slot_k, warp, lane), vs(slot_v, warp, lane), gs(slot_g, warp, lane);
+        // where the scaled output gradient is parked between the two backward levels (fp32 either way)
+        const Col<float> gpark((kBwd && kHalf) ? static_cast<void*>(gscratch) : static_cast<void*>(slot_g), warp, lane);
         float gw = 0.f, gu = 0.f;
 
         float kk[kL], vv[kL];
         float m = kMinExp, mn = 1e38f;
 #pragma unroll
         for (int i = 0; i < kL; ++i) {
-            kk[i] = ks[i * kCs];
-            vv[i] = vs[i * kCs];
+            kk[i] = ks.ld(i);
+            vv[i] = vs.ld(i);
             if (i < n) { m = wkv_max(m, kk[i]); mn = fminf(mn, kk[i]); }
         }
         const bool safe = (n == 0) || ((m - mn) + fabsf(w) * kL + fabsf(u) <= kFastRange);
         if (!__all_sync(0xffffffffu, safe)) {
             const ExchangeCtx xc{sub, ext, lane, warp, tile, tc.chunk};
-            rigorous_tile<kBwd>(p, xc, ks, vs, gs, n, w, u, gw, gu);
+            rigorous_tile<kBwd, E>(p, xc, ks, vs, gs, n, w, u, gw, gu);
         } else {
             const float lam = fast_exp(-w);
             const float2 lam2 = f2(lam, lam);
@@ -538,7 +578,7 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                     const float e = (i < n) ? fast_exp(kk[i] - M) : 0.f;
                     const float2 x = f2(e * vv[i], e);
                     const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
-                    ks[i * kCs] = __fdividef(nd.x, nd.y);
+                    ks.st(i, __fdividef(nd.x, nd.y));
                     pr = mul2(add2(pr, x), lam2);
                 }
             } else {
@@ -554,9 +594,9 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                     const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
                     const float inv = (i < n) ? __frcp_rn(nd.y) : 0.f;
                     const float y = nd.x * inv;
-                    const float g = gs[i * kCs] * inv;
+                    const float g = gs.ld(i) * inv;
                     const float h = g * y;
-                    gs[i * kCs] = g;
+                    gpark.st(i, g);
                     hh[i] = h;
                     gu += eu * (x.x * g - x.y * h);
                     gw -= g * pm.x - h * pm.y;
@@ -584,17 +624,17 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 for (int i = kL - 1; i >= 0; --i) {
                     const float e = (i < n) ? fast_exp(kk[i] + N) : 0.f;
                     part[i] = f2(e * (qq.x * vv[i] - qq.y), e * qq.x);          // (gk, gv) from later outputs
-                    qq = mul2(fma2(f2(gs[i * kCs], hh[i]), fl2, qq), lam2);
+                    qq = mul2(fma2(f2(gpark.ld(i), hh[i]), fl2, qq), lam2);
                 }
                 const float euf = eu * fl;
 #pragma unroll
                 for (int i = 0; i < kL; ++i) {
                     const float e = (i < n) ? fast_exp(kk[i] + N) : 0.f;
-                    const float g = gs[i * kCs], h = hh[i];
+                    const float g = gpark.ld(i), h = hh[i];
                     const float ev = e * vv[i];
                     const float self = euf * (ev * g - e * h);
-                    ks[i * kCs] = part[i].x + (ev * rr.x - e * rr.y) + self;
-                    vs[i * kCs] = part[i].y + e * rr.x + euf * e * g;
+                    ks.st(i, part[i].x + (ev * rr.x - e * rr.y) + self);
+                    vs.st(i, part[i].y + e * rr.x + euf * e * g);
                     gw -= ev * mrr.x - e * mrr.y;
                     rr = mul2(fma2(f2(g, h), fl2, rr), lam2);
                     mrr = fma2(mrr, lam2, rr);
@@ -635,17 +675,19 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 constexpr int kFwdStages = 3;
 
 // per-token max-shifted path, split in the same two halves (forward only)
-__device__ __noinline__ void rigorous_aggregates(const float* ks, const float* vs, int n, float w, Acc4& right,
+template <typename E>
+__device__ __noinline__ void rigorous_aggregates(const Col<E> ks, const Col<E> vs, int n, float w, Acc4& right,
                                                  Acc2& left) {
     right = acc4_zero();
     left = acc2_zero();
-    for (int i = 0; i < n; ++i) acc4_absorb(right, ks[i * kCs] + w * static_cast<float>(i), vs[i * kCs], 1.f);
-    for (int i = n - 1; i >= 0; --i) acc2_add(left, ks[i * kCs] - w * static_cast<float>(i), vs[i * kCs], 1.f);
+    for (int i = 0; i < n; ++i) acc4_absorb(right, ks.ld(i) + w * static_cast<float>(i), vs.ld(i), 1.f);
+    for (int i = n - 1; i >= 0; --i) acc2_add(left, ks.ld(i) - w * static_cast<float>(i), vs.ld(i), 1.f);
     right.o -= w * static_cast<float>(n);
     acc4_decay(right, w, static_cast<float>(kL - n));
     left.o -= w;
 }
-__device__ __noinline__ void rigorous_emit_forward(float* ks, const float* vs, int n, float w, float u,
+template <typename E>
+__device__ __noinline__ void rigorous_emit_forward(const Col<E> ks, const Col<E> vs, int n, float w, float u,
                                                    const Entering& e) {
     const float last = static_cast<float>(n - 1);
     Acc2 S = e.right;
@@ -654,23 +696,25 @@ __device__ __noinline__ void rigorous_emit_forward(float* ks, const float* vs, i
     for (int i = n - 1; i >= 0; --i) {
         const float d = last - static_cast<float>(i);
         stash[i] = acc2_at(S, w, d);
-        acc2_add(S, ks[i * kCs] + w * d, vs[i * kCs], 1.f);
+        acc2_add(S, ks.ld(i) + w * d, vs.ld(i), 1.f);
     }
     Acc2 P{e.left.a, e.left.b, e.left.o};
     for (int i = 0; i < n; ++i) {
-        const float k = ks[i * kCs], v = vs[i * kCs], d = static_cast<float>(i);
+        const float k = ks.ld(i), v = vs.ld(i), d = static_cast<float>(i);
         const TokenOut o = token_out(acc2_at(P, w, d), stash[i], k, v, u);
-        ks[i * kCs] = o.y;
+        ks.st(i, o.y);
         acc2_add(P, k + w * d, v, 1.f);
     }
 }
 
+template <typename E>
 __global__ void __launch_bounds__(kThreads, 2)
 biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                const __grid_constant__ CUtensorMap map_y, const Params p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    float* stage_base = reinterpret_cast<float*>(smem_raw);                         // [3][2][kTc][kCs]
-    float* sub = stage_base + kFwdStages * 2 * kSlotFloats;                         // [kWarps][kRows][kCs]
+    constexpr uint32_t kStageBytes = 2 * kSlotBytes<E>;
+    unsigned char* stage_base = smem_raw;                                           // [3][2][kTc][kCs] of E
+    float* sub = reinterpret_cast<float*>(stage_base + kFwdStages * kStageBytes);   // [kWarps][kRows][kCs]
     float* ext = sub + kWarps * kRecFloats;                                         // [kWarps][kRows][kCs]
     uint64_t* full = reinterpret_cast<uint64_t*>(ext + kWarps * kRecFloats);        // [3]
     const int warp = threadIdx.x >> 5;
@@ -688,10 +732,10 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
     auto issue_loads = [&](int n) {
         const int stage = n % kFwdStages;
         const TileCoord tc = decode_tile(p, first + n * G);
-        float* dst = stage_base + stage * 2 * kSlotFloats;
-        sm100::mbar_expect_tx(&full[stage], 2u * kSlotFloats * sizeof(float));
+        unsigned char* dst = stage_base + stage * kStageBytes;
+        sm100::mbar_expect_tx(&full[stage], kStageBytes);
         sm100::tma_load_3d(dst, &map_k, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
-        sm100::tma_load_3d(dst + kSlotFloats, &map_v, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
+        sm100::tma_load_3d(dst + kSlotBytes<E>, &map_v, &full[stage], tc.strip * kCs, tc.chunk * kTc, tc.b);
     };
     if (threadIdx.x == 0)
         for (int n = 0; n < kFwdStages && n < mine; ++n) issue_loads(n);
@@ -711,14 +755,14 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             const float u = (c < p.C) ? p.u[c] : 0.f;
             if (!sm100::mbar_wait(&full[stage], (n / kFwdStages) & 1, kSpinLimit)) atomicOr(p.status, 2u);
             const int nv = max(0, min(kL, p.T - (tc.chunk * kTc + warp * kL)));
-            const float* ks = stage_base + stage * 2 * kSlotFloats + (warp * kL) * kCs + lane;
-            const float* vs = ks + kSlotFloats;
+            const Col<E> ks(stage_base + stage * kStageBytes, warp, lane);
+            const Col<E> vs(stage_base + stage * kStageBytes + kSlotBytes<E>, warp, lane);
             float kk[kL], vv[kL];
             float m = kMinExp, mn = 1e38f;
 #pragma unroll
             for (int i = 0; i < kL; ++i) {
-                kk[i] = ks[i * kCs];
-                vv[i] = vs[i * kCs];
+                kk[i] = ks.ld(i);
+                vv[i] = vs.ld(i);
                 if (i < nv) { m = wkv_max(m, kk[i]); mn = fminf(mn, kk[i]); }
             }
             const bool safe = (nv == 0) || ((m - mn) + fabsf(w) * kL + fabsf(u) <= kFastRange);
@@ -759,9 +803,8 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             const float w = (c < p.C) ? p.w[c] : 0.f;
             const float u = (c < p.C) ? p.u[c] : 0.f;
             const int nv = max(0, min(kL, p.T - (tc.chunk * kTc + warp * kL)));
-            float* slot_k = stage_base + stage * 2 * kSlotFloats;
-            float* ks = slot_k + (warp * kL) * kCs + lane;
-            const float* vs = ks + kSlotFloats;
+            unsigned char* slot_k = stage_base + stage * kStageBytes;
+            const Col<E> ks(slot_k, warp, lane), vs(slot_k + kSlotBytes<E>, warp, lane);
             const Entering e1 = exchange_collect(p, ext, lane, warp, w, tile, tc.chunk, 0, 1, prev_in);
             if (!prev_safe) {
                 rigorous_emit_forward(ks, vs, nv, w, u, e1);
@@ -770,8 +813,8 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                 float m = kMinExp;
 #pragma unroll
                 for (int i = 0; i < kL; ++i) {
-                    kk[i] = ks[i * kCs];
-                    vv[i] = vs[i * kCs];
+                    kk[i] = ks.ld(i);
+                    vv[i] = vs.ld(i);
                     if (i < nv) m = wkv_max(m, kk[i]);
                 }
                 const float lam = fast_exp(-w);
@@ -795,7 +838,7 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                 for (int i = 0; i < kL; ++i) {
                     const float2 x = f2(kk[i] * vv[i], kk[i]);
                     const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
-                    ks[i * kCs] = __fdividef(nd.x, nd.y);
+                    ks.st(i, __fdividef(nd.x, nd.y));
                     pr = mul2(add2(pr, x), lam2);
                 }
             }
@@ -838,23 +881,39 @@ reduce_tile_partials(Params p, float* __restrict__ out) {
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-static bool make_map(CUtensorMap* map, const float* base, int B, int T, int C) {
-    return tensor_map::make_btc_f32(map, base, B, T, C, kCs, kTc);
+template <typename E>
+static bool make_map(CUtensorMap* map, const void* base, int B, int T, int C) {
+    return tensor_map::make_btc(map, base, B, T, C, kCs, kTc, !std::is_same<E, float>::value);
 }
 
+template <typename E>
 static constexpr size_t fwd_pipelined_smem_bytes() {
-    return (kFwdStages * 2 * kSlotFloats + 2 * kWarps * kRecFloats) * sizeof(float) + 64;
+    return kFwdStages * 2 * kSlotBytes<E> + 2 * kWarps * kRecFloats * sizeof(float) + 64;
+}
+
+template <bool kBwd, typename E>
+static constexpr size_t smem_bytes() {
+    return 2 * (kBwd ? 3 : 2) * kSlotBytes<E> + ((kBwd && !std::is_same<E, float>::value) ? kSlotFloats * sizeof(float) : 0) +
+           2 * kWarps * kRecFloats * sizeof(float) + 64;
 }
 
 struct DeviceInfo {
     int sms = 0;
-    int resident[2] = {0, 0};   // CTAs per SM, forward / backward
+    int resident[2][2] = {{0, 0}, {0, 0}};   // CTAs per SM: [float | bfloat16 tiles][forward | backward]
     bool ok = false;
 };
 
-template <bool kBwd>
-static constexpr size_t smem_bytes() {
-    return (2 * (kBwd ? 3 : 2) * kSlotFloats + 2 * kWarps * kRecFloats) * sizeof(float) + 64;
+template <typename E>
+static bool configure_kernels(int (&resident)[2]) {
+    bool good = cudaFuncSetAttribute(biwkv_fused_kernel<true, E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem_bytes<true, E>())) == cudaSuccess;
+    good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(fwd_pipelined_smem_bytes<E>())) == cudaSuccess;
+    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident[0], biwkv_forward_pipelined_kernel<E>,
+                                                                 kThreads, fwd_pipelined_smem_bytes<E>()) == cudaSuccess;
+    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident[1], biwkv_fused_kernel<true, E>, kThreads,
+                                                                 smem_bytes<true, E>()) == cudaSuccess;
+    return good && resident[0] > 0 && resident[1] > 0;
 }
 
 static const DeviceInfo& device_info() {
@@ -865,17 +924,10 @@ static const DeviceInfo& device_info() {
     if (d.ok) return d;
     cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
     bool good = tensor_map::encode_fn() != nullptr;
-    good = good && cudaFuncSetAttribute(biwkv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(smem_bytes<true>())) == cudaSuccess;
-    good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(fwd_pipelined_smem_bytes())) == cudaSuccess;
-    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[0], biwkv_forward_pipelined_kernel,
-                                                                 kThreads, fwd_pipelined_smem_bytes()) == cudaSuccess;
-    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&d.resident[1], biwkv_fused_kernel<true>,
-                                                                 kThreads, smem_bytes<true>()) == cudaSuccess;
+    good = good && configure_kernels<float>(d.resident[0]) && configure_kernels<__nv_bfloat16>(d.resident[1]);
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
-    d.ok = good && coop && d.sms > 0 && d.resident[0] > 0 && d.resident[1] > 0;
+    d.ok = good && coop && d.sms > 0;
     if (!d.ok) cudaGetLastError();
     return d;
 }
@@ -909,8 +961,8 @@ static Layout make_layout(int B, int T, int C, bool bwd) {
     return l;
 }
 
-bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs) {
-    if (C % 4 != 0) return false;                                  // TMA row pitch must be 16-byte
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bf16) {
+    if (C % (bf16 ? 8 : 4) != 0) return false;                     // TMA row pitch must be 16-byte
     for (const void* q : ptrs)
         if (reinterpret_cast<uintptr_t>(q) & 15u) return false;    // TMA base alignment
     const DeviceInfo& d = device_info();
@@ -919,15 +971,16 @@ bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs) {
     if (tiles > (1LL << 30)) return false;
     // every peer of a tile must be reachable inside one sweep of the resident grid
     const int n_chunks = (T + kTc - 1) / kTc;
-    const int grid = d.sms * std::min(d.resident[0], d.resident[1]);
+    const int (&res)[2] = d.resident[bf16 ? 1 : 0];
+    const int grid = d.sms * std::min(res[0], res[1]);
     return static_cast<long long>(n_chunks) * pick_interleave((C + kCs - 1) / kCs) < grid;
 }
 
 size_t workspace_bytes(int B, int T, int C, bool bwd) { return make_layout(B, T, C, bwd).total; }
 
-template <bool kBwd>
-static int launch(Layout& l, const float* w, const float* u, const float* k, const float* v, const float* gy,
-                  float* o0, float* o1, float* gwgu, void* workspace, cudaStream_t stream) {
+template <bool kBwd, typename E>
+static int launch(Layout& l, const float* w, const float* u, const E* k, const E* v, const E* gy, E* o0, E* o1,
+                  float* gwgu, void* workspace, cudaStream_t stream) {
     Params& p = l.p;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     p.w = w; p.u = u;
@@ -937,24 +990,24 @@ static int launch(Layout& l, const float* w, const float* u, const float* k, con
     p.partial = reinterpret_cast<float*>(ws + l.off_partial);
     cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
     CUtensorMap mk, mv, mg, m0, m1;
-    bool ok = make_map(&mk, k, p.B, p.T, p.C) && make_map(&mv, v, p.B, p.T, p.C) &&
-              make_map(&m0, o0, p.B, p.T, p.C);
-    ok = ok && make_map(&mg, kBwd ? gy : k, p.B, p.T, p.C) && make_map(&m1, kBwd ? o1 : o0, p.B, p.T, p.C);
+    bool ok = make_map<E>(&mk, k, p.B, p.T, p.C) && make_map<E>(&mv, v, p.B, p.T, p.C) &&
+              make_map<E>(&m0, o0, p.B, p.T, p.C);
+    ok = ok && make_map<E>(&mg, kBwd ? gy : k, p.B, p.T, p.C) && make_map<E>(&m1, kBwd ? o1 : o0, p.B, p.T, p.C);
     if (!ok) {
-        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) fp32 tensor map");
+        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
         return -1;
     }
     // status word + flags start at zero
     cudaMemsetAsync(ws, 0, l.off_exch, stream);
     const DeviceInfo& d = device_info();
-    const int grid = std::min(p.n_tiles, d.sms * d.resident[kBwd ? 1 : 0]);
+    const int grid = std::min(p.n_tiles, d.sms * d.resident[std::is_same<E, float>::value ? 0 : 1][kBwd ? 1 : 0]);
     void* args[] = {&mk, &mv, &mg, &m0, &m1, &p};
     void* fwd_args[] = {&mk, &mv, &m0, &p};
     const cudaError_t err =
-        kBwd ? cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_fused_kernel<true>), dim3(grid),
-                                           dim3(kThreads), args, smem_bytes<true>(), stream)
-             : cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_forward_pipelined_kernel), dim3(grid),
-                                           dim3(kThreads), fwd_args, fwd_pipelined_smem_bytes(), stream);
+        kBwd ? cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_fused_kernel<true, E>), dim3(grid),
+                                           dim3(kThreads), args, smem_bytes<true, E>(), stream)
+             : cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_forward_pipelined_kernel<E>), dim3(grid),
+                                           dim3(kThreads), fwd_args, fwd_pipelined_smem_bytes<E>(), stream);
     if (err != cudaSuccess) {
         set_error_detail(cudaGetErrorName(err));
         return -1;
@@ -970,13 +1023,29 @@ static int launch(Layout& l, const float* w, const float* u, const float* k, con
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
             void* workspace, cudaStream_t stream) {
     Layout l = make_layout(B, T, C, false);
-    return launch<false>(l, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
+    return launch<false, float>(l, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
 }
 
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
              const float* gy, float* gwgu, float* gk, float* gv, void* workspace, cudaStream_t stream) {
     Layout l = make_layout(B, T, C, true);
-    return launch<true>(l, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+    return launch<true, float>(l, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+}
+
+int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
+                 void* workspace, cudaStream_t stream) {
+    using E = __nv_bfloat16;
+    Layout l = make_layout(B, T, C, false);
+    return launch<false, E>(l, w, u, static_cast<const E*>(k), static_cast<const E*>(v), nullptr, static_cast<E*>(y),
+                            nullptr, nullptr, workspace, stream);
+}
+
+int backward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, const void* gy,
+                  float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream) {
+    using E = __nv_bfloat16;
+    Layout l = make_layout(B, T, C, true);
+    return launch<true, E>(l, w, u, static_cast<const E*>(k), static_cast<const E*>(v), static_cast<const E*>(gy),
+                           static_cast<E*>(gk), static_cast<E*>(gv), gwgu, workspace, stream);
 }
 
 }  // namespace fused

@@ -25,17 +25,22 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // Box of box_c channels x box_t tokens of one batch entry; out-of-range elements load as zero and
-// are clipped on store.  `base` must be 16-byte aligned and C a multiple of 4.
-inline bool make_btc_f32(CUtensorMap* map, const float* base, int B, int T, int C, int box_c, int box_t) {
+// are clipped on store.  `base` must be 16-byte aligned and the row pitch C * elem_bytes a multiple
+// of 16 (C % 4 == 0 for float, C % 8 == 0 for bfloat16).
+inline bool make_btc(CUtensorMap* map, const void* base, int B, int T, int C, int box_c, int box_t, bool bf16) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
+    const cuuint64_t eb = bf16 ? 2 : 4;
     const cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * 4, static_cast<cuuint64_t>(T) * C * 4};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(C) * eb, static_cast<cuuint64_t>(T) * C * eb};
     const cuuint32_t box[3] = {static_cast<cuuint32_t>(box_c), static_cast<cuuint32_t>(box_t), 1};
     const cuuint32_t estr[3] = {1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base),
+              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+inline bool make_btc_f32(CUtensorMap* map, const float* base, int B, int T, int C, int box_c, int box_t) {
+    return make_btc(map, base, B, T, C, box_c, box_t, false);
 }
 
 }  // namespace tensor_map

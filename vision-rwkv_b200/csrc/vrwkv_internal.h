@@ -20,13 +20,18 @@ int generic_backward(int B, int T, int C, const float* w, const float* u, const 
                      void* workspace, cudaStream_t stream);
 namespace fused {
 // True when the fused TMA path can serve this call on the current device.
-bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs);
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bf16 = false);
 size_t workspace_bytes(int B, int T, int C, bool bwd);
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
             float* y, void* workspace, cudaStream_t stream);
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
              const float* gy, float* gwgu, float* gk, float* gv, void* workspace,
              cudaStream_t stream);
+// k, v, y, gy, gk, gv hold bfloat16; w, u, gwgu stay float; arithmetic is the float kernels'.
+int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
+                 void* workspace, cudaStream_t stream);
+int backward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v,
+                  const void* gy, float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream);
 }  // namespace fused
 }  // namespace biwkv
 

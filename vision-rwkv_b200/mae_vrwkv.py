@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from . import ops
+from .vrwkv import biwkv_backward_as_reference, biwkv_forward_as_reference
 
 
 class WKV(torch.autograd.Function):
@@ -20,30 +20,13 @@ class WKV(torch.autograd.Function):
         if tuple(k.shape) != (B, T, C):
             raise RuntimeError(f"k has shape {tuple(k.shape)}, expected {(B, T, C)}")
         ctx.B, ctx.T, ctx.C = B, T, C
-        half_mode = (w.dtype == torch.half)
-        bf_mode = (w.dtype == torch.bfloat16)
         ctx.save_for_backward(w, u, k, v)
-        y = ops.biwkv_forward(w.float().contiguous(), u.float().contiguous(),
-                              k.float().contiguous(), v.float().contiguous())
-        if half_mode:
-            y = y.half()
-        elif bf_mode:
-            y = y.bfloat16()
-        return y
+        return biwkv_forward_as_reference(w, u, k, v)
 
     @staticmethod
     def backward(ctx, gy):
         w, u, k, v = ctx.saved_tensors
-        half_mode = (w.dtype == torch.half)
-        bf_mode = (w.dtype == torch.bfloat16)
-        gw, gu, gk, gv = ops.biwkv_backward(w.float().contiguous(), u.float().contiguous(),
-                                            k.float().contiguous(), v.float().contiguous(),
-                                            gy.float().contiguous())
-        if half_mode:
-            return (None, None, None, gw.half(), gu.half(), gk.half(), gv.half())
-        elif bf_mode:
-            return (None, None, None, gw.bfloat16(), gu.bfloat16(), gk.bfloat16(), gv.bfloat16())
-        return (None, None, None, gw, gu, gk, gv)
+        return (None, None, None) + tuple(biwkv_backward_as_reference(w, u, k, v, gy))
 
 
 def RUN_CUDA(B, T, C, w, u, k, v):

@@ -30,8 +30,10 @@ def _check_status(lib, ws, what):
         raise _lib.VrwkvError(f"{what}: device status word {word.value:#x} (a bounded wait ran out)")
 
 
-def _check_inputs(named):
-    dev = None
+UNSUPPORTED = 8      # VRWKV_ERR_UNSUPPORTED: the bf16 kernels do not cover this shape / alignment
+
+
+def _check_inputs(named, dtype=torch.float32, dev=None):
     for name, t in named:
         if not isinstance(t, torch.Tensor):
             raise TypeError(f"{name} must be a torch.Tensor")
@@ -39,8 +41,8 @@ def _check_inputs(named):
             raise RuntimeError(f"{name} must be a CUDA tensor")          # CHECK_CUDA
         if not t.is_contiguous():
             raise RuntimeError(f"{name} must be contiguous")             # CHECK_CONTIGUOUS
-        if t.dtype != torch.float32:
-            raise RuntimeError(f"{name} must be float32, got {t.dtype}")
+        if t.dtype != dtype:
+            raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
         if dev is None:
             dev = t.device
         elif t.device != dev:
@@ -63,13 +65,31 @@ def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
 
 
+def _is_bf16(t):
+    return isinstance(t, torch.Tensor) and t.dtype == torch.bfloat16
+
+
 def biwkv_forward(w, u, k, v):
-    """y = Bi-WKV(w, u, k, v); all float32 CUDA, k and v (B, T, C), w and u (C,)."""
-    dev = _check_inputs((("w", w), ("u", u), ("k", k), ("v", v)))
+    """y = Bi-WKV(w, u, k, v); CUDA tensors, k and v (B, T, C), w and u (C,) float32.
+    k and v are float32 (y float32) or both bfloat16 (y bfloat16, float32 arithmetic inside)."""
+    half = _is_bf16(k)
+    dev = _check_inputs((("w", w), ("u", u)))
+    _check_inputs((("k", k), ("v", v)), torch.bfloat16 if half else torch.float32, dev)
     B, T, C = _biwkv_shapes(w, u, k, v)
     lib = _lib.load()
     y = torch.empty_like(k)
     if k.numel() == 0:
+        return y
+    if half:
+        with torch.cuda.device(dev):
+            ws = _workspace(lib.vrwkv_biwkv_forward_workspace_bytes(B, T, C), dev)
+            st = lib.vrwkv_biwkv_forward_bf16(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                              y.data_ptr(), ws.data_ptr(), ws.numel(),
+                                              torch.cuda.current_stream().cuda_stream)
+            if st == UNSUPPORTED:        # odd channel count, unaligned view, ...: widen and use the f32 kernels
+                return biwkv_forward(w, u, k.float(), v.float()).bfloat16()
+            _lib.check(st, "vrwkv_biwkv_forward_bf16")
+            _check_status(lib, ws, "vrwkv_biwkv_forward_bf16")
         return y
     with torch.cuda.device(dev):
         nbytes = lib.vrwkv_biwkv_forward_workspace_bytes(B, T, C)
@@ -87,7 +107,9 @@ def biwkv_backward(w, u, k, v, gy, gwgu_out=None):
     """(gw, gu, gk, gv).  gw and gu are views of one (2, C) buffer, so a data-parallel
     caller can all-reduce both with a single collective; pass `gwgu_out` to have them
     written into a buffer of its own (for instance one registered with NCCL)."""
-    dev = _check_inputs((("w", w), ("u", u), ("k", k), ("v", v), ("gy", gy)))
+    half = _is_bf16(k)
+    dev = _check_inputs((("w", w), ("u", u)))
+    _check_inputs((("k", k), ("v", v), ("gy", gy)), torch.bfloat16 if half else torch.float32, dev)
     B, T, C = _biwkv_shapes(w, u, k, v, gy)
     lib = _lib.load()
     gk = torch.empty_like(k)
@@ -101,6 +123,18 @@ def biwkv_backward(w, u, k, v, gy, gwgu_out=None):
         gwgu = gwgu_out.view(2, C)
     if k.numel() == 0:
         gwgu.zero_()
+        return gwgu[0], gwgu[1], gk, gv
+    if half:
+        with torch.cuda.device(dev):
+            ws = _workspace(lib.vrwkv_biwkv_backward_workspace_bytes(B, T, C), dev)
+            st = lib.vrwkv_biwkv_backward_bf16(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                               gy.data_ptr(), gwgu.data_ptr(), gk.data_ptr(), gv.data_ptr(),
+                                               ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+            if st == UNSUPPORTED:
+                gw, gu, gk32, gv32 = biwkv_backward(w, u, k.float(), v.float(), gy.float(), gwgu_out=gwgu)
+                return gw, gu, gk32.bfloat16(), gv32.bfloat16()
+            _lib.check(st, "vrwkv_biwkv_backward_bf16")
+            _check_status(lib, ws, "vrwkv_biwkv_backward_bf16")
         return gwgu[0], gwgu[1], gk, gv
     with torch.cuda.device(dev):
         nbytes = lib.vrwkv_biwkv_backward_workspace_bytes(B, T, C)

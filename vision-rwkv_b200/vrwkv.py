@@ -14,41 +14,70 @@ What differs is underneath: no T_MAX, no C >= 32 or B*C % 32 requirement, a
 deterministic gw/gu reduction, and the recurrence evaluated without the reference
 kernel's in-segment decay deviation (its outputs differ from the recurrence by about
 1e-3 for T > 32).
+
+bfloat16 activations (`BF16_IO`, on by default; `VRWKV_BF16_IO=0` in the environment turns it
+off): when k and v arrive in bfloat16 - the usual case under autocast - the kernels read them and
+write y / gk / gv as bfloat16 directly with float32 arithmetic inside, instead of the reference's
+widen-compute-narrow passes (:34-37, :51-55).  The values are the same wherever the reference
+would itself return bfloat16 (`w` in bfloat16).  With a float32 `w` the reference returns a
+float32 y computed from the bfloat16 inputs; here that y has passed through bfloat16 once
+(relative difference up to 2^-9), and gy is rounded to bfloat16 on its way in.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
 from . import ops
 
+BF16_IO = os.environ.get("VRWKV_BF16_IO", "1") != "0"
+
+
+def _result_dtype(w):
+    return w.dtype if w.dtype in (torch.half, torch.bfloat16) else torch.float32
+
+
+def _bf16_path(k, v):
+    return BF16_IO and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+
+
+def biwkv_forward_as_reference(w, u, k, v):
+    """The body of WKV.forward: dtype handling of CLS/vrwkv.py:32-44 around the kernel call."""
+    w32, u32 = w.float().contiguous(), u.float().contiguous()
+    if _bf16_path(k, v):
+        y = ops.biwkv_forward(w32, u32, k.contiguous(), v.contiguous())
+    else:
+        y = ops.biwkv_forward(w32, u32, k.float().contiguous(), v.float().contiguous())
+    return y.to(_result_dtype(w))
+
+
+def biwkv_backward_as_reference(w, u, k, v, gy):
+    """The body of WKV.backward (CLS/vrwkv.py:47-61): (gw, gu, gk, gv) in the reference's dtypes."""
+    w32, u32 = w.float().contiguous(), u.float().contiguous()
+    out = _result_dtype(w)
+    if _bf16_path(k, v):
+        gw, gu, gk, gv = ops.biwkv_backward(w32, u32, k.contiguous(), v.contiguous(), gy.bfloat16().contiguous())
+        if out == torch.half:
+            gk, gv = gk.half(), gv.half()
+        # otherwise gk, gv stay bfloat16: the dtype autograd hands to a bfloat16 k anyway
+    else:
+        gw, gu, gk, gv = ops.biwkv_backward(w32, u32, k.float().contiguous(), v.float().contiguous(),
+                                            gy.float().contiguous())
+        gk, gv = gk.to(out), gv.to(out)
+    return gw.to(out), gu.to(out), gk, gv
+
 
 class WKV(torch.autograd.Function):
     @staticmethod
     def forward(ctx, w, u, k, v):
-        half_mode = (w.dtype == torch.half)
-        bf_mode = (w.dtype == torch.bfloat16)
         ctx.save_for_backward(w, u, k, v)
-        y = ops.biwkv_forward(w.float().contiguous(), u.float().contiguous(),
-                              k.float().contiguous(), v.float().contiguous())
-        if half_mode:
-            y = y.half()
-        elif bf_mode:
-            y = y.bfloat16()
-        return y
+        return biwkv_forward_as_reference(w, u, k, v)
 
     @staticmethod
     def backward(ctx, gy):
         w, u, k, v = ctx.saved_tensors
-        half_mode = (w.dtype == torch.half)
-        bf_mode = (w.dtype == torch.bfloat16)
-        gw, gu, gk, gv = ops.biwkv_backward(w.float().contiguous(), u.float().contiguous(),
-                                            k.float().contiguous(), v.float().contiguous(),
-                                            gy.float().contiguous())
-        if half_mode:
-            return (gw.half(), gu.half(), gk.half(), gv.half())
-        elif bf_mode:
-            return (gw.bfloat16(), gu.bfloat16(), gk.bfloat16(), gv.bfloat16())
-        return (gw, gu, gk, gv)
+        return biwkv_backward_as_reference(w, u, k, v, gy)
 
 
 def RUN_CUDA(w, u, k, v, decay_offset: int = 0):
