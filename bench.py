@@ -189,6 +189,22 @@ def side_measurements(dev, world, dist):
                                 "batch_per_gpu": B, "resolution": 224, "n_gpus": world,
                                 "gemm_dtype": "bf16 autocast", "wkv_dtype": "f32"}
     del model, img
+    # Bi-WKV with bfloat16 activations at the headline shape: 6 + 10 = 16 bytes per element fwd+bwd
+    Bh, Th, Ch = WORKLOAD["B"], WORKLOAD["T"], WORKLOAD["C"]
+    gh = torch.Generator(device=dev).manual_seed(11)
+    kh, vh, gyh = (torch.randn(Bh, Th, Ch, device=dev, generator=gh).bfloat16() for _ in range(3))
+    wh = (torch.rand(Ch, device=dev, generator=gh) * 2 - 1) / Th
+    uh = (torch.rand(Ch, device=dev, generator=gh) * 2 - 1) / Th
+
+    def biwkv_bf16_step():
+        ops.biwkv_forward(wh, uh, kh, vh)
+        ops.biwkv_backward(wh, uh, kh, vh, gyh)
+
+    ms = _timed(biwkv_bf16_step, dev, world, dist, iters=5)
+    out["biwkv_bf16_fwd_bwd"] = {"ms": ms, "B_per_gpu": Bh, "T": Th, "C": Ch,
+                                 "algorithmic_GBps": 16 * Bh * Th * Ch * world / (ms * 1e-3) / 1e9,
+                                 "elements_per_s": Bh * Th * Ch * world / (ms * 1e-3)}
+    del kh, vh, gyh
     # WKV6 operator as in VRWKV6-B: C=768, 12 heads, B=32 per GPU, T=196, fwd+bwd (exact fp32 sweeps)
     Bw, T, H = 32, 196, 12
     C = 64 * H
@@ -234,6 +250,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-chunk", type=int, default=4, help="sequences per pipelined chunk of the host-buffer call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"], help="sequences per GPU")
     ap.add_argument("--tokens", type=int, default=WORKLOAD["T"])
@@ -342,22 +359,12 @@ def main():
         out_y, out_gk, out_gv = (torch.empty(B, T, C, pin_memory=True) for _ in range(3))
         out_gwgu = torch.empty(2, C, pin_memory=True)
 
+        from vision_rwkv_b200.host import biwkv_forward_backward_host
+
         def e2e_step():
-            dw = hw.to(dev, non_blocking=True).requires_grad_(True)
-            du = hu.to(dev, non_blocking=True).requires_grad_(True)
-            dk = hk.to(dev, non_blocking=True).requires_grad_(True)
-            dv = hv.to(dev, non_blocking=True).requires_grad_(True)
-            dgy = hgy.to(dev, non_blocking=True)
-            y = RUN_CUDA(dw, du, dk, dv)
-            y.backward(dgy)
-            grads = torch.stack([dw.grad, du.grad])
-            if world > 1:
-                reducer.launch(grads)
-                reducer.wait()
-            out_y.copy_(y.detach(), non_blocking=True)
-            out_gk.copy_(dk.grad, non_blocking=True)
-            out_gv.copy_(dv.grad, non_blocking=True)
-            out_gwgu.copy_(grads, non_blocking=True)
+            # host tensors in, host tensors out: batch chunks pipelined over three streams (copy in | kernels | copy out)
+            biwkv_forward_backward_host(hw, hu, hk, hv, hgy, out_y, out_gk, out_gv, out_gwgu, device=dev,
+                                        chunk=args.e2e_chunk, reducer=reducer if world > 1 else None)
 
         e2e_step()
         sync_all()
@@ -375,6 +382,7 @@ def main():
         e_ms /= args.e2e_steps
         e2e = {"value": (BYTES_FWD + BYTES_BWD) * E * world / (e_ms * 1e-3) / 1e9, "unit": UNIT,
                "ms_per_step": e_ms, "steps": args.e2e_steps,
+               "api": "vision_rwkv_b200.host.biwkv_forward_backward_host (pinned host buffers in and out)",
                "h2d_bytes_per_step": (3 * E + 2 * C) * 4 * world,
                "d2h_bytes_per_step": (3 * E + 2 * C) * 4 * world}
         del hk, hv, hgy, out_y, out_gk, out_gv
