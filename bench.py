@@ -271,10 +271,12 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # stdout carries exactly one JSON line: whatever a library writes to file descriptor 1 from here on
+    # (NCCL prints its version banner there) is sent to stderr, and the line goes to the saved descriptor
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        # keep stdout to the one JSON line: no NCCL version banner
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
 
     import __graft_entry__
@@ -423,7 +425,7 @@ def main():
                "cores": threads, "kind": "port", "seconds": sec,
                "sample": f"B={sB} of {B} sequences, T={T}, C={C}, fp32 PyTorch scans, fwd+bwd"}
 
-    print(json.dumps({
+    line = json.dumps({
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -433,7 +435,9 @@ def main():
                    "l2": "inputs (2.4 GB per pass) exceed the 126 MB L2; no explicit flush"},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
         "clocks": clocks, "secondary": secondary,
-    }))
+    })
+    sys.stdout.flush()
+    os.write(json_fd, (line + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
