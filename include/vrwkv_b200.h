@@ -49,8 +49,10 @@ const char* vrwkv_last_error_detail(void);
 /* Number of kernels this library has launched in the calling process so far. */
 unsigned long long vrwkv_launch_count(void);
 
-/* Kernel path selection, for tests and measurements: 0 = automatic (default), 1 = always
- * the generic multi-launch path, 2 = same as 0.  Process-wide.  No reference counterpart. */
+/* Kernel path selection, for tests and measurements: 0 = automatic (default), 1 = the
+ * first-generation kernels (Bi-WKV: the generic multi-launch path; WKV6 tensor-core forward:
+ * the serial-phase kernel instead of the warp-specialised one), 2 = same as 0.  Process-wide.
+ * No reference counterpart. */
 int vrwkv_set_path(int path);
 /* Copies the device status word kept in the first 4 bytes of a workspace to *status_out
  * after synchronising `stream`.  0 means no bounded device-side wait ran out; bit 0 = a

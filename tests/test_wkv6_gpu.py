@@ -137,6 +137,19 @@ def test_bf16_inputs(cuda_device):
 TC_TOL = 1e-2
 
 
+@pytest.fixture(params=["pipelined", "serial"])
+def tc_kernel(request):
+    """The tensor-core tests run on both kernels: the warp-specialised one (default) and the
+    first-generation one in which all warps do every phase in turn."""
+    from vision_rwkv_b200 import _lib, ops
+    lib = _lib.load()
+    ops.CHECK_STATUS = True
+    assert lib.vrwkv_set_path(1 if request.param == "serial" else 0) == 0
+    yield request.param
+    lib.vrwkv_set_path(0)
+    ops.CHECK_STATUS = False
+
+
 def run_tc(dev, r, k, v, w, u, H):
     from vision_rwkv_b200 import ops
     f = [x.float().contiguous().to(dev) for x in (r, k, v, w, u)]
@@ -147,7 +160,7 @@ def run_tc(dev, r, k, v, w, u, H):
 
 @pytest.mark.parametrize("B,T,H", [(1, 1, 1), (2, 2, 1), (1, 3, 2), (2, 15, 1), (1, 16, 3), (1, 17, 2), (1, 31, 1),
                                    (2, 37, 2), (1, 64, 1), (1, 70, 1), (3, 196, 2), (1, 300, 1), (1, 1024, 1)])
-def test_tensor_core_forward_parity(cuda_device, B, T, H):
+def test_tensor_core_forward_parity(cuda_device, B, T, H, tc_kernel):
     r, k, v, w, u, _ = O.make_inputs(B, T, 64 * H, H, seed=T, round_to=torch.bfloat16)
     y = run_tc(cuda_device, r, k, v, w, u, H)
     ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
@@ -156,7 +169,7 @@ def test_tensor_core_forward_parity(cuda_device, B, T, H):
 
 
 @pytest.mark.parametrize("shift", [1.0, 1.7, 2.6, 4.0])
-def test_tensor_core_forward_strong_decay(cuda_device, shift):
+def test_tensor_core_forward_strong_decay(cuda_device, shift, tc_kernel):
     """A block whose accumulated log-decay passes 80 in some channel scores pairwise on the CUDA cores; the
     shifts cover none / some / all blocks taking that path, and one head only."""
     B, T, H = 2, 100, 2
@@ -171,7 +184,7 @@ def test_tensor_core_forward_strong_decay(cuda_device, shift):
     assert rel_err(y[..., 64:], ref[..., 64:]) <= TC_TOL
 
 
-def test_tensor_core_forward_matches_exact_sweeps_at_scale(cuda_device):
+def test_tensor_core_forward_matches_exact_sweeps_at_scale(cuda_device, tc_kernel):
     """Full-size check without the oracle: both kernels on the same inputs, T = 4096."""
     from vision_rwkv_b200 import ops
     B, T, H = 2, 4096, 3
@@ -185,7 +198,7 @@ def test_tensor_core_forward_matches_exact_sweeps_at_scale(cuda_device):
     assert rel_err(y_tc, y_ex.double().cpu()) <= TC_TOL
 
 
-def test_tensor_core_forward_reproducible_and_independent(cuda_device):
+def test_tensor_core_forward_reproducible_and_independent(cuda_device, tc_kernel):
     r, k, v, w, u, _ = O.make_inputs(2, 90, 128, 2, seed=5, round_to=torch.bfloat16)
     a = run_tc(cuda_device, r, k, v, w, u, 2)
     b = run_tc(cuda_device, r, k, v, w, u, 2)

@@ -183,7 +183,7 @@ int vrwkv_wkv6_forward_tc_f32(int B, int T, int C, int H, const float* r, const 
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < 256) return VRWKV_ERR_WORKSPACE;
     return finish(wkv6tc::forward(B, T, H, r, k, v, w_raw, u, y, static_cast<unsigned*>(workspace),
-                                  static_cast<cudaStream_t>(stream)));
+                                  g_path.load() != 1, static_cast<cudaStream_t>(stream)));
 }
 
 int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,

@@ -46,6 +46,7 @@ int backward(int B, int T, int H, const float* r, const float* k, const float* v
 
 namespace wkv6tc {
 // Tensor-core forward (bf16 operands, fp32 state).  `status` points at 4 writable device bytes.
+// pipelined = false runs the first-generation kernel (all warps do every phase in turn).
 int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw,
-            const float* u, float* y, unsigned* status, cudaStream_t stream);
+            const float* u, float* y, unsigned* status, bool pipelined, cudaStream_t stream);
 }  // namespace wkv6tc

@@ -413,12 +413,408 @@ wkv6_tc_forward_kernel(const Args a, const __grid_constant__ CUtensorMap map_r, 
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
 }
 
+// ---- the pipelined kernel ---------------------------------------------------------------------------
+// Same arithmetic, different schedule.  The serial kernel above does every phase of a block with all
+// of its warps, one phase after the other; what must be serial, though, is only
+//     state round trip (block n)  ->  read-out / update products (block n)  ->  round trip (n + 1).
+// Here one CTA walks one direction of one (batch, head) with nine warps in three roles:
+//   producers (warps 3, 6..12): operands of block n+1 (log-decay sums, scalings, bf16 rounding, the
+//       pairwise scores of a strongly decaying block) into the other of two operand sets, and the
+//       TMA loads of block n+2;
+//   loader (warp 13): the TMA loads of block n+2 as soon as the producers have read block n (issuing
+//       the four copies costs several hundred cycles, too many for a thread the others wait for);
+//   control (warp 2, owner of TMEM lanes 64..95): issues all tensor-core work; between the score
+//       product and the main products it masks the 16 x 16 scores into the P operand;
+//   state (warps 0, 1, 4, 5; each owns 32 TMEM lanes x 32 state columns): the round trip, and, while
+//       the main products of block n run, the output tile of block n-1 (TMEM -> shared -> TMA
+//       reduce-add into y, which the host zeroed; the two directions of a head are two CTAs).
+// Hand-overs are mbarriers (operands ready / operand set free / products done) and two named
+// barriers; every wait is bounded.
+constexpr int kPThreads = 448;    // 4 state warps, 1 control warp, 8 producer warps, 1 loader warp
+constexpr int kProducers = 256;
+constexpr int kBarRound = 1;     // named barrier: state + control, 160 threads
+constexpr int kBarYTile = 2;     // state, 128 threads
+constexpr int kBarProd = 3;      // producers, 256 threads
+
+struct OpSet {
+    __nv_bfloat16 opR[16 * 64];       // B of the read-out; through a base 1 KB lower also the A of the scores (rows 64..79)
+    __nv_bfloat16 opKb[16 * 64];      // B of the scores: rows = token s, K = key
+    __nv_bfloat16 opK[64 * 16];       // B of the update: rows = key, K = token
+    __nv_bfloat16 opV[64 * 16];       // A of the update and of the in-block part (rows 64..127 of the instruction: whatever follows)
+    __nv_bfloat16 opP[16 * 16];       // B of the in-block part: rows = token t, K = token s
+    float dtot[N];
+    float diag[SC];
+    uint32_t pairwise;                // the producers wrote opP themselves (strong decay)
+    uint32_t pad[15];
+};
+
+struct __align__(1024) SmemP {
+    __nv_bfloat16 opS[64 * 64];       // A of the read-out: S^T, rows = value, K = key (rows 64..127: the bytes that follow)
+    OpSet sets[2];
+    float raw[2][4][SC][N];           // r, k, v, w of two blocks in flight
+    float ytile[2][SC][N];
+    float acum[SC + 1][N];            // running log-decay sums, restarting every 4 tokens (rows 4, 8, 12, 16: totals of a quarter)
+    float u[N];
+    uint64_t raw_full[2];
+    uint64_t raw_free[2];
+    uint64_t ops_ready[2];
+    uint64_t ops_free[2];
+    uint64_t bar_main;
+    uint64_t bar_score;
+    uint32_t tmem_base;
+};
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool named_bar_or(int id, int threads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, %2, %3, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(threads)
+        : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&x)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7])
+                 : "r"(taddr));
+}
+
+__global__ void __launch_bounds__(kPThreads, 2)
+wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
+                         const __grid_constant__ CUtensorMap map_y) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    SmemP& s = *reinterpret_cast<SmemP*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int bh = blockIdx.x >> 1;
+    const bool rightward = (blockIdx.x & 1) == 0;
+    const int b = bh / a.H, h = bh % a.H;
+    const int T = a.T, C = a.H * N;
+    const size_t base = static_cast<size_t>(b) * T * C + static_cast<size_t>(h) * N;
+    const int n_steps = (T + SC - 1) / SC;
+
+    const bool is_state = (warp & 3) < 2 && warp < 8;          // warps 0, 1, 4, 5
+    const bool is_control = warp == 2;
+    const bool is_loader = warp == 13;
+    const bool is_producer = !is_state && !is_control && !is_loader;   // warps 3, 6..12
+    const int pid = ((warp == 3) ? 0 : warp - 5) * 32 + lane;   // producers: 0..255
+
+    auto tile_start = [&](int step) { return rightward ? step * SC : T - SC * (step + 1); };
+    auto row_of = [&](int t) { return rightward ? t : SC - 1 - t; };
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            sm100::mbar_init(&s.raw_full[i], 1);
+            sm100::mbar_init(&s.raw_free[i], 1);
+            sm100::mbar_init(&s.ops_ready[i], 1);
+            sm100::mbar_init(&s.ops_free[i], 1);
+        }
+        sm100::mbar_init(&s.bar_main, 1);
+        sm100::mbar_init(&s.bar_score, 1);
+        sm100::mbar_init_fence();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)),
+                     "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid < N) s.u[tid] = a.u[h * N + tid];
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s.tmem_base;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
+
+    bool failed = false;
+    auto wait_on = [&](uint64_t* bar, uint32_t parity) {
+        if (!failed && !sm100::mbar_wait(bar, parity, kWaitLimit)) { failed = true; atomicExch(a.status, 1u); }
+    };
+
+    if (is_producer) {
+        // =================================== producers ===================================
+        for (int q = 0; q < n_steps; ++q) {
+            const int slot = q & 1;
+            const uint32_t use_parity = (q >> 1) & 1;
+            OpSet& set = s.sets[slot];
+            float(&raw)[4][SC][N] = s.raw[slot];
+            wait_on(&s.raw_full[slot], use_parity);
+            if (q >= 2) wait_on(&s.ops_free[slot], use_parity ^ 1u);   // the products of block q-2 are done with this set
+            // ---- phase A: log-decays and their running sums; thread = (key channel, quarter of the block) ----
+            {
+                const int c = pid & 63, quarter = pid >> 6;
+                float wv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[j] = raw[3][row_of(quarter * 4 + j)][c];
+                float run = 0.f;
+                if (quarter == 0) s.acum[0][c] = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int t = quarter * 4 + j;
+                    run += (q * SC + t < T) ? -__expf(wv[j]) : 0.f;
+                    s.acum[t + 1][c] = run;
+                }
+            }
+            sm100::named_bar_sync(kBarProd, kProducers);
+            // a_t[c] = acum[t][c] + the totals (rows 4, 8, 12) of the quarters that end before t
+            // ---- job 1: thread = (token t, 4 key channels): Rs, Kb, bonus ----
+            {
+                const int t = pid >> 4, c0 = (pid & 15) * 4, row = row_of(t);
+                const float4 rv = *reinterpret_cast<const float4*>(&raw[0][row][c0]);
+                const float4 kv = *reinterpret_cast<const float4*>(&raw[1][row][c0]);
+                const float4 at = *reinterpret_cast<const float4*>(&s.acum[t][c0]);
+                const float4 at1 = *reinterpret_cast<const float4*>(&s.acum[t + 1][c0]);
+                const float4 q1 = *reinterpret_cast<const float4*>(&s.acum[4][c0]);
+                const float4 q2 = *reinterpret_cast<const float4*>(&s.acum[8][c0]);
+                const float4 q3 = *reinterpret_cast<const float4*>(&s.acum[12][c0]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&s.acum[16][c0]);
+                const float4 uu = *reinterpret_cast<const float4*>(&s.u[c0]);
+                const float rvv[4] = {rv.x, rv.y, rv.z, rv.w}, kvv[4] = {kv.x, kv.y, kv.z, kv.w};
+                const float a0[4] = {at.x, at.y, at.z, at.w}, a1[4] = {at1.x, at1.y, at1.z, at1.w};
+                const float t1[4] = {q1.x, q1.y, q1.z, q1.w}, t2[4] = {q2.x, q2.y, q2.z, q2.w};
+                const float t3[4] = {q3.x, q3.y, q3.z, q3.w}, t4[4] = {q4.x, q4.y, q4.z, q4.w};
+                const float uv[4] = {uu.x, uu.y, uu.z, uu.w};
+                float rs[4], kb[4], bonus = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a_t = a0[i] + (t > 4 ? t1[i] : 0.f) + (t > 8 ? t2[i] : 0.f) + (t > 12 ? t3[i] : 0.f);
+                    const float a_t1 = a1[i] + (t + 1 > 4 ? t1[i] : 0.f) + (t + 1 > 8 ? t2[i] : 0.f) + (t + 1 > 12 ? t3[i] : 0.f);
+                    const float A = (t1[i] + t2[i]) + (t3[i] + t4[i]);
+                    rs[i] = rvv[i] * __expf(a_t);
+                    kb[i] = (A < -kMaxLogDecay) ? 0.f : kvv[i] * __expf(-a_t1);
+                    bonus += rvv[i] * uv[i] * kvv[i];
+                }
+                *reinterpret_cast<uint2*>(&set.opR[op_index(16, t, c0)]) = make_uint2(pack_bf16(rs[0], rs[1]), pack_bf16(rs[2], rs[3]));
+                *reinterpret_cast<uint2*>(&set.opKb[op_index(16, t, c0)]) = make_uint2(pack_bf16(kb[0], kb[1]), pack_bf16(kb[2], kb[3]));
+                bonus += __shfl_xor_sync(0xffffffffu, bonus, 1);
+                bonus += __shfl_xor_sync(0xffffffffu, bonus, 2);
+                bonus += __shfl_xor_sync(0xffffffffu, bonus, 4);
+                bonus += __shfl_xor_sync(0xffffffffu, bonus, 8);
+                if ((pid & 15) == 0) set.diag[t] = rightward ? bonus : 0.f;
+            }
+            // ---- job 2: thread = (key channel, quarter of the block): Ks, V^T, e^A ----
+            bool big;
+            {
+                const int c = pid & 63, quarter = pid >> 6;
+                const float t1 = s.acum[4][c], t2 = s.acum[8][c], t3 = s.acum[12][c], t4 = s.acum[16][c];
+                const float A = (t1 + t2) + (t3 + t4);
+                big = A < -kMaxLogDecay;
+                float kh[4], vv[4], a1[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int t = quarter * 4 + j, row = row_of(t);
+                    a1[j] = s.acum[t + 1][c];
+                    kh[j] = raw[1][row][c];
+                    vv[j] = raw[2][row][c];
+                }
+                if (quarter == 0) set.dtot[c] = __expf(A);
+                const float before = (quarter > 0 ? t1 : 0.f) + (quarter > 1 ? t2 : 0.f) + (quarter > 2 ? t3 : 0.f);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) kh[j] *= __expf(A - (a1[j] + before));
+                *reinterpret_cast<uint2*>(&set.opK[op_index(64, c, quarter * 4)]) = make_uint2(pack_bf16(kh[0], kh[1]), pack_bf16(kh[2], kh[3]));
+                *reinterpret_cast<uint2*>(&set.opV[op_index(64, c, quarter * 4)]) = make_uint2(pack_bf16(vv[0], vv[1]), pack_bf16(vv[2], vv[3]));
+            }
+            const bool pairwise = named_bar_or(kBarProd, kProducers, big);   // also orders diag before the loop below
+            if (pairwise) {
+                // ---- strong decay: the 16 x 16 scores pairwise in fp32, every exponent <= 0 ----
+                const int t = pid >> 4, sidx = pid & 15;
+                const float* rt = raw[0][row_of(t)];
+                const float* ks = raw[1][row_of(sidx)];
+                float acc = 0.f;
+                if (sidx < t) {
+                    const int s1 = sidx + 1;
+#pragma unroll 8
+                    for (int i = 0; i < N; ++i) {
+                        const float q1 = s.acum[4][i], q2 = s.acum[8][i], q3 = s.acum[12][i];
+                        const float a_t = s.acum[t][i] + (t > 4 ? q1 : 0.f) + (t > 8 ? q2 : 0.f) + (t > 12 ? q3 : 0.f);
+                        const float a_s = s.acum[s1][i] + (s1 > 4 ? q1 : 0.f) + (s1 > 8 ? q2 : 0.f) + (s1 > 12 ? q3 : 0.f);
+                        acc += rt[i] * ks[i] * __expf(a_t - a_s);
+                    }
+                } else if (sidx == t) {
+                    acc = set.diag[t];
+                }
+                // one 4-byte store per lane pair: 2-byte shared stores are slow
+                const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+                if ((sidx & 1) == 0) *reinterpret_cast<uint32_t*>(&set.opP[op_index(16, t, sidx)]) = pack_bf16(acc, other);
+            }
+            if (pid == 0) set.pairwise = pairwise ? 1u : 0u;
+            sm100::fence_proxy_async_smem();
+            sm100::named_bar_sync(kBarProd, kProducers);
+            if (pid == 0) {
+                mbar_arrive(&s.ops_ready[slot]);
+                mbar_arrive(&s.raw_free[slot]);               // every producer is done reading this staging slot
+            }
+        }
+    } else if (is_loader) {
+        // =================================== loader ===================================
+        if (lane == 0) {
+            sm100::prefetch_tensormap(&map_r);
+            sm100::prefetch_tensormap(&map_k);
+            sm100::prefetch_tensormap(&map_v);
+            sm100::prefetch_tensormap(&map_w);
+            for (int step = 0; step < n_steps; ++step) {
+                const int slot = step & 1, y0 = tile_start(step);
+                if (step >= 2) wait_on(&s.raw_free[slot], ((step >> 1) & 1) ^ 1u);
+                sm100::mbar_expect_tx(&s.raw_full[slot], 4 * SC * N * sizeof(float));
+                sm100::tma_load_3d(&s.raw[slot][0][0][0], &map_r, &s.raw_full[slot], h * N, y0, b);
+                sm100::tma_load_3d(&s.raw[slot][1][0][0], &map_k, &s.raw_full[slot], h * N, y0, b);
+                sm100::tma_load_3d(&s.raw[slot][2][0][0], &map_v, &s.raw_full[slot], h * N, y0, b);
+                sm100::tma_load_3d(&s.raw[slot][3][0][0], &map_w, &s.raw_full[slot], h * N, y0, b);
+            }
+        }
+    } else if (is_control) {
+        // =================================== control ===================================
+        uint32_t score_parity = 0;
+        // descriptors are formed by the whole warp (warp-uniform values), one elected lane issues
+        const uint64_t d_state = make_desc(smem_u32(s.opS), 1024, 128);
+        for (int m = 0; m < n_steps; ++m) {
+            const int slot = m & 1;
+            OpSet& set = s.sets[slot];
+            const uint64_t d_r = make_desc(smem_u32(set.opR), 256, 128);
+            const uint64_t d_ra = make_desc(smem_u32(set.opR) - 1024, 256, 128);      // rows 64..79 = Rs
+            const uint64_t d_kb = make_desc(smem_u32(set.opKb), 256, 128);
+            const uint64_t d_v = make_desc(smem_u32(set.opV), 1024, 128);
+            const uint64_t d_p = make_desc(smem_u32(set.opP), 256, 128);
+            const uint64_t d_k = make_desc(smem_u32(set.opK), 1024, 128);
+            wait_on(&s.ops_ready[slot], (m >> 1) & 1);
+            const bool pairwise = set.pairwise != 0;
+            if (!pairwise) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < N / 16; ++ks)      // a K step of 16 = 512 bytes = 32 descriptor units
+                        umma_bf16(tmem + 80, d_ra + 32 * ks, d_kb + 32 * ks, instr_desc(128, 16), ks > 0 ? 1u : 0u);
+                    tc_commit(&s.bar_score);
+                }
+                __syncwarp();
+                wait_on(&s.bar_score, score_parity);
+                score_parity ^= 1u;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t x[16];
+                tmem_ld16_issue(lane_addr + 80, x);
+                tmem_ld_wait();
+                if (lane < 16) {
+                    float pr[16];
+                    const float dg = set.diag[lane];
+#pragma unroll
+                    for (int qq = 0; qq < SC; ++qq) pr[qq] = qq < lane ? __uint_as_float(x[qq]) : (qq == lane ? dg : 0.f);
+                    *reinterpret_cast<uint4*>(&set.opP[op_index(16, lane, 0)]) =
+                        make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
+                    *reinterpret_cast<uint4*>(&set.opP[op_index(16, lane, 8)]) =
+                        make_uint4(pack_bf16(pr[8], pr[9]), pack_bf16(pr[10], pr[11]), pack_bf16(pr[12], pr[13]), pack_bf16(pr[14], pr[15]));
+                }
+                sm100::fence_proxy_async_smem();
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            sm100::named_bar_sync(kBarRound, 160);            // the state warps have finished the round trip of block m
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t ycol = tmem + 64 + 32 * slot;      // y^T of even blocks at columns 64..79, odd at 96..111
+            if (elect_one()) {
+#pragma unroll
+                for (int ks = 0; ks < N / 16; ++ks)          // state operand: a K step of 16 = 2048 bytes = 128 units
+                    umma_bf16(ycol, d_state + 128 * ks, d_r + 32 * ks, instr_desc(128, 16), ks > 0 ? 1u : 0u);
+                umma_bf16(ycol, d_v, d_p, instr_desc(128, 16), 1u);
+                umma_bf16(tmem, d_v, d_k, instr_desc(128, 64), 1u);
+                tc_commit(&s.bar_main);
+                tc_commit(&s.ops_free[slot]);
+            }
+            __syncwarp();
+        }
+    } else {
+        // =================================== state ===================================
+        const int lg = warp & 1, ch = warp >> 2;               // 32 TMEM lanes x 32 state columns per warp
+        const int j = lg * 32 + lane;                          // value channel = TMEM lane
+        const int sid = ch * 64 + j;                           // 0..127 within the role
+        for (int m = 0; m <= n_steps; ++m) {
+            if (m >= 1) wait_on(&s.bar_main, (m - 1) & 1);     // products of block m-1 are complete
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (m < n_steps) {
+                const OpSet& set = s.sets[m & 1];
+                wait_on(&s.ops_ready[m & 1], (m >> 1) & 1);    // dtot of block m
+                // ---- round trip of this warp's 32 x 32 piece: bf16 copy for the read-out, decay in place ----
+                uint32_t x[2][16];
+                if (m > 0) {
+                    tmem_ld16_issue(lane_addr + ch * 32, x[0]);
+                    tmem_ld16_issue(lane_addr + ch * 32 + 16, x[1]);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) x[0][i] = x[1][i] = 0u;   // the walk starts from the zero state
+                }
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int c0 = ch * 32 + g * 16;
+                    float f[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(x[g][i]);
+                    *reinterpret_cast<uint4*>(&s.opS[op_index(64, j, c0)]) =
+                        make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                    *reinterpret_cast<uint4*>(&s.opS[op_index(64, j, c0 + 8)]) =
+                        make_uint4(pack_bf16(f[8], f[9]), pack_bf16(f[10], f[11]), pack_bf16(f[12], f[13]), pack_bf16(f[14], f[15]));
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) x[g][i] = __float_as_uint(f[i] * set.dtot[c0 + i]);
+                    tmem_st16(lane_addr + c0, x[g]);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                sm100::fence_proxy_async_smem();
+                if (sid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the y tile of block m-3 has left
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                sm100::named_bar_sync(kBarRound, 160);
+            }
+            if (m == n_steps) {
+                // last pass: no round trip above, so the y slot is released here
+                if (sid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                sm100::named_bar_sync(kBarYTile, 128);
+            }
+            if (m >= 1) {
+                // ---- y of block m-1, while the products of block m run: this warp takes 8 of the 16 tokens ----
+                const int step = m - 1, ys = step & 1;
+                uint32_t yt[8];
+                tmem_ld8_issue(lane_addr + 64 + 32 * ys + ch * 8, yt);
+                tmem_ld_wait();
+                const int y0 = tile_start(step);
+                if (y0 >= 0) {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) s.ytile[ys][row_of(ch * 8 + t)][j] = __uint_as_float(yt[t]);
+                    sm100::fence_proxy_async_smem();
+                    sm100::named_bar_sync(kBarYTile, 128);
+                    if (sid == 0) {
+                        tma_reduce_add_3d(&map_y, &s.ytile[ys][0][0], h * N, y0, b);      // rows past T are clipped
+                        sm100::tma_store_commit();
+                    }
+                } else {
+                    // ragged last block of the leftward walk: its tile would start before token 0
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        const int t_seq = step * SC + ch * 8 + t;
+                        if (t_seq < T) atomicAdd(a.y + base + static_cast<size_t>(T - 1 - t_seq) * C + j, __uint_as_float(yt[t]));
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        }
+        if (sid == 0) sm100::tma_store_wait_all();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+}
+
 int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw, const float* u,
-            float* y, unsigned* status, cudaStream_t stream) {
+            float* y, unsigned* status, bool pipelined, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(wkv6_tc_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(sizeof(Smem))) != cudaSuccess)
+                                 static_cast<int>(sizeof(Smem))) != cudaSuccess ||
+            cudaFuncSetAttribute(wkv6_tc_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(SmemP))) != cudaSuccess)
             return -1;
         configured = true;
     }
@@ -433,6 +829,12 @@ int forward(int B, int T, int H, const float* r, const float* k, const float* v,
     }
     Args a{B, T, H, r, k, v, w_raw, u, y, status};
     cudaMemsetAsync(status, 0, sizeof(unsigned), stream);
+    if (pipelined) {
+        // both directions add into y
+        cudaMemsetAsync(y, 0, static_cast<size_t>(B) * T * C * sizeof(float), stream);
+        wkv6_tc_pipelined_kernel<<<2 * B * H, kPThreads, sizeof(SmemP), stream>>>(a, mr, mk, mv, mw, my);
+        return 1;
+    }
     wkv6_tc_forward_kernel<<<B * H, kThreads, sizeof(Smem), stream>>>(a, mr, mk, mv, mw, my);
     return 1;
 }
