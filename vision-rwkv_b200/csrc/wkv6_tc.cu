@@ -453,7 +453,7 @@ struct __align__(1024) SmemP {
     OpSet sets[2];
     float raw[2][4][SC][N];           // r, k, v, w of two blocks in flight
     float ytile[2][SC][N];
-    float acum[SC + 1][N];            // running log-decay sums, restarting every 4 tokens (rows 4, 8, 12, 16: totals of a quarter)
+    float acum[SC + 1][N];            // a_0 .. a_16 per key channel
     float u[N];
     uint64_t raw_full[2];
     uint64_t raw_free[2];
@@ -546,24 +546,30 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
             OpSet& set = s.sets[slot];
             float(&raw)[4][SC][N] = s.raw[slot];
             wait_on(&s.raw_full[slot], use_parity);
-            if (q >= 2) wait_on(&s.ops_free[slot], use_parity ^ 1u);   // the products of block q-2 are done with this set
-            // ---- phase A: log-decays and their running sums; thread = (key channel, quarter of the block) ----
+            // ---- phase A: running sums of the log-decays, a_t[c] for t = 0..16; thread = (key channel, quarter of
+            //      the block), the four quarters of a channel in one warp so that their totals travel by shuffle ----
             {
-                const int c = pid & 63, quarter = pid >> 6;
+                const int c = (pid >> 5) * 8 + (lane & 7), quarter = lane >> 3;
                 float wv[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) wv[j] = raw[3][row_of(quarter * 4 + j)][c];
-                float run = 0.f;
-                if (quarter == 0) s.acum[0][c] = 0.f;
+                float pre[4], run = 0.f;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int t = quarter * 4 + j;
-                    run += (q * SC + t < T) ? -__expf(wv[j]) : 0.f;
-                    s.acum[t + 1][c] = run;
+                    run += (q * SC + quarter * 4 + j < T) ? -__expf(wv[j]) : 0.f;
+                    pre[j] = run;
                 }
+                // totals of the quarters before this one
+                const float up8 = __shfl_up_sync(0xffffffffu, run, 8);
+                const float up16 = __shfl_up_sync(0xffffffffu, run, 16);
+                const float up24 = __shfl_up_sync(0xffffffffu, run, 24);
+                const float before = (quarter > 0 ? up8 : 0.f) + (quarter > 1 ? up16 : 0.f) + (quarter > 2 ? up24 : 0.f);
+                if (quarter == 0) s.acum[0][c] = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s.acum[quarter * 4 + j + 1][c] = pre[j] + before;
             }
+            if (q >= 2) wait_on(&s.ops_free[slot], use_parity ^ 1u);   // the products of block q-2 are done with this set
             sm100::named_bar_sync(kBarProd, kProducers);
-            // a_t[c] = acum[t][c] + the totals (rows 4, 8, 12) of the quarters that end before t
             // ---- job 1: thread = (token t, 4 key channels): Rs, Kb, bonus ----
             {
                 const int t = pid >> 4, c0 = (pid & 15) * 4, row = row_of(t);
@@ -571,40 +577,35 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
                 const float4 kv = *reinterpret_cast<const float4*>(&raw[1][row][c0]);
                 const float4 at = *reinterpret_cast<const float4*>(&s.acum[t][c0]);
                 const float4 at1 = *reinterpret_cast<const float4*>(&s.acum[t + 1][c0]);
-                const float4 q1 = *reinterpret_cast<const float4*>(&s.acum[4][c0]);
-                const float4 q2 = *reinterpret_cast<const float4*>(&s.acum[8][c0]);
-                const float4 q3 = *reinterpret_cast<const float4*>(&s.acum[12][c0]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&s.acum[16][c0]);
-                const float4 uu = *reinterpret_cast<const float4*>(&s.u[c0]);
+                const float4 aA = *reinterpret_cast<const float4*>(&s.acum[SC][c0]);
                 const float rvv[4] = {rv.x, rv.y, rv.z, rv.w}, kvv[4] = {kv.x, kv.y, kv.z, kv.w};
                 const float a0[4] = {at.x, at.y, at.z, at.w}, a1[4] = {at1.x, at1.y, at1.z, at1.w};
-                const float t1[4] = {q1.x, q1.y, q1.z, q1.w}, t2[4] = {q2.x, q2.y, q2.z, q2.w};
-                const float t3[4] = {q3.x, q3.y, q3.z, q3.w}, t4[4] = {q4.x, q4.y, q4.z, q4.w};
-                const float uv[4] = {uu.x, uu.y, uu.z, uu.w};
-                float rs[4], kb[4], bonus = 0.f;
+                const float aa[4] = {aA.x, aA.y, aA.z, aA.w};
+                float rs[4], kb[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float a_t = a0[i] + (t > 4 ? t1[i] : 0.f) + (t > 8 ? t2[i] : 0.f) + (t > 12 ? t3[i] : 0.f);
-                    const float a_t1 = a1[i] + (t + 1 > 4 ? t1[i] : 0.f) + (t + 1 > 8 ? t2[i] : 0.f) + (t + 1 > 12 ? t3[i] : 0.f);
-                    const float A = (t1[i] + t2[i]) + (t3[i] + t4[i]);
-                    rs[i] = rvv[i] * __expf(a_t);
-                    kb[i] = (A < -kMaxLogDecay) ? 0.f : kvv[i] * __expf(-a_t1);
-                    bonus += rvv[i] * uv[i] * kvv[i];
+                    rs[i] = rvv[i] * __expf(a0[i]);
+                    kb[i] = (aa[i] < -kMaxLogDecay) ? 0.f : kvv[i] * __expf(-a1[i]);
                 }
                 *reinterpret_cast<uint2*>(&set.opR[op_index(16, t, c0)]) = make_uint2(pack_bf16(rs[0], rs[1]), pack_bf16(rs[2], rs[3]));
                 *reinterpret_cast<uint2*>(&set.opKb[op_index(16, t, c0)]) = make_uint2(pack_bf16(kb[0], kb[1]), pack_bf16(kb[2], kb[3]));
-                bonus += __shfl_xor_sync(0xffffffffu, bonus, 1);
-                bonus += __shfl_xor_sync(0xffffffffu, bonus, 2);
-                bonus += __shfl_xor_sync(0xffffffffu, bonus, 4);
-                bonus += __shfl_xor_sync(0xffffffffu, bonus, 8);
-                if ((pid & 15) == 0) set.diag[t] = rightward ? bonus : 0.f;
+                if (rightward) {       // the bonus exists in this direction only
+                    const float4 uu = *reinterpret_cast<const float4*>(&s.u[c0]);
+                    float bonus = (rv.x * uu.x * kv.x + rv.y * uu.y * kv.y) + (rv.z * uu.z * kv.z + rv.w * uu.w * kv.w);
+                    bonus += __shfl_xor_sync(0xffffffffu, bonus, 1);
+                    bonus += __shfl_xor_sync(0xffffffffu, bonus, 2);
+                    bonus += __shfl_xor_sync(0xffffffffu, bonus, 4);
+                    bonus += __shfl_xor_sync(0xffffffffu, bonus, 8);
+                    if ((pid & 15) == 0) set.diag[t] = bonus;
+                } else if ((pid & 15) == 0) {
+                    set.diag[t] = 0.f;
+                }
             }
             // ---- job 2: thread = (key channel, quarter of the block): Ks, V^T, e^A ----
             bool big;
             {
                 const int c = pid & 63, quarter = pid >> 6;
-                const float t1 = s.acum[4][c], t2 = s.acum[8][c], t3 = s.acum[12][c], t4 = s.acum[16][c];
-                const float A = (t1 + t2) + (t3 + t4);
+                const float A = s.acum[SC][c];
                 big = A < -kMaxLogDecay;
                 float kh[4], vv[4], a1[4];
 #pragma unroll
@@ -615,9 +616,8 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
                     vv[j] = raw[2][row][c];
                 }
                 if (quarter == 0) set.dtot[c] = __expf(A);
-                const float before = (quarter > 0 ? t1 : 0.f) + (quarter > 1 ? t2 : 0.f) + (quarter > 2 ? t3 : 0.f);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) kh[j] *= __expf(A - (a1[j] + before));
+                for (int j = 0; j < 4; ++j) kh[j] *= __expf(A - a1[j]);
                 *reinterpret_cast<uint2*>(&set.opK[op_index(64, c, quarter * 4)]) = make_uint2(pack_bf16(kh[0], kh[1]), pack_bf16(kh[2], kh[3]));
                 *reinterpret_cast<uint2*>(&set.opV[op_index(64, c, quarter * 4)]) = make_uint2(pack_bf16(vv[0], vv[1]), pack_bf16(vv[2], vv[3]));
             }
@@ -629,14 +629,8 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
                 const float* ks = raw[1][row_of(sidx)];
                 float acc = 0.f;
                 if (sidx < t) {
-                    const int s1 = sidx + 1;
 #pragma unroll 8
-                    for (int i = 0; i < N; ++i) {
-                        const float q1 = s.acum[4][i], q2 = s.acum[8][i], q3 = s.acum[12][i];
-                        const float a_t = s.acum[t][i] + (t > 4 ? q1 : 0.f) + (t > 8 ? q2 : 0.f) + (t > 12 ? q3 : 0.f);
-                        const float a_s = s.acum[s1][i] + (s1 > 4 ? q1 : 0.f) + (s1 > 8 ? q2 : 0.f) + (s1 > 12 ? q3 : 0.f);
-                        acc += rt[i] * ks[i] * __expf(a_t - a_s);
-                    }
+                    for (int i = 0; i < N; ++i) acc += rt[i] * ks[i] * __expf(s.acum[t][i] - s.acum[sidx + 1][i]);
                 } else if (sidx == t) {
                     acc = set.diag[t];
                 }
