@@ -28,6 +28,11 @@
 // Accuracy is that of bf16 operands with fp32 accumulation (about 1e-2 of max|y|); the exact fp32
 // sweeps of wkv6_sweeps.cu remain the default for float32 callers.
 //
+// Two kernels share this arithmetic.  wkv6_tc_forward_kernel, described above, does every phase of
+// a block with all of its four warps in turn.  wkv6_tc_pipelined_kernel, further down and the one
+// used by default, splits the phases over warp roles so that only the state's round trip and the
+// products remain serial.
+//
 // Reference being replaced: classification/mmcls_custom/models/backbones/cuda_v6/wkv6_cuda.cu:6-97.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
