@@ -188,7 +188,21 @@ def side_measurements(dev, world, dist):
     out["vrwkv_b_inference"] = {"img_per_s": B * world / (ms * 1e-3), "ms_per_batch": ms,
                                 "batch_per_gpu": B, "resolution": 224, "n_gpus": world,
                                 "gemm_dtype": "bf16 autocast", "wkv_dtype": "f32"}
-    del model, img
+    del model
+    # VRWKV6-B (embed 768, 12 heads, 12 blocks): same images; under autocast r, k, v reach the WKV6 operator in
+    # bfloat16 and the tcgen05 forward runs
+    from vision_rwkv_b200.backbone6 import build_v6
+    model6 = build_v6("vrwkv6_b").to(dev).eval()
+
+    def infer6():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            model6(img)
+
+    ms = _timed(infer6, dev, world, dist, iters=5)
+    out["vrwkv6_b_inference"] = {"img_per_s": B * world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": B,
+                                 "resolution": 224, "n_gpus": world, "gemm_dtype": "bf16 autocast",
+                                 "wkv_dtype": "bf16 operands on tensor cores, f32 state"}
+    del model6, img
     # Bi-WKV with bfloat16 activations at the headline shape: 6 + 10 = 16 bytes per element fwd+bwd
     Bh, Th, Ch = WORKLOAD["B"], WORKLOAD["T"], WORKLOAD["C"]
     gh = torch.Generator(device=dev).manual_seed(11)

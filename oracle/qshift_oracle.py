@@ -32,3 +32,24 @@ def q_shift(x, resolution, shift_pixel=1, gamma=0.25):
 def qshift_mix(x, mixes, resolution, shift_pixel=1, gamma=0.25):
     xx = q_shift(x, resolution, shift_pixel, gamma)
     return [x * m + xx * (1 - m) for m in mixes]
+
+
+def q_shift_multihead(x, resolution, shift_pixel=1, head_dim=64):
+    """The per-head variant of VRWKV6 (classification/mmcls_custom/models/backbones/vrwkv6.py:75-101):
+    within every head of `head_dim` channels the quarters take the value of the left, right,
+    upper and lower neighbour at distance `shift_pixel`; a missing neighbour gives 0.  Written
+    token by token so that it shares nothing with the slice-assignment forms."""
+    B, T, C = x.shape
+    H, W = resolution
+    out = torch.zeros_like(x)
+    offsets = [(0, -shift_pixel), (0, shift_pixel), (-shift_pixel, 0), (shift_pixel, 0)]   # (dh, dw) of the source
+    quarter = head_dim // 4
+    for h in range(H):
+        for w in range(W):
+            for head in range(C // head_dim):
+                for part, (dh, dw) in enumerate(offsets):
+                    hs, ws = h + dh, w + dw
+                    if 0 <= hs < H and 0 <= ws < W:
+                        c0 = head * head_dim + part * quarter
+                        out[:, h * W + w, c0:c0 + quarter] = x[:, hs * W + ws, c0:c0 + quarter]
+    return out
