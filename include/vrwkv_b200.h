@@ -35,8 +35,9 @@ enum vrwkv_status {
     VRWKV_ERR_LAUNCH = 5,      /* cudaGetLastError() reported a failure after a launch     */
     VRWKV_ERR_DEVICE = 6,      /* driver entry point or device attribute unavailable       */
     VRWKV_ERR_HEAD_SIZE = 7,   /* WKV6: C != 64 * H                                        */
-    VRWKV_ERR_UNSUPPORTED = 8  /* bf16 entry points: shape or alignment outside what their
-                                  kernels cover; nothing ran, use the f32 entry points       */
+    VRWKV_ERR_UNSUPPORTED = 8  /* bf16 and saved-result entry points: shape or alignment outside
+                                  what their kernels cover; nothing ran, use the plain f32
+                                  entry points                                               */
 };
 
 /* Library version, major*10000 + minor*100 + patch. */
@@ -90,6 +91,23 @@ size_t vrwkv_biwkv_backward_workspace_bytes(int B, int T, int C);
 int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
                              const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Forward that keeps what the backward needs, and the backward that uses it.  The reference's
+ * backward rebuilds y, 1/Den and the shift per token inside its kernel and holds them in three
+ * scratch tensors (bi_wkv_kernel.cu:259-302, 415-417).  Here the forward can write log Den_t next
+ * to y (one extra float per element), and vrwkv_biwkv_backward_saved_f32 takes k, v, gy and the
+ * saved y, log Den: it needs one cross-tile exchange instead of two and is about 40 % faster than
+ * vrwkv_biwkv_backward_f32, at the price of keeping logden (B*T*C floats) from forward to backward.
+ * Results agree with the recomputing pair to float32 rounding.  Same workspace sizes.  Both are
+ * served by the single-pass TMA kernels only (C % 4 == 0, 16-byte aligned tensors, T below about
+ * 37 000); otherwise they return VRWKV_ERR_UNSUPPORTED and nothing ran. */
+int vrwkv_biwkv_forward_save_f32(int B, int T, int C, const float* w, const float* u, const float* k,
+                                 const float* v, float* y, float* logden, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+int vrwkv_biwkv_backward_saved_f32(int B, int T, int C, const float* w, const float* u, const float* k,
+                                   const float* v, const float* gy, const float* y, const float* logden,
+                                   float* gwgu, float* gk, float* gv, void* workspace,
+                                   size_t workspace_bytes, void* stream);
 
 /* bfloat16 activations: k, v, y, gy, gk, gv are bfloat16 bit patterns (uint16_t), w, u and
  * gwgu stay float, arithmetic is the f32 kernels' (inputs widened in shared memory, results

@@ -26,6 +26,8 @@ SIGNATURES = {
     "vrwkv_biwkv_forward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 6 + [_c_size_t, _ptr]),
     "vrwkv_biwkv_backward_workspace_bytes": (_c_size_t, [_c_int] * 3),
     "vrwkv_biwkv_backward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 9 + [_c_size_t, _ptr]),
+    "vrwkv_biwkv_forward_save_f32": (_c_int, [_c_int] * 3 + [_ptr] * 7 + [_c_size_t, _ptr]),
+    "vrwkv_biwkv_backward_saved_f32": (_c_int, [_c_int] * 3 + [_ptr] * 11 + [_c_size_t, _ptr]),
     "vrwkv_biwkv_forward_bf16": (_c_int, [_c_int] * 3 + [_ptr] * 6 + [_c_size_t, _ptr]),
     "vrwkv_biwkv_backward_bf16": (_c_int, [_c_int] * 3 + [_ptr] * 9 + [_c_size_t, _ptr]),
     "vrwkv_biwkv_forward_f32_noalloc": (_c_int, [_c_int] * 3 + [_ptr] * 6),

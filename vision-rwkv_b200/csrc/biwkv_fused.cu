@@ -686,7 +686,7 @@ __device__ __noinline__ void rigorous_aggregates(const Col<E> ks, const Col<E> v
     acc4_decay(right, w, static_cast<float>(kL - n));
     left.o -= w;
 }
-template <typename E>
+template <typename E, bool kSave>
 __device__ __noinline__ void rigorous_emit_forward(const Col<E> ks, const Col<E> vs, int n, float w, float u,
                                                    const Entering& e) {
     const float last = static_cast<float>(n - 1);
@@ -703,14 +703,18 @@ __device__ __noinline__ void rigorous_emit_forward(const Col<E> ks, const Col<E>
         const float k = ks.ld(i), v = vs.ld(i), d = static_cast<float>(i);
         const TokenOut o = token_out(acc2_at(P, w, d), stash[i], k, v, u);
         ks.st(i, o.y);
+        if (kSave) vs.st(i, o.m - logf(o.inv_den));          // log Den_t
         acc2_add(P, k + w * d, v, 1.f);
     }
 }
 
-template <typename E>
+// kSave: also write log Den_t (one float per element, into the v slot and out through map_l) for
+// the backward that starts from the saved y and log Den instead of recomputing them.
+template <typename E, bool kSave>
 __global__ void __launch_bounds__(kThreads, 2)
 biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                               const __grid_constant__ CUtensorMap map_y, const Params p) {
+                               const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_l,
+                               const Params p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr uint32_t kStageBytes = 2 * kSlotBytes<E>;
     unsigned char* stage_base = smem_raw;                                           // [3][2][kTc][kCs] of E
@@ -807,7 +811,7 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             const Col<E> ks(slot_k, warp, lane), vs(slot_k + kSlotBytes<E>, warp, lane);
             const Entering e1 = exchange_collect(p, ext, lane, warp, w, tile, tc.chunk, 0, 1, prev_in);
             if (!prev_safe) {
-                rigorous_emit_forward(ks, vs, nv, w, u, e1);
+                rigorous_emit_forward<E, kSave>(ks, vs, nv, w, u, e1);
             } else {
                 float kk[kL], vv[kL];
                 float m = kMinExp;
@@ -839,6 +843,7 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                     const float2 x = f2(kk[i] * vv[i], kk[i]);
                     const float2 nd = fma2(x, f2(eu, eu), add2(pr, stash[i]));
                     ks.st(i, __fdividef(nd.x, nd.y));
+                    if (kSave) vs.st(i, M + __logf(nd.y));   // log Den_t; v of this token is in a register
                     pr = mul2(add2(pr, x), lam2);
                 }
             }
@@ -846,11 +851,390 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             __syncthreads();
             if (threadIdx.x == 0) {
                 sm100::tma_store_3d(&map_y, slot_k, tc.strip * kCs, tc.chunk * kTc, tc.b);
+                if (kSave) sm100::tma_store_3d(&map_l, slot_k + kSlotBytes<E>, tc.strip * kCs, tc.chunk * kTc, tc.b);
                 sm100::tma_store_commit();
             }
         }
         prev_in = cur_in;
         prev_safe = cur_safe;
+    }
+    if (threadIdx.x == 0) sm100::tma_store_wait_all();
+}
+
+// ---- backward from the saved forward results ----------------------------------------------------
+// When the forward has kept y and log Den (biwkv_forward_pipelined_kernel<float, true>), the
+// backward does not need the first exchange level at all: G_t = gy_t / Den_t and H_t = G_t y_t are
+// local.  What remains is one level for the adjoint pairs [G, H], with first moments in distance in
+// *both* directions, because gw is then taken entirely from the adjoint side:
+//   gw = - sum_j e^{k_j} ((MQ^G_j + MR^G_j) v_j - (MQ^H_j + MR^H_j)).
+// Records therefore have ten rows (a, b, ma, mb, o for each direction).
+constexpr int kRows2 = 10;
+constexpr int kRecFloats2 = kRows2 * kCs;
+
+__device__ __forceinline__ void post_left4(float* rec, const Acc4& s) {
+    rec[5 * kCs] = s.a; rec[6 * kCs] = s.b; rec[7 * kCs] = s.ma; rec[8 * kCs] = s.mb; rec[9 * kCs] = s.o;
+}
+struct Entering4 {
+    Acc4 left;    // adjoint state entering the sub-chunk at its first token (from earlier outputs)
+    Acc4 right;   // ... at its last position (from later outputs)
+};
+struct Inside4 {
+    Acc4 inP, inS;
+};
+
+__device__ __forceinline__ Inside4 exchange_publish4(const Params& p, float* sub, int lane, int warp, float w, int tile,
+                                                     const Acc4& own_right, const Acc4& own_left) {
+    post_acc4(sub + warp * kRecFloats2 + lane, own_right);
+    post_left4(sub + warp * kRecFloats2 + lane, own_left);
+    __syncthreads();
+    Acc4 inP, inS;
+    {
+        float x4[kWarps], x2[kWarps];
+        float m4 = kMinExp, m2 = kMinExp;
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            const float* r = sub + s * kRecFloats2 + lane;
+            x4[s] = (s < warp) ? r[4 * kCs] - w * static_cast<float>((warp - 1 - s) * kL) : kMinExp;
+            x2[s] = (s > warp) ? r[9 * kCs] - w * static_cast<float>((s - warp - 1) * kL) : kMinExp;
+            m4 = wkv_max(m4, x4[s]);
+            m2 = wkv_max(m2, x2[s]);
+        }
+        inP = Acc4{0.f, 0.f, 0.f, 0.f, m4};
+        inS = Acc4{0.f, 0.f, 0.f, 0.f, m2};
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            const float* r = sub + s * kRecFloats2 + lane;
+            if (s < warp) {
+                const float f = fast_exp(x4[s] - m4);
+                const float d = static_cast<float>((warp - 1 - s) * kL);
+                const float a = r[0], b = r[kCs];
+                inP.a += f * a;
+                inP.b += f * b;
+                inP.ma += f * (r[2 * kCs] + d * a);
+                inP.mb += f * (r[3 * kCs] + d * b);
+            }
+            if (s > warp) {
+                const float f = fast_exp(x2[s] - m2);
+                const float d = static_cast<float>((s - warp - 1) * kL);
+                const float a = r[5 * kCs], b = r[6 * kCs];
+                inS.a += f * a;
+                inS.b += f * b;
+                inS.ma += f * (r[7 * kCs] + d * a);
+                inS.mb += f * (r[8 * kCs] + d * b);
+            }
+        }
+    }
+    if (warp == kWarps - 1 || warp == 0) {
+        float* mine = p.exch + static_cast<size_t>(tile) * kRecFloats2 + lane;
+        if (warp == kWarps - 1) {
+            Acc4 t = inP;
+            acc4_decay(t, w, static_cast<float>(kL));
+            post_acc4(mine, merge4(t, own_right));
+        }
+        if (warp == 0) {
+            Acc4 t = inS;
+            acc4_decay(t, w, static_cast<float>(kL));
+            post_left4(mine, merge4(t, own_left));
+        }
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence();
+            atomicAdd(p.flags + tile, 1u);
+        }
+    }
+    return Inside4{inP, inS};
+}
+
+__device__ __forceinline__ Entering4 exchange_collect4(const Params& p, float* ext, int lane, int warp, float w, int tile,
+                                                       int chunk, const Inside4& in) {
+    {
+        const int first = tile - chunk * p.interleave;
+        Acc4 P = acc4_zero(), S = acc4_zero();
+        for (int j0 = warp; j0 < p.n_chunks; j0 += 4 * kWarps) {
+            // flags polled four at a time with relaxed loads; the record loads take their address from the
+            // polled values, which orders them after the flags (see exchange_collect)
+            bool ok = true;
+            const unsigned* fl[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                fl[q] = (j < p.n_chunks && j != chunk) ? p.flags + (first + j * p.interleave) : nullptr;
+            }
+            unsigned seen[4] = {0u, 0u, 0u, 0u};
+            for (uint32_t spins = 0;; ++spins) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (seen[q] < 2u) seen[q] = fl[q] ? sm100::flag_relaxed(fl[q]) : 2u;
+                if (seen[0] >= 2u && seen[1] >= 2u && seen[2] >= 2u && seen[3] >= 2u) break;
+                if (spins > kSpinLimit ||
+                    ((spins & 1023u) == 1023u && *reinterpret_cast<volatile unsigned*>(p.status) != 0u)) {
+                    ok = false;
+                    break;
+                }
+                __nanosleep(spins < 8 ? 32 : 128);
+            }
+            const unsigned seen_all = seen[0] | seen[1] | seen[2] | seen[3];
+            const size_t dep = seen_all >> 31;
+            if (!ok && lane == 0) atomicOr(p.status, 1u);
+            float r0[4], r1[4], r2[4], r3[4], x[4];
+            float mP = kMinExp, mS = kMinExp;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                r0[q] = r1[q] = r2[q] = r3[q] = 0.f;
+                x[q] = kMinExp;
+                if (j < p.n_chunks && j != chunk) {
+                    const float* rec = p.exch + static_cast<size_t>(first + j * p.interleave) * kRecFloats2 + lane + dep +
+                                       (j < chunk ? 0 : 5 * kCs);
+                    r0[q] = sm100::ld_cg(rec); r1[q] = sm100::ld_cg(rec + kCs);
+                    r2[q] = sm100::ld_cg(rec + 2 * kCs); r3[q] = sm100::ld_cg(rec + 3 * kCs);
+                    x[q] = sm100::ld_cg(rec + 4 * kCs);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                if (j < p.n_chunks && j != chunk) {
+                    const float d = static_cast<float>((j < chunk ? chunk - 1 - j : j - chunk - 1) * kTc);
+                    x[q] -= w * d;
+                    r2[q] += d * r0[q];
+                    r3[q] += d * r1[q];
+                    if (j < chunk) mP = wkv_max(mP, x[q]);
+                    else mS = wkv_max(mS, x[q]);
+                }
+            }
+            Acc4 bp{0.f, 0.f, 0.f, 0.f, mP}, bs{0.f, 0.f, 0.f, 0.f, mS};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int j = j0 + q * kWarps;
+                if (j < p.n_chunks && j != chunk) {
+                    if (j < chunk) {
+                        const float f = fast_exp(x[q] - mP);
+                        bp.a += f * r0[q]; bp.b += f * r1[q]; bp.ma += f * r2[q]; bp.mb += f * r3[q];
+                    } else {
+                        const float f = fast_exp(x[q] - mS);
+                        bs.a += f * r0[q]; bs.b += f * r1[q]; bs.ma += f * r2[q]; bs.mb += f * r3[q];
+                    }
+                }
+            }
+            P = merge4(P, bp);
+            S = merge4(S, bs);
+        }
+        post_acc4(ext + warp * kRecFloats2 + lane, P);
+        post_left4(ext + warp * kRecFloats2 + lane, S);
+    }
+    __syncthreads();
+    Entering4 out;
+    {
+        float m4 = kMinExp, m2 = kMinExp;
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            m4 = wkv_max(m4, ext[s * kRecFloats2 + 4 * kCs + lane]);
+            m2 = wkv_max(m2, ext[s * kRecFloats2 + 9 * kCs + lane]);
+        }
+        Acc4 P{0.f, 0.f, 0.f, 0.f, m4}, S{0.f, 0.f, 0.f, 0.f, m2};
+#pragma unroll
+        for (int s = 0; s < kWarps; ++s) {
+            const float* r = ext + s * kRecFloats2 + lane;
+            const float f4 = fast_exp(r[4 * kCs] - m4), f2_ = fast_exp(r[9 * kCs] - m2);
+            P.a += f4 * r[0]; P.b += f4 * r[kCs]; P.ma += f4 * r[2 * kCs]; P.mb += f4 * r[3 * kCs];
+            S.a += f2_ * r[5 * kCs]; S.b += f2_ * r[6 * kCs]; S.ma += f2_ * r[7 * kCs]; S.mb += f2_ * r[8 * kCs];
+        }
+        acc4_decay(P, w, static_cast<float>(warp * kL));
+        acc4_decay(S, w, static_cast<float>((kWarps - 1 - warp) * kL));
+        out.left = merge4(P, in.inP);
+        out.right = merge4(S, in.inS);
+    }
+    return out;
+}
+
+// per-token max-shifted path of the saved-result backward (any exponent range)
+__device__ __noinline__ void rigorous_tile_saved(const Params& p, float* sub, float* ext, int lane, int warp, int tile,
+                                                 int chunk, const Col<float> ks, const Col<float> vs, const Col<float> gs,
+                                                 const Col<float> ys, const Col<float> ls, int n, float w, float u,
+                                                 float& gw_out, float& gu_out) {
+    const float last = static_cast<float>(n - 1);
+    float gg[kL], hh[kL], xo[kL];
+    Acc4 later = acc4_zero(), earlier = acc4_zero();
+    for (int i = 0; i < n; ++i) {
+        gg[i] = gs.ld(i);
+        hh[i] = gg[i] * ys.ld(i);
+        xo[i] = -ls.ld(i);
+    }
+    for (int i = 0; i < n; ++i) acc4_absorb(later, xo[i] + w * static_cast<float>(i), gg[i], hh[i]);
+    for (int i = n - 1; i >= 0; --i) acc4_absorb(earlier, xo[i] - w * static_cast<float>(i), gg[i], hh[i]);
+    later.o -= w * static_cast<float>(n);
+    acc4_decay(later, w, static_cast<float>(kL - n));
+    earlier.o -= w;
+    const Inside4 in = exchange_publish4(p, sub, lane, warp, w, tile, later, earlier);
+    const Entering4 e = exchange_collect4(p, ext, lane, warp, w, tile, chunk, in);
+    Acc4 R = e.left;                                 // anchored at token 0
+    Acc4 Q = e.right;
+    acc4_decay(Q, w, static_cast<float>(kL - n));   // anchored at token n-1
+    float gw = 0.f, gu = 0.f;
+    float pk[kL], pv[kL];
+    for (int i = n - 1; i >= 0; --i) {
+        const float d = last - static_cast<float>(i);
+        const float k = ks.ld(i), v = vs.ld(i);
+        const float ex = wkv_exp(k + Q.o - w * d);
+        pv[i] = ex * Q.a;
+        pk[i] = ex * (Q.a * v - Q.b);
+        gw -= ex * (Q.ma * v - Q.mb);
+        acc4_absorb(Q, xo[i] + w * d, gg[i], hh[i]);
+    }
+    for (int i = 0; i < n; ++i) {
+        const float k = ks.ld(i), v = vs.ld(i), d = static_cast<float>(i);
+        const float ex = wkv_exp(k + R.o - w * d);
+        const float es = wkv_exp(u + k + xo[i]);
+        const float self = es * (v * gg[i] - hh[i]);
+        vs.st(i, pv[i] + ex * R.a + es * gg[i]);
+        ks.st(i, pk[i] + ex * (R.a * v - R.b) + self);
+        gu += self;
+        gw -= ex * (R.ma * v - R.mb);
+        acc4_absorb(R, xo[i] + w * d, gg[i], hh[i]);
+    }
+    gw_out = gw;
+    gu_out = gu;
+}
+
+constexpr int kSavedSlots = 5;     // k, v, gy, y, log Den
+__global__ void __launch_bounds__(kThreads, 2)
+biwkv_backward_saved_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_y,
+                            const __grid_constant__ CUtensorMap map_l, const __grid_constant__ CUtensorMap map_gk,
+                            const __grid_constant__ CUtensorMap map_gv, const Params p) {
+    constexpr uint32_t kSlot = kSlotBytes<float>;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* slots = smem_raw;                                                // [5][kTc][kCs] floats, one stage
+    float* sub = reinterpret_cast<float*>(slots + kSavedSlots * kSlot);            // [kWarps][kRows2][kCs]
+    float* ext = sub + kWarps * kRecFloats2;
+    float* red = sub;
+    uint64_t* full = reinterpret_cast<uint64_t*>(ext + kWarps * kRecFloats2);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(full, 1);
+        sm100::mbar_init_fence();
+    }
+    __syncthreads();
+    auto issue_loads = [&](int tile) {
+        const TileCoord tc = decode_tile(p, tile);
+        const int x = tc.strip * kCs, y = tc.chunk * kTc;
+        sm100::mbar_expect_tx(full, kSavedSlots * kSlot);
+        sm100::tma_load_3d(slots + 0 * kSlot, &map_k, full, x, y, tc.b);
+        sm100::tma_load_3d(slots + 1 * kSlot, &map_v, full, x, y, tc.b);
+        sm100::tma_load_3d(slots + 2 * kSlot, &map_g, full, x, y, tc.b);
+        sm100::tma_load_3d(slots + 3 * kSlot, &map_y, full, x, y, tc.b);
+        sm100::tma_load_3d(slots + 4 * kSlot, &map_l, full, x, y, tc.b);
+    };
+    if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < p.n_tiles) issue_loads(blockIdx.x);
+
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+        const TileCoord tc = decode_tile(p, tile);
+        const int c = tc.strip * kCs + lane;
+        const float w = (c < p.C) ? p.w[c] : 0.f;
+        const float u = (c < p.C) ? p.u[c] : 0.f;
+        if (!sm100::mbar_wait(full, it & 1, kSpinLimit)) atomicOr(p.status, 2u);
+        const int t0 = tc.chunk * kTc + warp * kL;
+        const int n = max(0, min(kL, p.T - t0));
+        const Col<float> ks(slots, warp, lane), vs(slots + kSlot, warp, lane), gs(slots + 2 * kSlot, warp, lane);
+        const Col<float> ys(slots + 3 * kSlot, warp, lane), ls(slots + 4 * kSlot, warp, lane);
+        float gw = 0.f, gu = 0.f;
+
+        float kk[kL], vv[kL];
+        float mk = kMinExp, mnk = 1e38f, X = kMinExp, mnx = 1e38f;
+#pragma unroll
+        for (int i = 0; i < kL; ++i) {
+            kk[i] = ks.ld(i);
+            vv[i] = vs.ld(i);
+            const float xl = -ls.ld(i);
+            if (i < n) {
+                mk = wkv_max(mk, kk[i]); mnk = fminf(mnk, kk[i]);
+                X = wkv_max(X, xl); mnx = fminf(mnx, xl);
+            }
+        }
+        const bool safe = (n == 0) || ((mk - mnk) + (X - mnx) + fabsf(w) * kL + fabsf(u) <= kFastRange);
+        if (!__all_sync(0xffffffffu, safe)) {
+            rigorous_tile_saved(p, sub, ext, lane, warp, tile, tc.chunk, ks, vs, gs, ys, ls, n, w, u, gw, gu);
+        } else {
+            const float lam = fast_exp(-w);
+            const float2 lam2 = f2(lam, lam);
+            const float eu = fast_exp(u);
+            // ---- G' = gy e^{-log Den - X}, H' = G' y (scale e^{X}); aggregates with first moments both ways ----
+            float hh[kL];
+            float2 r = f2(0.f, 0.f), mr = f2(0.f, 0.f), q = f2(0.f, 0.f), mq = f2(0.f, 0.f);
+            float mu = lam;
+#pragma unroll
+            for (int i = 0; i < kL; ++i) {
+                const float g = (i < n) ? gs.ld(i) * fast_exp(-ls.ld(i) - X) : 0.f;
+                const float h = g * ys.ld(i);
+                gs.st(i, g);
+                hh[i] = (i < n) ? h : 0.f;
+                const float2 gh = f2(g, hh[i]);
+                r = mul2(add2(r, gh), lam2);
+                mr = fma2(mr, lam2, r);
+                q = fma2(gh, f2(mu, mu), q);
+                const float mw = mu * static_cast<float>(i + 1);
+                mq = fma2(gh, f2(mw, mw), mq);
+                mu *= lam;
+            }
+            const Inside4 in = exchange_publish4(p, sub, lane, warp, w, tile, Acc4{r.x, r.y, mr.x, mr.y, X},
+                                                 Acc4{q.x, q.y, mq.x, mq.y, X});
+            const Entering4 e = exchange_collect4(p, ext, lane, warp, w, tile, tc.chunk, in);
+            const Acc4 cr = e.left, cq = e.right;
+            // adjoint values live in scale e^{N}; inputs re-enter as e^{k + N}
+            const float N = wkv_max(X, wkv_max(cr.o, cq.o));
+            const float fl = fast_exp(X - N), fr = fast_exp(cr.o - N), fq = fast_exp(cq.o - N);
+            float2 qq = f2(cq.a * fq, cq.b * fq), mqq = f2(cq.ma * fq, cq.mb * fq);
+            float2 rr = f2(cr.a * fr, cr.b * fr), mrr = f2(cr.ma * fr, cr.mb * fr);
+            const float2 fl2 = f2(fl, fl);
+            float2 part[kL];
+#pragma unroll
+            for (int i = kL - 1; i >= 0; --i) {
+                const float ex = (i < n) ? fast_exp(kk[i] + N) : 0.f;
+                part[i] = f2(ex * (qq.x * vv[i] - qq.y), ex * qq.x);          // (gk, gv) from later outputs
+                gw -= ex * (mqq.x * vv[i] - mqq.y);
+                qq = mul2(fma2(f2(gs.ld(i), hh[i]), fl2, qq), lam2);
+                mqq = fma2(mqq, lam2, qq);
+            }
+            const float euf = eu * fl;
+#pragma unroll
+            for (int i = 0; i < kL; ++i) {
+                const float ex = (i < n) ? fast_exp(kk[i] + N) : 0.f;
+                const float g = gs.ld(i), h = hh[i];
+                const float ev = ex * vv[i];
+                const float self = euf * (ev * g - ex * h);
+                ks.st(i, part[i].x + (ev * rr.x - ex * rr.y) + self);
+                vs.st(i, part[i].y + ex * rr.x + euf * ex * g);
+                gu += self;
+                gw -= ev * mrr.x - ex * mrr.y;
+                rr = mul2(fma2(f2(g, h), fl2, rr), lam2);
+                mrr = fma2(mrr, lam2, rr);
+            }
+        }
+        red[(warp * 2 + 0) * kCs + lane] = gw;
+        red[(warp * 2 + 1) * kCs + lane] = gu;
+        __syncthreads();
+        if (warp < 2) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < kWarps; ++s) acc += red[(s * 2 + warp) * kCs + lane];
+            p.partial[(static_cast<size_t>(tile) * 2 + warp) * kCs + lane] = acc;
+        }
+        sm100::fence_proxy_async_smem();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            sm100::tma_store_3d(&map_gk, slots, tc.strip * kCs, tc.chunk * kTc, tc.b);
+            sm100::tma_store_3d(&map_gv, slots + kSlot, tc.strip * kCs, tc.chunk * kTc, tc.b);
+            sm100::tma_store_commit();
+            const int next = tile + gridDim.x;
+            if (next < p.n_tiles) {
+                sm100::tma_store_wait_read();        // one stage: the outputs must have left before the next tile lands
+                issue_loads(next);
+            }
+        }
     }
     if (threadIdx.x == 0) sm100::tma_store_wait_all();
 }
@@ -907,9 +1291,9 @@ template <typename E>
 static bool configure_kernels(int (&resident)[2]) {
     bool good = cudaFuncSetAttribute(biwkv_fused_kernel<true, E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem_bytes<true, E>())) == cudaSuccess;
-    good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    good = good && cudaFuncSetAttribute(biwkv_forward_pipelined_kernel<E, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(fwd_pipelined_smem_bytes<E>())) == cudaSuccess;
-    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident[0], biwkv_forward_pipelined_kernel<E>,
+    good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident[0], biwkv_forward_pipelined_kernel<E, false>,
                                                                  kThreads, fwd_pipelined_smem_bytes<E>()) == cudaSuccess;
     good = good && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident[1], biwkv_fused_kernel<true, E>, kThreads,
                                                                  smem_bytes<true, E>()) == cudaSuccess;
@@ -992,7 +1376,8 @@ static int launch(Layout& l, const float* w, const float* u, const E* k, const E
     CUtensorMap mk, mv, mg, m0, m1;
     bool ok = make_map<E>(&mk, k, p.B, p.T, p.C) && make_map<E>(&mv, v, p.B, p.T, p.C) &&
               make_map<E>(&m0, o0, p.B, p.T, p.C);
-    ok = ok && make_map<E>(&mg, kBwd ? gy : k, p.B, p.T, p.C) && make_map<E>(&m1, kBwd ? o1 : o0, p.B, p.T, p.C);
+    ok = ok && make_map<E>(&mg, kBwd ? gy : k, p.B, p.T, p.C) &&
+         make_map<E>(&m1, (kBwd || o1 != nullptr) ? o1 : o0, p.B, p.T, p.C);
     if (!ok) {
         set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
         return -1;
@@ -1002,12 +1387,24 @@ static int launch(Layout& l, const float* w, const float* u, const E* k, const E
     const DeviceInfo& d = device_info();
     const int grid = std::min(p.n_tiles, d.sms * d.resident[std::is_same<E, float>::value ? 0 : 1][kBwd ? 1 : 0]);
     void* args[] = {&mk, &mv, &mg, &m0, &m1, &p};
-    void* fwd_args[] = {&mk, &mv, &m0, &p};
+    void* fwd_args[] = {&mk, &mv, &m0, &m1, &p};
+    void* fwd_kernel = reinterpret_cast<void*>(biwkv_forward_pipelined_kernel<E, false>);
+    if constexpr (std::is_same<E, float>::value) {
+        if (!kBwd && o1 != nullptr) {                 // forward that also writes log Den into o1
+            static bool configured = false;
+            if (!configured) {
+                cudaFuncSetAttribute(biwkv_forward_pipelined_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(fwd_pipelined_smem_bytes<float>()));
+                configured = true;
+            }
+            fwd_kernel = reinterpret_cast<void*>(biwkv_forward_pipelined_kernel<float, true>);
+        }
+    }
     const cudaError_t err =
         kBwd ? cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_fused_kernel<true, E>), dim3(grid),
                                            dim3(kThreads), args, smem_bytes<true, E>(), stream)
-             : cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_forward_pipelined_kernel<E>), dim3(grid),
-                                           dim3(kThreads), fwd_args, fwd_pipelined_smem_bytes<E>(), stream);
+             : cudaLaunchCooperativeKernel(fwd_kernel, dim3(grid), dim3(kThreads), fwd_args,
+                                           fwd_pipelined_smem_bytes<E>(), stream);
     if (err != cudaSuccess) {
         set_error_detail(cudaGetErrorName(err));
         return -1;
@@ -1030,6 +1427,79 @@ int backward(int B, int T, int C, const float* w, const float* u, const float* k
              const float* gy, float* gwgu, float* gk, float* gv, void* workspace, cudaStream_t stream) {
     Layout l = make_layout(B, T, C, true);
     return launch<true, float>(l, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+}
+
+static constexpr size_t saved_smem_bytes() {
+    return kSavedSlots * kSlotBytes<float> + 2 * kWarps * kRecFloats2 * sizeof(float) + 64;
+}
+
+// CTAs of the saved-result backward that fit one SM (0: the kernel cannot run here)
+static int saved_resident() {
+    static int cached[64];
+    static bool known[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!known[dev]) {
+        int n = 0;
+        if (cudaFuncSetAttribute(biwkv_backward_saved_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(saved_smem_bytes())) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, biwkv_backward_saved_kernel, kThreads,
+                                                          saved_smem_bytes()) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        cached[dev] = n;
+        known[dev] = true;
+    }
+    return cached[dev];
+}
+
+bool eligible_saved(int B, int T, int C, std::initializer_list<const void*> ptrs) {
+    if (!eligible(B, T, C, ptrs, false)) return false;
+    const int res = saved_resident();
+    if (res <= 0) return false;
+    const int n_chunks = (T + kTc - 1) / kTc;
+    return static_cast<long long>(n_chunks) * pick_interleave((C + kCs - 1) / kCs) < static_cast<long long>(device_info().sms) * res;
+}
+
+int backward_saved(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+                   const float* gy, const float* y, const float* logden, float* gwgu, float* gk, float* gv,
+                   void* workspace, cudaStream_t stream) {
+    Layout l = make_layout(B, T, C, true);       // sized for two 8-row levels: more than one 10-row level needs
+    Params& p = l.p;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    p.w = w; p.u = u;
+    p.status = reinterpret_cast<unsigned*>(ws + l.off_status);
+    p.flags = reinterpret_cast<unsigned*>(ws + l.off_flags);
+    p.exch = reinterpret_cast<float*>(ws + l.off_exch);
+    p.partial = reinterpret_cast<float*>(ws + l.off_partial);
+    cudaFree(nullptr);
+    CUtensorMap mk, mv, mg, my, ml, m0, m1;
+    const bool ok = make_map<float>(&mk, k, B, T, C) && make_map<float>(&mv, v, B, T, C) && make_map<float>(&mg, gy, B, T, C) &&
+                    make_map<float>(&my, y, B, T, C) && make_map<float>(&ml, logden, B, T, C) &&
+                    make_map<float>(&m0, gk, B, T, C) && make_map<float>(&m1, gv, B, T, C);
+    if (!ok) {
+        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
+        return -1;
+    }
+    cudaMemsetAsync(ws, 0, l.off_exch, stream);
+    const int grid = std::min(p.n_tiles, device_info().sms * saved_resident());
+    void* args[] = {&mk, &mv, &mg, &my, &ml, &m0, &m1, &p};
+    const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(biwkv_backward_saved_kernel), dim3(grid),
+                                                        dim3(kThreads), args, saved_smem_bytes(), stream);
+    if (err != cudaSuccess) {
+        set_error_detail(cudaGetErrorName(err));
+        return -1;
+    }
+    reduce_tile_partials<<<dim3(p.n_strips, 2), dim3(32, 32), 0, stream>>>(p, gwgu);
+    return 2;
+}
+
+int forward_save(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
+                 float* logden, void* workspace, cudaStream_t stream) {
+    Layout l = make_layout(B, T, C, false);
+    return launch<false, float>(l, w, u, k, v, nullptr, y, logden, nullptr, workspace, stream);
 }
 
 int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,

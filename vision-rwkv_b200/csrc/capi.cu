@@ -55,7 +55,7 @@ const char* vrwkv_status_string(int status) {
         case VRWKV_ERR_LAUNCH: return "CUDA reported an error after a kernel launch";
         case VRWKV_ERR_DEVICE: return "required driver entry point or device attribute unavailable";
         case VRWKV_ERR_HEAD_SIZE: return "WKV6 requires C == 64 * H";
-        case VRWKV_ERR_UNSUPPORTED: return "shape or alignment not covered by the bf16 kernels; use the f32 entry points";
+        case VRWKV_ERR_UNSUPPORTED: return "shape or alignment not covered by this entry point's kernels; use the plain f32 entry points";
         default: return "unknown status";
     }
 }
@@ -123,6 +123,31 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
     cudaMemsetAsync(workspace, 0, 256, s);
     return finish(biwkv::generic_backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv,
                                           static_cast<char*>(workspace) + 256, s));
+}
+
+int vrwkv_biwkv_forward_save_f32(int B, int T, int C, const float* w, const float* u, const float* k,
+                                 const float* v, float* y, float* logden, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+    if (int st = check_shape(B, T, C)) return st;
+    if (!w || !u || !k || !v || !y || !logden || !workspace) return VRWKV_ERR_NULL;
+    if (misaligned4(w) || misaligned4(u) || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return VRWKV_ERR_ALIGNMENT;
+    if (workspace_bytes < vrwkv_biwkv_forward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
+    if (!biwkv::fused::eligible(B, T, C, {k, v, y, logden})) return VRWKV_ERR_UNSUPPORTED;
+    return finish(biwkv::fused::forward_save(B, T, C, w, u, k, v, y, logden, workspace, static_cast<cudaStream_t>(stream)));
+}
+
+int vrwkv_biwkv_backward_saved_f32(int B, int T, int C, const float* w, const float* u, const float* k,
+                                   const float* v, const float* gy, const float* y, const float* logden,
+                                   float* gwgu, float* gk, float* gv, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+    if (int st = check_shape(B, T, C)) return st;
+    if (!w || !u || !k || !v || !gy || !y || !logden || !gwgu || !gk || !gv || !workspace) return VRWKV_ERR_NULL;
+    if (misaligned4(w) || misaligned4(u) || misaligned4(gwgu) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return VRWKV_ERR_ALIGNMENT;
+    if (workspace_bytes < vrwkv_biwkv_backward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
+    if (!biwkv::fused::eligible_saved(B, T, C, {k, v, gy, y, logden, gk, gv})) return VRWKV_ERR_UNSUPPORTED;
+    return finish(biwkv::fused::backward_saved(B, T, C, w, u, k, v, gy, y, logden, gwgu, gk, gv, workspace,
+                                               static_cast<cudaStream_t>(stream)));
 }
 
 int vrwkv_biwkv_forward_bf16(int B, int T, int C, const float* w, const float* u, const uint16_t* k,

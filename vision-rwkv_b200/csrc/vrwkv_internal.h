@@ -27,6 +27,14 @@ int forward(int B, int T, int C, const float* w, const float* u, const float* k,
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
              const float* gy, float* gwgu, float* gk, float* gv, void* workspace,
              cudaStream_t stream);
+// Forward that also writes log Den (one float per element), and the backward that starts from the
+// saved y and log Den: one exchange level instead of two.
+bool eligible_saved(int B, int T, int C, std::initializer_list<const void*> ptrs);
+int forward_save(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
+                 float* logden, void* workspace, cudaStream_t stream);
+int backward_saved(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+                   const float* gy, const float* y, const float* logden, float* gwgu, float* gk, float* gv,
+                   void* workspace, cudaStream_t stream);
 // k, v, y, gy, gk, gv hold bfloat16; w, u, gwgu stay float; arithmetic is the float kernels'.
 int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
                  void* workspace, cudaStream_t stream);

@@ -20,13 +20,15 @@ class WKV(torch.autograd.Function):
         if tuple(k.shape) != (B, T, C):
             raise RuntimeError(f"k has shape {tuple(k.shape)}, expected {(B, T, C)}")
         ctx.B, ctx.T, ctx.C = B, T, C
-        ctx.save_for_backward(w, u, k, v)
-        return biwkv_forward_as_reference(w, u, k, v)
+        keep = [] if any(ctx.needs_input_grad) else None
+        y = biwkv_forward_as_reference(w, u, k, v, keep)
+        ctx.save_for_backward(w, u, k, v, *(keep or ()))
+        return y
 
     @staticmethod
     def backward(ctx, gy):
-        w, u, k, v = ctx.saved_tensors
-        return (None, None, None) + tuple(biwkv_backward_as_reference(w, u, k, v, gy))
+        w, u, k, v, *kept = ctx.saved_tensors
+        return (None, None, None) + tuple(biwkv_backward_as_reference(w, u, k, v, gy, kept))
 
 
 def RUN_CUDA(B, T, C, w, u, k, v):

@@ -103,6 +103,58 @@ def biwkv_forward(w, u, k, v):
     return y
 
 
+def biwkv_forward_save(w, u, k, v):
+    """(y, logden): the forward that also keeps log Den_t for `biwkv_backward_saved`; float32 only.
+    Returns (y, None) when the single-pass kernels do not cover the call (odd channel count,
+    unaligned view, ...): the caller then uses the recomputing backward."""
+    dev = _check_inputs((("w", w), ("u", u), ("k", k), ("v", v)))
+    B, T, C = _biwkv_shapes(w, u, k, v)
+    lib = _lib.load()
+    y = torch.empty_like(k)
+    if k.numel() == 0:
+        return y, None
+    logden = torch.empty_like(k)
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_biwkv_forward_workspace_bytes(B, T, C), dev)
+        st = lib.vrwkv_biwkv_forward_save_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                              y.data_ptr(), logden.data_ptr(), ws.data_ptr(), ws.numel(),
+                                              torch.cuda.current_stream().cuda_stream)
+        if st == UNSUPPORTED:
+            return biwkv_forward(w, u, k, v), None
+        _lib.check(st, "vrwkv_biwkv_forward_save_f32")
+        _check_status(lib, ws, "vrwkv_biwkv_forward_save_f32")
+    return y, logden
+
+
+def biwkv_backward_saved(w, u, k, v, gy, y, logden, gwgu_out=None):
+    """(gw, gu, gk, gv) from the results `biwkv_forward_save` kept: one cross-tile exchange instead of two."""
+    dev = _check_inputs((("w", w), ("u", u), ("k", k), ("v", v), ("gy", gy), ("y", y), ("logden", logden)))
+    B, T, C = _biwkv_shapes(w, u, k, v, gy)
+    if y.shape != k.shape or logden.shape != k.shape:
+        raise RuntimeError("y and logden must have the shape of k")
+    lib = _lib.load()
+    gk = torch.empty_like(k)
+    gv = torch.empty_like(k)
+    if gwgu_out is None:
+        gwgu = torch.empty((2, C), dtype=torch.float32, device=dev)
+    else:
+        _check_inputs((("gwgu_out", gwgu_out),))
+        if gwgu_out.numel() != 2 * C:
+            raise RuntimeError("gwgu_out must hold 2*C values")
+        gwgu = gwgu_out.view(2, C)
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_biwkv_backward_workspace_bytes(B, T, C), dev)
+        st = lib.vrwkv_biwkv_backward_saved_f32(B, T, C, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                gy.data_ptr(), y.data_ptr(), logden.data_ptr(), gwgu.data_ptr(),
+                                                gk.data_ptr(), gv.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                torch.cuda.current_stream().cuda_stream)
+        if st == UNSUPPORTED:
+            return biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu_out)
+        _lib.check(st, "vrwkv_biwkv_backward_saved_f32")
+        _check_status(lib, ws, "vrwkv_biwkv_backward_saved_f32")
+    return gwgu[0], gwgu[1], gk, gv
+
+
 def biwkv_backward(w, u, k, v, gy, gwgu_out=None):
     """(gw, gu, gk, gv).  gw and gu are views of one (2, C) buffer, so a data-parallel
     caller can all-reduce both with a single collective; pass `gwgu_out` to have them
