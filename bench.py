@@ -263,6 +263,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--recompute", action="store_true",
+                    help="time the forward/backward pair that keeps nothing between the two calls")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunk", type=int, default=4, help="sequences per pipelined chunk of the host-buffer call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -313,9 +315,22 @@ def main():
     gwgu = torch.empty(2, C, device=dev)
     reducer = GradAllReducer()
 
+    # The training step as the autograd surface runs it by default: the forward keeps log Den next to y,
+    # the backward starts from both (--recompute: the pair that keeps nothing and rebuilds them).
+    def forward_step():
+        if args.recompute:
+            return ops.biwkv_forward(w, u, k, v), None
+        return ops.biwkv_forward_save(w, u, k, v)
+
+    def backward_step(y, logden):
+        if logden is None:
+            ops.biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu)
+        else:
+            ops.biwkv_backward_saved(w, u, k, v, gy, y, logden, gwgu_out=gwgu)
+
     def step():
-        y = ops.biwkv_forward(w, u, k, v)
-        ops.biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu)
+        y, logden = forward_step()
+        backward_step(y, logden)
         if world > 1:
             reducer.launch(gwgu)
             reducer.wait()
@@ -345,9 +360,9 @@ def main():
     for i in range(args.steps):
         a, b, c = fwd_ev[i]
         a.record()
-        ops.biwkv_forward(w, u, k, v)
+        y_i, logden_i = forward_step()
         b.record()
-        ops.biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu)
+        backward_step(y_i, logden_i)
         c.record()
         if world > 1:
             reducer.launch(gwgu)
@@ -444,6 +459,8 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"biwkv_fwd_bwd B={B}/gpu T={T} C={C} fp32",
+                   "backward": "recomputes y and Den" if args.recompute else
+                               "starts from the y and log Den the forward kept (4 more bytes per element written, 8 read)",
                    "global_batch": B * world, "parallelism": f"batch-sharded x{world}",
                    "collective": "one all-reduce of gw|gu (2,C) per step" if world > 1 else "none",
                    "l2": "inputs (2.4 GB per pass) exceed the 126 MB L2; no explicit flush"},
