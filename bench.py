@@ -436,7 +436,13 @@ def main():
     fwd_gbs = BYTES_FWD * E / (fwd_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "biwkv backward (all launches of one backward call)",
                 "achieved": bwd_gbs, "peak": peak, "peak_source": f"{peak_kind} copy bandwidth",
-                "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": None,
+                "unit": "GB/s", "frac": bwd_gbs / peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel from the ncu capture at B=8
+                # (profiles/), scaled to this launch by its element count: the traffic is proportional to it
+                "traffic": (480.0e6 if args.recompute else 694.5e6) * E / (8 * 4096 * 768),
+                "traffic_source": "ncu at B=8,T=4096,C=768 scaled by elements: "
+                                  + ("profiles/biwkv_fused_b8_t4096_c768.md" if args.recompute
+                                     else "profiles/biwkv_saved_b8_t4096_c768.md"),
                 "algorithmic_bytes_per_launch": BYTES_BWD * E, "ms_per_launch": bwd_ms,
                 "forward": {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "ms": fwd_ms,
                             "algorithmic_bytes": BYTES_FWD * E},
