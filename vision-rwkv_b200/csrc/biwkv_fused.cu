@@ -67,12 +67,32 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kFastRange = 60.f;
 constexpr uint32_t kSpinLimit = 1u << 20;   // ~0.1 s of polling
 
+// Division of a non-negative 31-bit number by a launch constant: q = (n * mul) >> shift with
+// mul = ceil(2^shift / d), shift = 31 + ceil(log2 d) (exact for every n < 2^31).  The tile loops
+// decode their tile id several times per tile; three hardware divisions each were a tenth of the
+// forward's instructions.
+struct FastDiv {
+    uint32_t mul, shift;
+};
+static inline FastDiv make_fastdiv(uint32_t d) {
+    uint32_t s = 0;
+    while ((1u << s) < d) ++s;
+    FastDiv f;
+    f.mul = static_cast<uint32_t>(((1ull << (31 + s)) + d - 1) / d);
+    f.shift = 31 + s;
+    return f;
+}
+__device__ __forceinline__ int fast_div(int n, FastDiv f) {
+    return static_cast<int>((static_cast<uint64_t>(static_cast<uint32_t>(n)) * f.mul) >> f.shift);
+}
+
 struct Params {
     int B, T, C;
     int n_chunks;      // tiles along T
     int n_strips;      // tiles along C
     int interleave;    // strips whose tiles alternate in the id order (divides n_strips)
     int n_tiles;
+    FastDiv by_span, by_interleave, by_strips;
     const float* w;
     const float* u;
     float* exch;       // [n_tiles][levels][kRows][kCs]
@@ -86,12 +106,12 @@ struct TileCoord {
 };
 __device__ __forceinline__ TileCoord decode_tile(const Params& p, int id) {
     const int span = p.interleave * p.n_chunks;
-    const int block = id / span;
+    const int block = fast_div(id, p.by_span);
     const int r = id - block * span;
-    const int chunk = r / p.interleave;
+    const int chunk = fast_div(r, p.by_interleave);
     const int gs = block * p.interleave + (r - chunk * p.interleave);   // strip index over all sequences
     TileCoord t;
-    t.b = gs / p.n_strips;
+    t.b = fast_div(gs, p.by_strips);
     t.strip = gs - t.b * p.n_strips;
     t.chunk = chunk;
     return t;
@@ -1336,6 +1356,9 @@ static Layout make_layout(int B, int T, int C, bool bwd) {
     p.n_strips = (C + kCs - 1) / kCs;
     p.interleave = pick_interleave(p.n_strips);
     p.n_tiles = B * p.n_strips * p.n_chunks;
+    p.by_span = make_fastdiv(static_cast<uint32_t>(p.interleave * p.n_chunks));
+    p.by_interleave = make_fastdiv(static_cast<uint32_t>(p.interleave));
+    p.by_strips = make_fastdiv(static_cast<uint32_t>(p.n_strips));
     const int levels = bwd ? 2 : 1;
     l.off_status = 0;
     l.off_flags = 256;
