@@ -166,6 +166,13 @@ int vrwkv_wkv6_forward_f32(int B, int T, int C, int H, const float* r, const flo
 int vrwkv_wkv6_forward_tc_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
                               const float* w_raw, const float* u, float* y, void* workspace,
                               size_t workspace_bytes, void* stream);
+/* The same kernel for callers whose r, k, v are bfloat16 (uint16_t bit patterns; the usual case
+ * under autocast): the tiles are read as bfloat16, so the `.float()` passes in front of the
+ * reference's call (CLS/vrwkv6.py:220 hands whatever dtype the projections produced to a kernel
+ * that reads float) disappear.  w_raw, u and y stay float32. */
+int vrwkv_wkv6_forward_tc_bf16(int B, int T, int C, int H, const uint16_t* r, const uint16_t* k,
+                               const uint16_t* v, const float* w_raw, const float* u, float* y,
+                               void* workspace, size_t workspace_bytes, void* stream);
 
 /* vrwkv_wkv6_backward_f32 replaces
  *   cuda_backward(int B,int T,int C,int H,float*r,...,float*gy,float*gr,float*gk,float*gv,

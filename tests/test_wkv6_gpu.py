@@ -231,7 +231,7 @@ def test_autograd_picks_tensor_cores_for_half_inputs(cuda_device, monkeypatch):
     from vision_rwkv_b200 import ops, vrwkv6
     seen = []
     real = ops.wkv6_forward
-    monkeypatch.setattr(ops, "wkv6_forward", lambda *a, **kw: (seen.append(kw.get("tensor_cores")), real(*a, **kw))[1])
+    monkeypatch.setattr(ops, "wkv6_forward", lambda *a, **kw: (seen.append(bool(kw.get("tensor_cores"))), real(*a, **kw))[1])
     B, T, H = 1, 48, 1
     r, k, v, w, u, _ = O.make_inputs(B, T, 64, H, seed=2, round_to=torch.bfloat16)
     dev = cuda_device
@@ -240,3 +240,36 @@ def test_autograd_picks_tensor_cores_for_half_inputs(cuda_device, monkeypatch):
     monkeypatch.setattr(vrwkv6, "FORWARD_PATH", "exact")
     vrwkv6.RUN_CUDA_RWKV6(B, T, 64, H, *[x.bfloat16().to(dev) for x in (r, k, v)], w.float().to(dev), u.float().to(dev))
     assert seen == [False, True, False]
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 1, 1), (2, 15, 1), (1, 17, 2), (2, 37, 2), (3, 196, 2), (1, 300, 1), (1, 1024, 1)])
+def test_tensor_core_forward_reads_bfloat16_inputs(cuda_device, B, T, H):
+    """r, k, v handed over in bfloat16 (w, u float32): same numbers as widening them first."""
+    from vision_rwkv_b200 import ops
+    ops.CHECK_STATUS = True
+    try:
+        r, k, v, w, u, _ = O.make_inputs(B, T, 64 * H, H, seed=T + 1, round_to=torch.bfloat16)
+        dev = cuda_device
+        half = [x.bfloat16().contiguous().to(dev) for x in (r, k, v)]
+        wf, uf = w.float().contiguous().to(dev), u.float().contiguous().to(dev)
+        y16 = ops.wkv6_forward(*half, wf, uf, H, tensor_cores=True)
+        y32 = ops.wkv6_forward(*[x.float() for x in half], wf, uf, H, tensor_cores=True)
+        torch.cuda.synchronize()
+    finally:
+        ops.CHECK_STATUS = False
+    ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
+    assert rel_err(y16, ref) <= TC_TOL
+    assert torch.equal(y16, y32)          # the inputs were bfloat16 values either way: identical arithmetic
+
+
+def test_tensor_core_bfloat16_strong_decay(cuda_device):
+    from vision_rwkv_b200 import ops
+    B, T, H = 2, 100, 2
+    r, k, v, w, u, _ = O.make_inputs(B, T, 64 * H, H, seed=11, round_to=torch.bfloat16)
+    w = w.clone()
+    w[..., :64] += 2.6
+    dev = cuda_device
+    y = ops.wkv6_forward(*[x.bfloat16().contiguous().to(dev) for x in (r, k, v)], w.float().contiguous().to(dev),
+                         u.float().contiguous().to(dev), H, tensor_cores=True)
+    ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
+    assert rel_err(y, ref) <= TC_TOL

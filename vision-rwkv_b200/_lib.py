@@ -33,6 +33,7 @@ SIGNATURES = {
     "vrwkv_biwkv_forward_f32_noalloc": (_c_int, [_c_int] * 3 + [_ptr] * 6),
     "vrwkv_wkv6_forward_f32": (_c_int, [_c_int] * 4 + [_ptr] * 7),
     "vrwkv_wkv6_forward_tc_f32": (_c_int, [_c_int] * 4 + [_ptr] * 7 + [_c_size_t, _ptr]),
+    "vrwkv_wkv6_forward_tc_bf16": (_c_int, [_c_int] * 4 + [_ptr] * 7 + [_c_size_t, _ptr]),
     "vrwkv_wkv6_backward_workspace_bytes": (_c_size_t, [_c_int] * 4),
     "vrwkv_wkv6_backward_f32": (_c_int, [_c_int] * 4 + [_ptr] * 12 + [_c_size_t, _ptr]),
     "vrwkv_qshift_mix_forward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 4),

@@ -211,6 +211,19 @@ int vrwkv_wkv6_forward_tc_f32(int B, int T, int C, int H, const float* r, const 
                                   g_path.load() != 1, static_cast<cudaStream_t>(stream)));
 }
 
+int vrwkv_wkv6_forward_tc_bf16(int B, int T, int C, int H, const uint16_t* r, const uint16_t* k,
+                               const uint16_t* v, const float* w_raw, const float* u, float* y,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (int st = check_wkv6(B, T, C, H)) return st;
+    if (!r || !k || !v || !w_raw || !u || !y || !workspace) return VRWKV_ERR_NULL;
+    if (misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(w_raw) || misaligned4(u) ||
+        misaligned16(y) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return VRWKV_ERR_ALIGNMENT;
+    if (workspace_bytes < 256) return VRWKV_ERR_WORKSPACE;
+    return finish(wkv6tc::forward_bf16in(B, T, H, r, k, v, w_raw, u, y, static_cast<unsigned*>(workspace),
+                                         static_cast<cudaStream_t>(stream)));
+}
+
 int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
                             const float* w_raw, const float* u, const float* gy, float* gr, float* gk,
                             float* gv, float* gw, float* gu, void* workspace, size_t workspace_bytes,

@@ -57,4 +57,7 @@ namespace wkv6tc {
 // pipelined = false runs the first-generation kernel (all warps do every phase in turn).
 int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw,
             const float* u, float* y, unsigned* status, bool pipelined, cudaStream_t stream);
+// r, k, v in bfloat16 (read as such by the kernel: no widening pass), w_raw, u, y float32.
+int forward_bf16in(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw,
+                   const float* u, float* y, unsigned* status, cudaStream_t stream);
 }  // namespace wkv6tc

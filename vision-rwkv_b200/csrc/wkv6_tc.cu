@@ -492,6 +492,24 @@ __device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&x)[8])
                  : "r"(taddr));
 }
 
+// r, k, v staging tiles hold float32 or, for callers whose activations are bfloat16, bfloat16 in the
+// first half of the same space (w stays float32).  bfloat16 elements are read as the 32-bit word
+// of a channel pair, never as 2-byte accesses.
+template <bool kHalfIn>
+__device__ __forceinline__ float4 raw_ld4(const float* tile, int row, int c0) {
+    if (!kHalfIn) return *reinterpret_cast<const float4*>(tile + row * N + c0);
+    const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(tile) + row * N + c0);
+    return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                       __uint_as_float(w.y & 0xffff0000u));
+}
+template <bool kHalfIn>
+__device__ __forceinline__ float raw_ld1(const float* tile, int row, int c) {
+    if (!kHalfIn) return tile[row * N + c];
+    const uint32_t word = reinterpret_cast<const uint32_t*>(tile)[(row * N + c) >> 1];
+    return __uint_as_float((c & 1) ? (word & 0xffff0000u) : (word << 16));
+}
+
+template <bool kHalfIn>
 __global__ void __launch_bounds__(kPThreads, 2)
 wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
@@ -578,8 +596,8 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
             // ---- job 1: thread = (token t, 4 key channels): Rs, Kb, bonus ----
             {
                 const int t = pid >> 4, c0 = (pid & 15) * 4, row = row_of(t);
-                const float4 rv = *reinterpret_cast<const float4*>(&raw[0][row][c0]);
-                const float4 kv = *reinterpret_cast<const float4*>(&raw[1][row][c0]);
+                const float4 rv = raw_ld4<kHalfIn>(&raw[0][0][0], row, c0);
+                const float4 kv = raw_ld4<kHalfIn>(&raw[1][0][0], row, c0);
                 const float4 at = *reinterpret_cast<const float4*>(&s.acum[t][c0]);
                 const float4 at1 = *reinterpret_cast<const float4*>(&s.acum[t + 1][c0]);
                 const float4 aA = *reinterpret_cast<const float4*>(&s.acum[SC][c0]);
@@ -617,8 +635,8 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
                 for (int j = 0; j < 4; ++j) {
                     const int t = quarter * 4 + j, row = row_of(t);
                     a1[j] = s.acum[t + 1][c];
-                    kh[j] = raw[1][row][c];
-                    vv[j] = raw[2][row][c];
+                    kh[j] = raw_ld1<kHalfIn>(&raw[1][0][0], row, c);
+                    vv[j] = raw_ld1<kHalfIn>(&raw[2][0][0], row, c);
                 }
                 if (quarter == 0) set.dtot[c] = __expf(A);
 #pragma unroll
@@ -630,12 +648,13 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
             if (pairwise) {
                 // ---- strong decay: the 16 x 16 scores pairwise in fp32, every exponent <= 0 ----
                 const int t = pid >> 4, sidx = pid & 15;
-                const float* rt = raw[0][row_of(t)];
-                const float* ks = raw[1][row_of(sidx)];
+                const int row_t = row_of(t), row_s = row_of(sidx);
                 float acc = 0.f;
                 if (sidx < t) {
 #pragma unroll 8
-                    for (int i = 0; i < N; ++i) acc += rt[i] * ks[i] * __expf(s.acum[t][i] - s.acum[sidx + 1][i]);
+                    for (int i = 0; i < N; ++i)
+                        acc += raw_ld1<kHalfIn>(&raw[0][0][0], row_t, i) * raw_ld1<kHalfIn>(&raw[1][0][0], row_s, i) *
+                               __expf(s.acum[t][i] - s.acum[sidx + 1][i]);
                 } else if (sidx == t) {
                     acc = set.diag[t];
                 }
@@ -661,7 +680,7 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
             for (int step = 0; step < n_steps; ++step) {
                 const int slot = step & 1, y0 = tile_start(step);
                 if (step >= 2) wait_on(&s.raw_free[slot], ((step >> 1) & 1) ^ 1u);
-                sm100::mbar_expect_tx(&s.raw_full[slot], 4 * SC * N * sizeof(float));
+                sm100::mbar_expect_tx(&s.raw_full[slot], (kHalfIn ? 3 * 2 + 4 : 4 * 4) * SC * N);
                 sm100::tma_load_3d(&s.raw[slot][0][0][0], &map_r, &s.raw_full[slot], h * N, y0, b);
                 sm100::tma_load_3d(&s.raw[slot][1][0][0], &map_k, &s.raw_full[slot], h * N, y0, b);
                 sm100::tma_load_3d(&s.raw[slot][2][0][0], &map_v, &s.raw_full[slot], h * N, y0, b);
@@ -806,36 +825,56 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
 }
 
-int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw, const float* u,
-            float* y, unsigned* status, bool pipelined, cudaStream_t stream) {
+static bool configure_once() {
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(wkv6_tc_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(sizeof(Smem))) != cudaSuccess ||
-            cudaFuncSetAttribute(wkv6_tc_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            cudaFuncSetAttribute(wkv6_tc_pipelined_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(SmemP))) != cudaSuccess ||
+            cudaFuncSetAttribute(wkv6_tc_pipelined_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(sizeof(SmemP))) != cudaSuccess)
-            return -1;
+            return false;
         configured = true;
     }
+    return true;
+}
+
+// half_in: r, k, v point at bfloat16; w_raw, u, y are float32 either way
+static int launch(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw, const float* u,
+                  float* y, unsigned* status, bool half_in, bool pipelined, cudaStream_t stream) {
+    if (!configure_once()) return -1;
     cudaFree(nullptr);   // descriptors are encoded against the current context; a fresh thread may not have one bound
     const int C = H * N;
     CUtensorMap mr, mk, mv, mw, my;
-    if (!(tensor_map::make_btc_f32(&mr, r, B, T, C, N, SC) && tensor_map::make_btc_f32(&mk, k, B, T, C, N, SC) &&
-          tensor_map::make_btc_f32(&mv, v, B, T, C, N, SC) && tensor_map::make_btc_f32(&mw, w_raw, B, T, C, N, SC) &&
+    if (!(tensor_map::make_btc(&mr, r, B, T, C, N, SC, half_in) && tensor_map::make_btc(&mk, k, B, T, C, N, SC, half_in) &&
+          tensor_map::make_btc(&mv, v, B, T, C, N, SC, half_in) && tensor_map::make_btc_f32(&mw, w_raw, B, T, C, N, SC) &&
           tensor_map::make_btc_f32(&my, y, B, T, C, N, SC))) {
-        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) fp32 tensor map");
+        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
         return -1;
     }
-    Args a{B, T, H, r, k, v, w_raw, u, y, status};
+    Args a{B, T, H, static_cast<const float*>(r), static_cast<const float*>(k), static_cast<const float*>(v), w_raw, u, y,
+           status};
     cudaMemsetAsync(status, 0, sizeof(unsigned), stream);
-    if (pipelined) {
+    if (pipelined || half_in) {
         // both directions add into y
         cudaMemsetAsync(y, 0, static_cast<size_t>(B) * T * C * sizeof(float), stream);
-        wkv6_tc_pipelined_kernel<<<2 * B * H, kPThreads, sizeof(SmemP), stream>>>(a, mr, mk, mv, mw, my);
+        if (half_in) wkv6_tc_pipelined_kernel<true><<<2 * B * H, kPThreads, sizeof(SmemP), stream>>>(a, mr, mk, mv, mw, my);
+        else wkv6_tc_pipelined_kernel<false><<<2 * B * H, kPThreads, sizeof(SmemP), stream>>>(a, mr, mk, mv, mw, my);
         return 1;
     }
     wkv6_tc_forward_kernel<<<B * H, kThreads, sizeof(Smem), stream>>>(a, mr, mk, mv, mw, my);
     return 1;
+}
+
+int forward(int B, int T, int H, const float* r, const float* k, const float* v, const float* w_raw, const float* u,
+            float* y, unsigned* status, bool pipelined, cudaStream_t stream) {
+    return launch(B, T, H, r, k, v, w_raw, u, y, status, false, pipelined, stream);
+}
+
+int forward_bf16in(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw, const float* u,
+                   float* y, unsigned* status, cudaStream_t stream) {
+    return launch(B, T, H, r, k, v, w_raw, u, y, status, true, true, stream);
 }
 
 }  // namespace wkv6tc

@@ -217,21 +217,27 @@ def _wkv6_shapes(r, k, v, w, u, H, gy=None):
 
 def wkv6_forward(r, k, v, w, u, H, tensor_cores=False):
     """y (float32) of the bidirectional WKV6; w is the raw decay input (decay = exp(-exp(w))).
-    tensor_cores=True runs the tcgen05 kernel (bf16 operand rounding, about 1e-2 accuracy)."""
-    dev = _check_inputs((("r", r), ("k", k), ("v", v), ("w", w), ("u", u)))
+    tensor_cores=True runs the tcgen05 kernel (bf16 operand rounding, about 1e-2 accuracy); it also
+    accepts r, k, v in bfloat16 (w, u float32) and then reads them without a widening pass."""
+    half_in = tensor_cores and _is_bf16(r) and _is_bf16(k) and _is_bf16(v)
+    if half_in:
+        dev = _check_inputs((("w", w), ("u", u)))
+        _check_inputs((("r", r), ("k", k), ("v", v)), torch.bfloat16, dev)
+    else:
+        dev = _check_inputs((("r", r), ("k", k), ("v", v), ("w", w), ("u", u)))
     B, T, C = _wkv6_shapes(r, k, v, w, u, H)
     lib = _lib.load()
     y = torch.empty((B, T, C), device=dev, dtype=torch.float32)
     if y.numel() == 0:
         return y
     if tensor_cores:
+        name = "vrwkv_wkv6_forward_tc_bf16" if half_in else "vrwkv_wkv6_forward_tc_f32"
         with torch.cuda.device(dev):
             ws = _workspace(256, dev)
-            st = lib.vrwkv_wkv6_forward_tc_f32(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                               w.data_ptr(), u.data_ptr(), y.data_ptr(), ws.data_ptr(),
-                                               ws.numel(), torch.cuda.current_stream().cuda_stream)
-            _lib.check(st, "vrwkv_wkv6_forward_tc_f32")
-            _check_status(lib, ws, "vrwkv_wkv6_forward_tc_f32")
+            st = getattr(lib, name)(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
+                                    y.data_ptr(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+            _lib.check(st, name)
+            _check_status(lib, ws, name)
         return y
     with torch.cuda.device(dev):
         st = lib.vrwkv_wkv6_forward_f32(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(),

@@ -55,8 +55,11 @@ class WKV_6(torch.autograd.Function):
             if tuple(r.shape) != (B, T, C):
                 raise RuntimeError(f"r has shape {tuple(r.shape)}, expected {(B, T, C)}")
             ctx.save_for_backward(r, k, v, w, u)
-            return ops.wkv6_forward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), H,
-                                    tensor_cores=_use_tensor_cores(r, k, v))
+            if _use_tensor_cores(r, k, v):
+                if all(x.dtype == torch.bfloat16 for x in (r, k, v)):      # read as they are, no widening pass
+                    return ops.wkv6_forward(r, k, v, _f32(w), _f32(u), H, tensor_cores=True)
+                return ops.wkv6_forward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), H, tensor_cores=True)
+            return ops.wkv6_forward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), H)
 
     @staticmethod
     def backward(ctx, gy):
