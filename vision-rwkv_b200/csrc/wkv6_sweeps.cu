@@ -34,7 +34,8 @@
 namespace wkv6 {
 
 constexpr int N = 64;          // head size
-constexpr int kBatch = 16;     // tokens per shared-memory batch
+constexpr int kBatch = 8;      // tokens per shared-memory batch (two batches of 10 KB per block: 11 blocks per SM)
+constexpr int kParts = N / kBatch;   // threads that share one token's dot products
 constexpr int kVecs = 5;       // r, k, v, gy, decay
 enum Kind { KIND_Y = 0, KIND_GR = 1, KIND_GK = 2, KIND_GV = 3 };
 enum Vec { V_R = 0, V_K = 1, V_V = 2, V_G = 3, V_D = 4 };
@@ -65,9 +66,13 @@ struct Batch {
 };
 
 // One pass of one kind over the whole sequence.  kRow: thread owns a row (key channel) of
-// the state, else a column (value channel).  kForward: direction of time.  kFirst: first
+// the state, else a column (value channel).  kForward: direction of time.  kOut: how the result
+// meets the other direction's: OUT_WRITE (first pass of a block), OUT_ADD (second pass of the same
+// block), OUT_ATOMIC (the two directions run in two blocks and add into a zeroed output: exactly
+// two addends per element, so the sum does not depend on their order).  kFirst: first
 // pass of the block (writes its output; the second pass adds to it).
-template <int kKind, bool kForward, bool kFirst>
+enum OutMode { OUT_WRITE = 0, OUT_ADD = 1, OUT_ATOMIC = 2 };
+template <int kKind, bool kForward, int kOut>
 __device__ __forceinline__ void sweep(const Args& a, Batch* buf, int b, int h, float u_self, const float* u_smem,
                                       float& gu_acc) {
     constexpr bool kRow = (kKind == KIND_GR || kKind == KIND_GK);
@@ -90,7 +95,7 @@ __device__ __forceinline__ void sweep(const Args& a, Batch* buf, int b, int h, f
 #pragma unroll
             for (int q = 0; q < (kBatch * N / 4) / N; ++q) {          // 256 chunks of 16 B, 64 threads
                 const int chunk = q * N + tid;
-                const int row = chunk >> 4, col4 = (chunk & 15) * 4;
+                const int row = chunk >> 4, col4 = (chunk & 15) * 4;      // 16 chunks of 16 bytes per token row
                 const int t = bt0 + row;
                 if (t < T) cp_async16(&dst->vec[vsel][row][col4], src + base + static_cast<size_t>(t) * C + col4);
             }
@@ -118,19 +123,20 @@ __device__ __forceinline__ void sweep(const Args& a, Batch* buf, int b, int h, f
         // decay in place, per-token scalars
         for (int row = 0; row < rows; ++row) cur->vec[V_D][row][tid] = expf(-expf(cur->vec[V_D][row][tid]));
         {
-            const int row = tid >> 2, part = tid & 3;
+            const int row = tid / kParts, part = tid % kParts;
             float s1 = 0.f, s2 = 0.f;
             if (row < rows) {
 #pragma unroll
-                for (int n = part * 16; n < part * 16 + 16; ++n) {
+                for (int n = part * kBatch; n < part * kBatch + kBatch; ++n) {
                     if (a.src[V_G] != nullptr) s1 += cur->vec[V_V][row][n] * cur->vec[V_G][row][n];
                     s2 += cur->vec[V_R][row][n] * u_smem[n] * cur->vec[V_K][row][n];
                 }
             }
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-            s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-            s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+#pragma unroll
+            for (int m = 1; m < kParts; m <<= 1) {
+                s1 += __shfl_xor_sync(0xffffffffu, s1, m);
+                s2 += __shfl_xor_sync(0xffffffffu, s2, m);
+            }
             if (part == 0 && row < kBatch) { cur->vg[row] = s1; cur->ruk[row] = s2; }
         }
         __syncthreads();
@@ -186,14 +192,17 @@ __device__ __forceinline__ void sweep(const Args& a, Batch* buf, int b, int h, f
                 if (kKind == KIND_GK) out += u_self * cur->vec[V_R][row][tid] * cur->vg[row];
             }
             float* dst = a.out[kKind] + idx;
-            if (kFirst) *dst = out;
-            else *dst += out;
+            if (kOut == OUT_WRITE) *dst = out;
+            else if (kOut == OUT_ADD) *dst += out;
+            else atomicAdd(dst, out);
         }
         __syncthreads();   // the batch buffer is refilled two iterations later
     }
 }
 
-template <bool kBackward>
+// kSplit: blockIdx.z picks the direction and the two blocks of a (batch, head, kind) add into a zeroed
+// output; otherwise one block runs both directions in turn.
+template <bool kBackward, bool kSplit>
 __global__ void __launch_bounds__(N) wkv6_sweep_kernel(const Args a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Batch* buf = reinterpret_cast<Batch*>(smem_raw);
@@ -205,19 +214,23 @@ __global__ void __launch_bounds__(N) wkv6_sweep_kernel(const Args a) {
     __syncthreads();
     const float u_self = u_smem[tid];
     float gu = 0.f;
+    constexpr int kOut1 = kSplit ? OUT_ATOMIC : OUT_WRITE, kOut2 = kSplit ? OUT_ATOMIC : OUT_ADD;
+    const bool first = !kSplit || blockIdx.z == 0, second = !kSplit || blockIdx.z == 1;
     if (!kBackward) {
-        sweep<KIND_Y, false, true>(a, buf, b, h, u_self, u_smem, gu);   // leftward state first
-        sweep<KIND_Y, true, false>(a, buf, b, h, u_self, u_smem, gu);
+        if (first) sweep<KIND_Y, false, kOut1>(a, buf, b, h, u_self, u_smem, gu);   // leftward state first
+        if (second) sweep<KIND_Y, true, kOut2>(a, buf, b, h, u_self, u_smem, gu);
     } else if (kind == KIND_GR) {
-        sweep<KIND_GR, true, true>(a, buf, b, h, u_self, u_smem, gu);
-        sweep<KIND_GR, false, false>(a, buf, b, h, u_self, u_smem, gu);
-        a.gu_part[static_cast<size_t>(b) * a.H * N + h * N + tid] = gu;
+        if (first) {
+            sweep<KIND_GR, true, kOut1>(a, buf, b, h, u_self, u_smem, gu);
+            a.gu_part[static_cast<size_t>(b) * a.H * N + h * N + tid] = gu;            // the bonus lives in this direction
+        }
+        if (second) sweep<KIND_GR, false, kOut2>(a, buf, b, h, u_self, u_smem, gu);
     } else if (kind == KIND_GK) {
-        sweep<KIND_GK, false, true>(a, buf, b, h, u_self, u_smem, gu);  // rightward adjoint: back in time
-        sweep<KIND_GK, true, false>(a, buf, b, h, u_self, u_smem, gu);
+        if (first) sweep<KIND_GK, false, kOut1>(a, buf, b, h, u_self, u_smem, gu);  // rightward adjoint: back in time
+        if (second) sweep<KIND_GK, true, kOut2>(a, buf, b, h, u_self, u_smem, gu);
     } else {
-        sweep<KIND_GV, false, true>(a, buf, b, h, u_self, u_smem, gu);
-        sweep<KIND_GV, true, false>(a, buf, b, h, u_self, u_smem, gu);
+        if (first) sweep<KIND_GV, false, kOut1>(a, buf, b, h, u_self, u_smem, gu);
+        if (second) sweep<KIND_GV, true, kOut2>(a, buf, b, h, u_self, u_smem, gu);
     }
 }
 
@@ -247,16 +260,33 @@ __global__ void wkv6_bonus_grad_kernel(int B, int C, const float* __restrict__ p
     gu[c] = acc;
 }
 
-static bool configure() {
-    static bool done = false, ok = false;
-    if (done) return ok;
-    done = true;
-    ok = cudaFuncSetAttribute(wkv6_sweep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(2 * sizeof(Batch))) == cudaSuccess &&
-         cudaFuncSetAttribute(wkv6_sweep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(2 * sizeof(Batch))) == cudaSuccess;
-    return ok;
+// Blocks of the sweep kernel that fit the device at once (0 if the kernel cannot be configured).
+static int resident_blocks() {
+    static int cached[64];
+    static bool known[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!known[dev]) {
+        const int smem = static_cast<int>(2 * sizeof(Batch));
+        bool ok = cudaFuncSetAttribute(wkv6_sweep_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                  cudaFuncSetAttribute(wkv6_sweep_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                  cudaFuncSetAttribute(wkv6_sweep_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                  cudaFuncSetAttribute(wkv6_sweep_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
+        int per_sm = 0, sms = 0;
+        ok = ok && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, wkv6_sweep_kernel<true, false>, N, smem) == cudaSuccess;
+        ok = ok && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        cached[dev] = ok ? per_sm * sms : 0;
+        known[dev] = true;
+    }
+    return cached[dev];
 }
+static bool configure() { return resident_blocks() > 0; }
+
+// The two directions of a (batch, head, kind) go to two blocks when that still fits the device in
+// one wave: the walks are latency-bound, so twice the blocks is close to twice the speed then.
+static bool split_directions(int blocks) { return 2 * blocks <= resident_blocks(); }
 
 size_t backward_workspace(int B, int T, int H) {
     const size_t E = static_cast<size_t>(B) * T * H * N;
@@ -271,7 +301,12 @@ int forward(int B, int T, int H, const float* r, const float* k, const float* v,
     a.src[V_R] = r; a.src[V_K] = k; a.src[V_V] = v; a.src[V_G] = nullptr; a.src[V_D] = w_raw;
     a.u = u;
     a.out[KIND_Y] = y;
-    wkv6_sweep_kernel<false><<<dim3(B * H), N, 2 * sizeof(Batch), stream>>>(a);
+    if (split_directions(B * H)) {
+        cudaMemsetAsync(y, 0, static_cast<size_t>(B) * T * H * N * sizeof(float), stream);
+        wkv6_sweep_kernel<false, true><<<dim3(B * H, 1, 2), N, 2 * sizeof(Batch), stream>>>(a);
+    } else {
+        wkv6_sweep_kernel<false, false><<<dim3(B * H), N, 2 * sizeof(Batch), stream>>>(a);
+    }
     return 1;
 }
 
@@ -289,7 +324,14 @@ int backward(int B, int T, int H, const float* r, const float* k, const float* v
     a.out[KIND_GR] = gr; a.out[KIND_GK] = gk; a.out[KIND_GV] = gv;
     for (int i = 0; i < 4; ++i) a.cum[i] = ws + i * E;
     a.gu_part = ws + 4 * E;
-    wkv6_sweep_kernel<true><<<dim3(B * H, 3), N, 2 * sizeof(Batch), stream>>>(a);
+    if (split_directions(3 * B * H)) {
+        cudaMemsetAsync(gr, 0, E * sizeof(float), stream);
+        cudaMemsetAsync(gk, 0, E * sizeof(float), stream);
+        cudaMemsetAsync(gv, 0, E * sizeof(float), stream);
+        wkv6_sweep_kernel<true, true><<<dim3(B * H, 3, 2), N, 2 * sizeof(Batch), stream>>>(a);
+    } else {
+        wkv6_sweep_kernel<true, false><<<dim3(B * H, 3), N, 2 * sizeof(Batch), stream>>>(a);
+    }
     const int blocks = static_cast<int>(std::min<size_t>((E + 255) / 256, 148 * 16));
     wkv6_decay_grad_kernel<<<blocks, 256, 0, stream>>>(B, T, C, w_raw, a.cum[0], a.cum[1], a.cum[2], a.cum[3], gw);
     wkv6_bonus_grad_kernel<<<(C + 127) / 128, 128, 0, stream>>>(B, C, a.gu_part, gu);
