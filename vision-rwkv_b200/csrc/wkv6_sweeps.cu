@@ -203,7 +203,7 @@ __device__ __forceinline__ void sweep(const Args& a, Batch* buf, int b, int h, f
 // kSplit: blockIdx.z picks the direction and the two blocks of a (batch, head, kind) add into a zeroed
 // output; otherwise one block runs both directions in turn.
 template <bool kBackward, bool kSplit>
-__global__ void __launch_bounds__(N) wkv6_sweep_kernel(const Args a) {
+__global__ void __launch_bounds__(N, 9) wkv6_sweep_kernel(const Args a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Batch* buf = reinterpret_cast<Batch*>(smem_raw);
     __shared__ float u_smem[N];

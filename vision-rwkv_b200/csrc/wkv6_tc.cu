@@ -423,9 +423,9 @@ wkv6_tc_forward_kernel(const Args a, const __grid_constant__ CUtensorMap map_r, 
 // of its warps, one phase after the other; what must be serial, though, is only
 //     state round trip (block n)  ->  read-out / update products (block n)  ->  round trip (n + 1).
 // Here one CTA walks one direction of one (batch, head) with nine warps in three roles:
-//   producers (warps 3, 6..12): operands of block n+1 (log-decay sums, scalings, bf16 rounding, the
-//       pairwise scores of a strongly decaying block) into the other of two operand sets, and the
-//       TMA loads of block n+2;
+//   producers (warps 3, 6..12, two groups of four): group g prepares the operands of the blocks g, g+2, ...
+//       (log-decay sums, scalings, bf16 rounding, the pairwise scores of a strongly decaying block)
+//       into operand set g, two block periods ahead of their use;
 //   loader (warp 13): the TMA loads of block n+2 as soon as the producers have read block n (issuing
 //       the four copies costs several hundred cycles, too many for a thread the others wait for);
 //   control (warp 2, owner of TMEM lanes 64..95): issues all tensor-core work; between the score
@@ -436,10 +436,9 @@ wkv6_tc_forward_kernel(const Args a, const __grid_constant__ CUtensorMap map_r, 
 // Hand-overs are mbarriers (operands ready / operand set free / products done) and two named
 // barriers; every wait is bounded.
 constexpr int kPThreads = 448;    // 4 state warps, 1 control warp, 8 producer warps, 1 loader warp
-constexpr int kProducers = 256;
 constexpr int kBarRound = 1;     // named barrier: state + control, 160 threads
 constexpr int kBarYTile = 2;     // state, 128 threads
-constexpr int kBarProd = 3;      // producers, 256 threads
+constexpr int kBarProd = 3;      // producer group 0 (128 threads); group 1 uses the next id
 
 struct OpSet {
     __nv_bfloat16 opR[16 * 64];       // B of the read-out; through a base 1 KB lower also the A of the scores (rows 64..79)
@@ -458,7 +457,7 @@ struct __align__(1024) SmemP {
     OpSet sets[2];
     float raw[2][4][SC][N];           // r, k, v, w of two blocks in flight
     float ytile[2][SC][N];
-    float acum[SC + 1][N];            // a_0 .. a_16 per key channel
+    float acum[2][SC + 1][N];         // a_0 .. a_16 per key channel, one array per producer group
     float u[N];
     uint64_t raw_full[2];
     uint64_t raw_free[2];
@@ -563,44 +562,47 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
 
     if (is_producer) {
         // =================================== producers ===================================
-        for (int q = 0; q < n_steps; ++q) {
-            const int slot = q & 1;
+        // two groups of four warps; group g prepares the blocks q = g, g + 2, ... into operand set g from staging
+        // slot g, with its own running-sum array and named barrier, so that a block has two block periods to get ready
+        const int group = pid >> 7, gid = pid & 127;
+        const int bar_id = kBarProd + group;
+        float(&acum)[SC + 1][N] = s.acum[group];
+        OpSet& set = s.sets[group];
+        float(&raw)[4][SC][N] = s.raw[group];
+        for (int q = group; q < n_steps; q += 2) {
             const uint32_t use_parity = (q >> 1) & 1;
-            OpSet& set = s.sets[slot];
-            float(&raw)[4][SC][N] = s.raw[slot];
-            wait_on(&s.raw_full[slot], use_parity);
-            // ---- phase A: running sums of the log-decays, a_t[c] for t = 0..16; thread = (key channel, quarter of
-            //      the block), the four quarters of a channel in one warp so that their totals travel by shuffle ----
+            wait_on(&s.raw_full[group], use_parity);
+            // ---- phase A: running sums of the log-decays, a_t[c] for t = 0..16; thread = (key channel, half of the
+            //      block), the two halves of a channel in one warp so that the first half's total travels by shuffle ----
             {
-                const int c = (pid >> 5) * 8 + (lane & 7), quarter = lane >> 3;
-                float wv[4];
+                const int c = (gid >> 5) * 16 + (lane & 15), half = lane >> 4;
+                float wv[8];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) wv[j] = raw[3][row_of(quarter * 4 + j)][c];
-                float pre[4], run = 0.f;
+                for (int j = 0; j < 8; ++j) wv[j] = raw[3][row_of(half * 8 + j)][c];
+                float pre[8], run = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    run += (q * SC + quarter * 4 + j < T) ? -__expf(wv[j]) : 0.f;
+                for (int j = 0; j < 8; ++j) {
+                    run += (q * SC + half * 8 + j < T) ? -__expf(wv[j]) : 0.f;
                     pre[j] = run;
                 }
-                // totals of the quarters before this one
-                const float up8 = __shfl_up_sync(0xffffffffu, run, 8);
-                const float up16 = __shfl_up_sync(0xffffffffu, run, 16);
-                const float up24 = __shfl_up_sync(0xffffffffu, run, 24);
-                const float before = (quarter > 0 ? up8 : 0.f) + (quarter > 1 ? up16 : 0.f) + (quarter > 2 ? up24 : 0.f);
-                if (quarter == 0) s.acum[0][c] = 0.f;
+                const float up = __shfl_up_sync(0xffffffffu, run, 16);
+                const float before = half ? up : 0.f;
+                if (half == 0) acum[0][c] = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) s.acum[quarter * 4 + j + 1][c] = pre[j] + before;
+                for (int j = 0; j < 8; ++j) acum[half * 8 + j + 1][c] = pre[j] + before;
             }
-            if (q >= 2) wait_on(&s.ops_free[slot], use_parity ^ 1u);   // the products of block q-2 are done with this set
-            sm100::named_bar_sync(kBarProd, kProducers);
-            // ---- job 1: thread = (token t, 4 key channels): Rs, Kb, bonus ----
-            {
-                const int t = pid >> 4, c0 = (pid & 15) * 4, row = row_of(t);
+            if (q >= 2) wait_on(&s.ops_free[group], use_parity ^ 1u);   // the products of block q-2 are done with this set
+            sm100::named_bar_sync(bar_id, 128);
+            // ---- job 1: work item = (token t, 4 key channels): Rs, Kb, bonus; two items per thread ----
+#pragma unroll
+            for (int rep = 0; rep < 2; ++rep) {
+                const int it = gid + 128 * rep;
+                const int t = it >> 4, c0 = (it & 15) * 4, row = row_of(t);
                 const float4 rv = raw_ld4<kHalfIn>(&raw[0][0][0], row, c0);
                 const float4 kv = raw_ld4<kHalfIn>(&raw[1][0][0], row, c0);
-                const float4 at = *reinterpret_cast<const float4*>(&s.acum[t][c0]);
-                const float4 at1 = *reinterpret_cast<const float4*>(&s.acum[t + 1][c0]);
-                const float4 aA = *reinterpret_cast<const float4*>(&s.acum[SC][c0]);
+                const float4 at = *reinterpret_cast<const float4*>(&acum[t][c0]);
+                const float4 at1 = *reinterpret_cast<const float4*>(&acum[t + 1][c0]);
+                const float4 aA = *reinterpret_cast<const float4*>(&acum[SC][c0]);
                 const float rvv[4] = {rv.x, rv.y, rv.z, rv.w}, kvv[4] = {kv.x, kv.y, kv.z, kv.w};
                 const float a0[4] = {at.x, at.y, at.z, at.w}, a1[4] = {at1.x, at1.y, at1.z, at1.w};
                 const float aa[4] = {aA.x, aA.y, aA.z, aA.w};
@@ -619,22 +621,24 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
                     bonus += __shfl_xor_sync(0xffffffffu, bonus, 2);
                     bonus += __shfl_xor_sync(0xffffffffu, bonus, 4);
                     bonus += __shfl_xor_sync(0xffffffffu, bonus, 8);
-                    if ((pid & 15) == 0) set.diag[t] = bonus;
-                } else if ((pid & 15) == 0) {
+                    if ((it & 15) == 0) set.diag[t] = bonus;
+                } else if ((it & 15) == 0) {
                     set.diag[t] = 0.f;
                 }
             }
-            // ---- job 2: thread = (key channel, quarter of the block): Ks, V^T, e^A ----
-            bool big;
-            {
-                const int c = pid & 63, quarter = pid >> 6;
-                const float A = s.acum[SC][c];
-                big = A < -kMaxLogDecay;
+            // ---- job 2: work item = (key channel, quarter of the block): Ks, V^T, e^A; two items per thread ----
+            bool big = false;
+#pragma unroll
+            for (int rep = 0; rep < 2; ++rep) {
+                const int it = gid + 128 * rep;
+                const int c = it & 63, quarter = it >> 6;
+                const float A = acum[SC][c];
+                big = big || (A < -kMaxLogDecay);
                 float kh[4], vv[4], a1[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int t = quarter * 4 + j, row = row_of(t);
-                    a1[j] = s.acum[t + 1][c];
+                    a1[j] = acum[t + 1][c];
                     kh[j] = raw_ld1<kHalfIn>(&raw[1][0][0], row, c);
                     vv[j] = raw_ld1<kHalfIn>(&raw[2][0][0], row, c);
                 }
@@ -644,30 +648,33 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
                 *reinterpret_cast<uint2*>(&set.opK[op_index(64, c, quarter * 4)]) = make_uint2(pack_bf16(kh[0], kh[1]), pack_bf16(kh[2], kh[3]));
                 *reinterpret_cast<uint2*>(&set.opV[op_index(64, c, quarter * 4)]) = make_uint2(pack_bf16(vv[0], vv[1]), pack_bf16(vv[2], vv[3]));
             }
-            const bool pairwise = named_bar_or(kBarProd, kProducers, big);   // also orders diag before the loop below
+            const bool pairwise = named_bar_or(bar_id, 128, big);   // also orders diag before the loop below
             if (pairwise) {
                 // ---- strong decay: the 16 x 16 scores pairwise in fp32, every exponent <= 0 ----
-                const int t = pid >> 4, sidx = pid & 15;
-                const int row_t = row_of(t), row_s = row_of(sidx);
-                float acc = 0.f;
-                if (sidx < t) {
+                for (int rep = 0; rep < 2; ++rep) {
+                    const int it = gid + 128 * rep;
+                    const int t = it >> 4, sidx = it & 15;
+                    const int row_t = row_of(t), row_s = row_of(sidx);
+                    float acc = 0.f;
+                    if (sidx < t) {
 #pragma unroll 8
-                    for (int i = 0; i < N; ++i)
-                        acc += raw_ld1<kHalfIn>(&raw[0][0][0], row_t, i) * raw_ld1<kHalfIn>(&raw[1][0][0], row_s, i) *
-                               __expf(s.acum[t][i] - s.acum[sidx + 1][i]);
-                } else if (sidx == t) {
-                    acc = set.diag[t];
+                        for (int i = 0; i < N; ++i)
+                            acc += raw_ld1<kHalfIn>(&raw[0][0][0], row_t, i) * raw_ld1<kHalfIn>(&raw[1][0][0], row_s, i) *
+                                   __expf(acum[t][i] - acum[sidx + 1][i]);
+                    } else if (sidx == t) {
+                        acc = set.diag[t];
+                    }
+                    // one 4-byte store per lane pair: 2-byte shared stores are slow
+                    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+                    if ((sidx & 1) == 0) *reinterpret_cast<uint32_t*>(&set.opP[op_index(16, t, sidx)]) = pack_bf16(acc, other);
                 }
-                // one 4-byte store per lane pair: 2-byte shared stores are slow
-                const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
-                if ((sidx & 1) == 0) *reinterpret_cast<uint32_t*>(&set.opP[op_index(16, t, sidx)]) = pack_bf16(acc, other);
             }
-            if (pid == 0) set.pairwise = pairwise ? 1u : 0u;
+            if (gid == 0) set.pairwise = pairwise ? 1u : 0u;
             sm100::fence_proxy_async_smem();
-            sm100::named_bar_sync(kBarProd, kProducers);
-            if (pid == 0) {
-                mbar_arrive(&s.ops_ready[slot]);
-                mbar_arrive(&s.raw_free[slot]);               // every producer is done reading this staging slot
+            sm100::named_bar_sync(bar_id, 128);
+            if (gid == 0) {
+                mbar_arrive(&s.ops_ready[group]);
+                mbar_arrive(&s.raw_free[group]);              // every producer of the group is done reading this staging slot
             }
         }
     } else if (is_loader) {
