@@ -188,7 +188,24 @@ def side_measurements(dev, world, dist):
     out["vrwkv_b_inference"] = {"img_per_s": B * world / (ms * 1e-3), "ms_per_batch": ms,
                                 "batch_per_gpu": B, "resolution": 224, "n_gpus": world,
                                 "gemm_dtype": "bf16 autocast", "wkv_dtype": "f32"}
-    del model
+    # the same network, forward + backward of a sum-of-squares loss (no optimizer step), batch 32 per GPU:
+    # bfloat16 activations reach Bi-WKV under autocast, so its bf16-tile kernels run in both directions
+    model.train()
+    img_t = img[:32]
+
+    def train_step():
+        for p_ in model.parameters():
+            p_.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(img_t)[0].float().square().mean()
+        loss.backward()
+
+    ms = _timed(train_step, dev, world, dist, iters=5)
+    out["vrwkv_b_forward_backward"] = {"img_per_s": 32 * world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": 32,
+                                       "resolution": 224, "n_gpus": world, "gemm_dtype": "bf16 autocast",
+                                       "wkv_dtype": "bf16 tiles, f32 arithmetic", "optimizer": "none",
+                                       "gradient_all_reduce": "none (per-rank replicas)"}
+    del model, img_t
     # VRWKV6-B (embed 768, 12 heads, 12 blocks): same images; under autocast r, k, v reach the WKV6 operator in
     # bfloat16 and the tcgen05 forward runs
     from vision_rwkv_b200.backbone6 import build_v6
