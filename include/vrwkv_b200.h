@@ -210,6 +210,18 @@ int vrwkv_qshift_mix_backward_f32(int B, int H, int W, int C, int group, int shi
                                   float* gx, float* const* gmix, void* workspace, size_t workspace_bytes,
                                   void* stream);
 
+/* The per-head shift of VRWKV6 (q_shift_multihead, CLS/vrwkv6.py:75-101) fused with the same
+ * interpolations (VRWKV_ChannelMix of vrwkv6.py: xk, xr): within every head of head_dim channels
+ * the four quarters take the left, right, upper and lower neighbour.  head_dim is a multiple of 4
+ * that divides C.  Workspace of the backward: vrwkv_qshift_mix_backward_workspace_bytes. */
+int vrwkv_qshift_multihead_mix_forward_f32(int B, int H, int W, int C, int head_dim, int shift, int n_out,
+                                           const float* x, const float* const* mix, float* const* out,
+                                           void* stream);
+int vrwkv_qshift_multihead_mix_backward_f32(int B, int H, int W, int C, int head_dim, int shift, int n_out,
+                                            const float* x, const float* const* mix,
+                                            const float* const* gout, float* gx, float* const* gmix,
+                                            void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

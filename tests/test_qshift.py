@@ -53,3 +53,40 @@ def test_fused_kernel_matches_oracle(cuda_device, B, H, W, C, s, gamma, n):
     assert rel_err(xd.grad, xr.grad) < 1e-6
     for a, b in zip(md, mr):
         assert a.grad.shape == b.grad.shape and rel_err(a.grad, b.grad) < 1e-5
+
+
+MULTIHEAD_CASES = [(2, 14, 14, 192, 64, 1, 2), (1, 5, 7, 128, 64, 1, 2), (2, 3, 4, 64, 64, 2, 3), (1, 6, 6, 48, 16, 1, 1),
+                   (1, 1, 9, 128, 64, 1, 2), (1, 12, 20, 256, 64, 1, 2)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,H,W,C,head_dim,s,n", MULTIHEAD_CASES)
+def test_fused_per_head_shift_matches_oracle(cuda_device, B, H, W, C, head_dim, s, n):
+    """The VRWKV6 variant: the four shifted quarters repeat inside every head."""
+    from vision_rwkv_b200.qshift import qshift_mix
+    g = torch.Generator().manual_seed(B * 100 + C + head_dim)
+    x = torch.randn(B, H * W, C, generator=g)
+    mixes = [torch.rand(1, 1, C, generator=g) for _ in range(n)]
+    gouts = [torch.randn(B, H * W, C, generator=g) for _ in range(n)]
+    xr = x.double().requires_grad_(True)
+    mr = [m.double().requires_grad_(True) for m in mixes]
+    xx = O.q_shift_multihead(xr, (H, W), s, head_dim)
+    ref = [xr * m + xx * (1 - m) for m in mr]
+    torch.autograd.backward(ref, [go.double() for go in gouts])
+    xd = x.to(cuda_device).requires_grad_(True)
+    md = [m.to(cuda_device).requires_grad_(True) for m in mixes]
+    outs = qshift_mix(xd, md, (H, W), s, head_dim=head_dim)
+    torch.autograd.backward(outs, [go.to(cuda_device) for go in gouts])
+    for o, r in zip(outs, ref):
+        assert rel_err(o, r.detach()) < 1e-6
+    assert rel_err(xd.grad, xr.grad) < 1e-6
+    for a, b in zip(md, mr):
+        assert a.grad.shape == b.grad.shape and rel_err(a.grad, b.grad) < 1e-5
+
+
+@pytest.mark.gpu
+def test_per_head_shift_rejects_bad_head_size(cuda_device):
+    from vision_rwkv_b200 import _lib
+    lib = _lib.load()
+    assert lib.vrwkv_qshift_multihead_mix_forward_f32(1, 2, 2, 96, 64, 1, 1, 0, 0, 0, 0) == 1      # 64 does not divide 96
+    assert lib.vrwkv_qshift_multihead_mix_forward_f32(1, 2, 2, 60, 6, 1, 1, 0, 0, 0, 0) == 1       # not a multiple of 4

@@ -39,6 +39,8 @@ SIGNATURES = {
     "vrwkv_qshift_mix_forward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 4),
     "vrwkv_qshift_mix_backward_workspace_bytes": (_c_size_t, [_c_int] * 5),
     "vrwkv_qshift_mix_backward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 6 + [_c_size_t, _ptr]),
+    "vrwkv_qshift_multihead_mix_forward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 4),
+    "vrwkv_qshift_multihead_mix_backward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 6 + [_c_size_t, _ptr]),
 }
 
 _lib = None

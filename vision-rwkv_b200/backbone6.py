@@ -7,10 +7,11 @@ classification/mmcls_custom/models/backbones/vrwkv6.py:75-477 (`q_shift_multihea
 time_maa_g,time_maa_w1,time_maa_w2,time_decay,time_decay_w1,time_decay_w2,time_faaaa,key,value,
 receptance,gate,output,ln_x}`, `layers.N.ffn.{spatial_mix_k,spatial_mix_r,key,receptance,value}`.
 
-Only the recurrence is a kernel of this package here (`RUN_CUDA_RWKV6`: the tcgen05 forward
-when r, k, v arrive in half / bfloat16, i.e. under autocast; exact fp32 sweeps otherwise and for
-every backward).  The per-head token shift, the low-rank data-dependent mixes and the
-GroupNorm / gate epilogue are stock torch operations.
+Kernels of this package: the recurrence (`RUN_CUDA_RWKV6`: the tcgen05 forward when r, k, v
+arrive in half / bfloat16, i.e. under autocast; exact fp32 sweeps otherwise and for every
+backward) and the ChannelMix's per-head token shift + two interpolations (`qshift_mix(...,
+head_dim=64)`).  The SpatialMix's shift feeds low-rank data-dependent mixes and stays a torch
+slice copy, like the GroupNorm / gate epilogue.
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ import torch.nn.functional as F
 import torch.utils.checkpoint as cp
 
 from .backbone import _PatchEmbed, _ramp
+from .qshift import qshift_mix
 from .vrwkv6 import HEAD_SIZE, RUN_CUDA_RWKV6
 
 MIX_RANK = 32       # width of the low-rank branch that produces the five mixing offsets
@@ -105,9 +107,8 @@ class ChannelMixV6(nn.Module):
         self.value = nn.Linear(hidden, n_embd, bias=False)
 
     def forward(self, x, resolution):
-        xx = q_shift_multihead(x, self.shift_pixel, resolution)
-        xk = x * self.spatial_mix_k + xx * (1 - self.spatial_mix_k)
-        xr = x * self.spatial_mix_r + xx * (1 - self.spatial_mix_r)
+        xk, xr = qshift_mix(x, (self.spatial_mix_k, self.spatial_mix_r), resolution, self.shift_pixel,
+                            head_dim=HEAD_SIZE)          # per-head shift + both interpolations in one pass
         k = torch.square(torch.relu(self.key(xk)))
         if self.key_norm is not None:
             k = self.key_norm(k)

@@ -23,7 +23,8 @@ constexpr int kTokensPerBlock = 32;
 
 struct Args {
     int B, H, W, C;
-    int group;     // channels per shifted group = int(C * gamma)
+    int group;     // channels per shifted group = int(C * gamma), or head_dim / 4 for the per-head variant
+    int period;    // 0: the four groups are channels [0, 4 * group); n: they repeat every n channels (n = head_dim)
     int shift;     // pixels
     int n_out;
     const float* x;
@@ -36,7 +37,7 @@ struct Args {
 
 // Token that channel c of token (h, w) reads its shifted value from; -1 = zero fill.
 __device__ __forceinline__ int source_token(const Args& a, int h, int w, int c) {
-    const int g = c / a.group;
+    const int g = (a.period ? c % a.period : c) / a.group;
     int hs = h, ws = w;
     if (g == 0) ws = w - a.shift;
     else if (g == 1) ws = w + a.shift;
@@ -47,7 +48,7 @@ __device__ __forceinline__ int source_token(const Args& a, int h, int w, int c) 
 }
 // Token whose shifted value is read *from* (h, w) for channel c (the transpose); -1 = none.
 __device__ __forceinline__ int reader_token(const Args& a, int h, int w, int c) {
-    const int g = c / a.group;
+    const int g = (a.period ? c % a.period : c) / a.group;
     int hd = h, wd = w;
     if (g == 0) wd = w + a.shift;
     else if (g == 1) wd = w - a.shift;
@@ -233,19 +234,56 @@ static int qshift_check(int B, int H, int W, int C, int group, int shift, int n_
     return VRWKV_OK;
 }
 
-extern "C" int vrwkv_qshift_mix_forward_f32(int B, int H, int W, int C, int group, int shift, int n_out,
-                                            const float* x, const float* const* mix, float* const* out,
-                                            void* stream) {
+static int qshift_forward_any(int B, int H, int W, int C, int group, int period, int shift, int n_out, const float* x,
+                              const float* const* mix, float* const* out, void* stream) {
     if (int st = qshift_check(B, H, W, C, group, shift, n_out)) return st;
     if (!x || !mix || !out) return VRWKV_ERR_NULL;
     qshift::Args a{};
-    a.B = B; a.H = H; a.W = W; a.C = C; a.group = group; a.shift = shift; a.n_out = n_out; a.x = x;
+    a.B = B; a.H = H; a.W = W; a.C = C; a.group = group; a.period = period; a.shift = shift; a.n_out = n_out; a.x = x;
     for (int m = 0; m < n_out; ++m) {
         if (!mix[m] || !out[m]) return VRWKV_ERR_NULL;
         a.mix[m] = mix[m];
         a.out[m] = out[m];
     }
     return record_launches(qshift::forward(a, static_cast<cudaStream_t>(stream)));
+}
+
+static int qshift_backward_any(int B, int H, int W, int C, int group, int period, int shift, int n_out, const float* x,
+                               const float* const* mix, const float* const* gout, float* gx, float* const* gmix,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (int st = qshift_check(B, H, W, C, group, shift, n_out)) return st;
+    if (!x || !mix || !gout || !gx || !gmix || !workspace) return VRWKV_ERR_NULL;
+    if (workspace_bytes < qshift::backward_workspace(B, H, W, C, n_out)) return VRWKV_ERR_WORKSPACE;
+    qshift::Args a{};
+    a.B = B; a.H = H; a.W = W; a.C = C; a.group = group; a.period = period; a.shift = shift; a.n_out = n_out; a.x = x;
+    a.gx = gx;
+    a.partial = static_cast<float*>(workspace);
+    float* gm[qshift::kMaxOut] = {nullptr, nullptr, nullptr};
+    for (int m = 0; m < n_out; ++m) {
+        if (!mix[m] || !gout[m] || !gmix[m]) return VRWKV_ERR_NULL;
+        a.mix[m] = mix[m];
+        a.gout[m] = gout[m];
+        gm[m] = gmix[m];
+    }
+    return record_launches(qshift::backward(a, gm, static_cast<cudaStream_t>(stream)));
+}
+
+// head_dim channels per head, a multiple of 4 that divides C; the groups are its quarters
+static int multihead_check(int C, int head_dim) {
+    return (head_dim < 4 || head_dim % 4 != 0 || C % head_dim != 0) ? VRWKV_ERR_SHAPE : VRWKV_OK;
+}
+
+extern "C" int vrwkv_qshift_mix_forward_f32(int B, int H, int W, int C, int group, int shift, int n_out,
+                                            const float* x, const float* const* mix, float* const* out,
+                                            void* stream) {
+    return qshift_forward_any(B, H, W, C, group, 0, shift, n_out, x, mix, out, stream);
+}
+
+extern "C" int vrwkv_qshift_multihead_mix_forward_f32(int B, int H, int W, int C, int head_dim, int shift, int n_out,
+                                                      const float* x, const float* const* mix, float* const* out,
+                                                      void* stream) {
+    if (int st = multihead_check(C, head_dim)) return st;
+    return qshift_forward_any(B, H, W, C, head_dim / 4, head_dim, shift, n_out, x, mix, out, stream);
 }
 
 extern "C" size_t vrwkv_qshift_mix_backward_workspace_bytes(int B, int H, int W, int C, int n_out) {
@@ -257,19 +295,14 @@ extern "C" int vrwkv_qshift_mix_backward_f32(int B, int H, int W, int C, int gro
                                              const float* x, const float* const* mix, const float* const* gout,
                                              float* gx, float* const* gmix, void* workspace, size_t workspace_bytes,
                                              void* stream) {
-    if (int st = qshift_check(B, H, W, C, group, shift, n_out)) return st;
-    if (!x || !mix || !gout || !gx || !gmix || !workspace) return VRWKV_ERR_NULL;
-    if (workspace_bytes < qshift::backward_workspace(B, H, W, C, n_out)) return VRWKV_ERR_WORKSPACE;
-    qshift::Args a{};
-    a.B = B; a.H = H; a.W = W; a.C = C; a.group = group; a.shift = shift; a.n_out = n_out; a.x = x;
-    a.gx = gx;
-    a.partial = static_cast<float*>(workspace);
-    float* gm[qshift::kMaxOut] = {nullptr, nullptr, nullptr};
-    for (int m = 0; m < n_out; ++m) {
-        if (!mix[m] || !gout[m] || !gmix[m]) return VRWKV_ERR_NULL;
-        a.mix[m] = mix[m];
-        a.gout[m] = gout[m];
-        gm[m] = gmix[m];
-    }
-    return record_launches(qshift::backward(a, gm, static_cast<cudaStream_t>(stream)));
+    return qshift_backward_any(B, H, W, C, group, 0, shift, n_out, x, mix, gout, gx, gmix, workspace, workspace_bytes, stream);
+}
+
+extern "C" int vrwkv_qshift_multihead_mix_backward_f32(int B, int H, int W, int C, int head_dim, int shift, int n_out,
+                                                       const float* x, const float* const* mix,
+                                                       const float* const* gout, float* gx, float* const* gmix,
+                                                       void* workspace, size_t workspace_bytes, void* stream) {
+    if (int st = multihead_check(C, head_dim)) return st;
+    return qshift_backward_any(B, H, W, C, head_dim / 4, head_dim, shift, n_out, x, mix, gout, gx, gmix, workspace,
+                               workspace_bytes, stream);
 }

@@ -272,7 +272,7 @@ def _ptr_array(tensors):
     return arr
 
 
-def _qshift_args(x, mixes, resolution, shift_pixel, gamma):
+def _qshift_args(x, mixes, resolution, shift_pixel, gamma, head_dim=None):
     if x.dim() != 3:
         raise RuntimeError(f"x must be (B, T, C), got {tuple(x.shape)}")
     B, T, C = x.shape
@@ -281,38 +281,44 @@ def _qshift_args(x, mixes, resolution, shift_pixel, gamma):
         raise RuntimeError(f"patch resolution {H}x{W} does not match T={T}")
     if not 1 <= len(mixes) <= 3:
         raise RuntimeError("between one and three mix vectors")
-    if gamma > 0.25:
-        raise RuntimeError("channel_gamma must be <= 1/4")            # the reference asserts the same
-    group = int(C * gamma)
-    if group <= 0:
-        raise RuntimeError(f"int(C * gamma) = 0 for C={C}")
+    if head_dim is not None:
+        if head_dim % 4 or C % head_dim:                                # vrwkv6.py:78-79 asserts the same
+            raise RuntimeError(f"head_dim={head_dim} must be a multiple of 4 that divides C={C}")
+        group = head_dim
+    else:
+        if gamma > 0.25:
+            raise RuntimeError("channel_gamma must be <= 1/4")        # the reference asserts the same
+        group = int(C * gamma)
+        if group <= 0:
+            raise RuntimeError(f"int(C * gamma) = 0 for C={C}")
     for m in mixes:
         if m.numel() != C:
             raise RuntimeError(f"mix vectors must hold C={C} values")
     return B, H, W, C, group
 
 
-def qshift_mix_forward(x, mixes, resolution, shift_pixel=1, gamma=0.25):
-    """[x * mix + q_shift(x) * (1 - mix) for mix in mixes], one fused pass."""
+def qshift_mix_forward(x, mixes, resolution, shift_pixel=1, gamma=0.25, head_dim=None):
+    """[x * mix + q_shift(x) * (1 - mix) for mix in mixes], one fused pass.  head_dim=None: the four
+    shifted groups are int(C * gamma) channels each (VRWKV); head_dim=n: the per-head shift of VRWKV6."""
     dev = _check_inputs([("x", x)] + [(f"mix{i}", m) for i, m in enumerate(mixes)])
-    B, H, W, C, group = _qshift_args(x, mixes, resolution, shift_pixel, gamma)
+    B, H, W, C, group = _qshift_args(x, mixes, resolution, shift_pixel, gamma, head_dim)
     lib = _lib.load()
+    entry = lib.vrwkv_qshift_mix_forward_f32 if head_dim is None else lib.vrwkv_qshift_multihead_mix_forward_f32
     outs = [torch.empty_like(x) for _ in mixes]
     if x.numel() == 0:
         return outs
     with torch.cuda.device(dev):
-        st = lib.vrwkv_qshift_mix_forward_f32(B, H, W, C, group, shift_pixel, len(mixes), x.data_ptr(),
-                                              _ptr_array(mixes), _ptr_array(outs),
-                                              torch.cuda.current_stream().cuda_stream)
+        st = entry(B, H, W, C, group, shift_pixel, len(mixes), x.data_ptr(), _ptr_array(mixes), _ptr_array(outs),
+                   torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_qshift_mix_forward_f32")
     return outs
 
 
-def qshift_mix_backward(x, mixes, gouts, resolution, shift_pixel=1, gamma=0.25):
+def qshift_mix_backward(x, mixes, gouts, resolution, shift_pixel=1, gamma=0.25, head_dim=None):
     """(gx, [gmix...]) for `qshift_mix_forward`."""
     dev = _check_inputs([("x", x)] + [(f"mix{i}", m) for i, m in enumerate(mixes)]
                         + [(f"gout{i}", g) for i, g in enumerate(gouts)])
-    B, H, W, C, group = _qshift_args(x, mixes, resolution, shift_pixel, gamma)
+    B, H, W, C, group = _qshift_args(x, mixes, resolution, shift_pixel, gamma, head_dim)
     if len(gouts) != len(mixes) or any(g.shape != x.shape for g in gouts):
         raise RuntimeError("one output gradient of the shape of x per mix vector")
     lib = _lib.load()
@@ -322,7 +328,8 @@ def qshift_mix_backward(x, mixes, gouts, resolution, shift_pixel=1, gamma=0.25):
         return gx, [g.zero_() for g in gmix]
     with torch.cuda.device(dev):
         ws = _workspace(lib.vrwkv_qshift_mix_backward_workspace_bytes(B, H, W, C, len(mixes)), dev)
-        st = lib.vrwkv_qshift_mix_backward_f32(B, H, W, C, group, shift_pixel, len(mixes), x.data_ptr(),
+        entry = lib.vrwkv_qshift_mix_backward_f32 if head_dim is None else lib.vrwkv_qshift_multihead_mix_backward_f32
+        st = entry(B, H, W, C, group, shift_pixel, len(mixes), x.data_ptr(),
                                                _ptr_array(mixes), _ptr_array(gouts), gx.data_ptr(),
                                                _ptr_array(gmix), ws.data_ptr(), ws.numel(),
                                                torch.cuda.current_stream().cuda_stream)
