@@ -19,7 +19,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-DEFAULT_REF = "/root/reference"
+DEFAULT_REF = os.environ.get("VRWKV_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))   # where the reference checkout sits
 
 TARGETS = {
     "libref_biwkv.so": ("ref_shim_biwkv.cu", "classification/mae/vrwkv/cuda/wkv_cuda.cu",

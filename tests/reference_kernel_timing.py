@@ -1,6 +1,6 @@
 """Times the reference's own CUDA kernels (oracle/_ref/, built by oracle/build_ref.py) next to
 this repository's kernels on the same GPU, same shapes, CUDA events, best of N.  A measurement
-aid for DESIGN.md / profiles/, not a pytest module and not part of the product.
+aid for the design notes and profiles/, not a pytest module and not part of the product.
 
     python tests/reference_kernel_timing.py            # Bi-WKV B=64,T=4096,C=768 and WKV6 B=32,T=196,C=768
 """
