@@ -126,7 +126,10 @@ def run_reference_arm(args):
         return
     threads = os.cpu_count() or 1
     T, C = WORKLOAD["T"], WORKLOAD["C"]
-    sample_B = 1
+    # size the per-step sample like the cpu_baseline leg does: as many sequences as take about 5 s, so that
+    # every host thread has work (one sequence alone leaves most of them idle) and the run stays bounded
+    probe = cpu_recurrence_seconds(1, T, C, threads)
+    sample_B = max(1, min(WORKLOAD["B"], int(5.0 / probe)))
     times = []
     for i in range(args.warmup + args.steps):
         dt = cpu_recurrence_seconds(sample_B, T, C, threads)
