@@ -71,3 +71,41 @@ def test_two_ranks_match_one(tmp_path):
         assert torch.allclose(p["gwgu"][0], gw, rtol=1e-12, atol=1e-13)
         assert torch.allclose(p["gwgu"][1], gu, rtol=1e-12, atol=1e-13)
     assert torch.equal(parts[0]["gwgu"], parts[1]["gwgu"])
+
+
+def _failing_worker(rank, world, port, out_dir):
+    """Step 1: both ranks reduce.  Then rank 1 leaves (between steps, nothing of its own in flight) and
+    rank 0 starts the next collective alone: the process-group timeout must end it with an error."""
+    import datetime
+    import sys
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from vision_rwkv_b200.parallel import GradAllReducer
+    reducer = GradAllReducer()
+    buf = torch.full((2, 4), float(rank + 1), dtype=torch.float64)
+    reducer.launch(buf)
+    reducer.wait()
+    assert torch.equal(buf, torch.full((2, 4), 3.0, dtype=torch.float64))
+    if rank == 1:
+        return                                   # gone: no destroy, no further collective
+    t0 = time.time()
+    outcome = "completed"
+    try:
+        reducer.launch(buf)
+        reducer.wait()
+    except Exception as exc:                     # noqa: BLE001 - any transport / timeout error is the expected outcome
+        outcome = "error: " + type(exc).__name__
+    with open(f"{out_dir}/r0.txt", "w") as f:
+        f.write(f"{outcome}\n{time.time() - t0:.1f}\n")
+
+
+def test_missing_rank_ends_the_all_reduce_with_an_error(tmp_path):
+    """Failure detection without a GPU fault: a rank that never joins makes the collective fail on the
+    host within the process-group timeout instead of hanging the caller."""
+    mp.spawn(_failing_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    outcome, seconds = (tmp_path / "r0.txt").read_text().splitlines()[:2]
+    assert outcome.startswith("error"), outcome
+    assert float(seconds) < 60.0
