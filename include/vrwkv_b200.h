@@ -50,9 +50,12 @@ const char* vrwkv_last_error_detail(void);
 /* Number of kernels this library has launched in the calling process so far. */
 unsigned long long vrwkv_launch_count(void);
 
-/* Kernel path selection, for tests and measurements: 0 = automatic (default), 1 = the
+/* Kernel path selection, for tests and measurements: 0 = automatic (default: Bi-WKV takes the
+ * cluster-resident single-pass kernels when T <= 4096, C % 4 == 0 and the tensors are 16-byte
+ * aligned, else the persistent tile kernels, else the generic multi-launch path), 1 = the
  * first-generation kernels (Bi-WKV: the generic multi-launch path; WKV6 tensor-core forward:
- * the serial-phase kernel instead of the warp-specialised one), 2 = same as 0.  Process-wide.
+ * the serial-phase kernel instead of the warp-specialised one), 2 = Bi-WKV skips the
+ * cluster-resident kernels (persistent tile kernels where eligible).  Process-wide.
  * No reference counterpart. */
 int vrwkv_set_path(int path);
 /* Copies the device status word kept in the first 4 bytes of a workspace to *status_out

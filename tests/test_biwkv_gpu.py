@@ -22,14 +22,15 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 TOL = 1e-5
 
 
-@pytest.fixture(autouse=True, params=["auto", "generic"])
+@pytest.fixture(autouse=True, params=["auto", "tiles", "generic"])
 def kernel_path(request):
-    """Every test runs twice: automatic path selection (the fused TMA kernels wherever they
-    are eligible) and the generic multi-launch kernels."""
+    """Every test runs three times: automatic path selection (the cluster-resident kernels wherever
+    they are eligible), the persistent tile kernels that serve longer sequences, and the generic
+    multi-launch kernels."""
     from vision_rwkv_b200 import _lib, ops
     lib = _lib.load()
     ops.CHECK_STATUS = True
-    assert lib.vrwkv_set_path(1 if request.param == "generic" else 0) == 0
+    assert lib.vrwkv_set_path({"auto": 0, "generic": 1, "tiles": 2}[request.param]) == 0
     yield request.param
     lib.vrwkv_set_path(0)
     ops.CHECK_STATUS = False

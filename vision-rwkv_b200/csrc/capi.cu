@@ -9,7 +9,7 @@
 
 namespace {
 std::atomic<unsigned long long> g_launches{0};
-std::atomic<int> g_path{0};   // 0 auto, 1 generic only, 2 fused whenever eligible
+std::atomic<int> g_path{0};   // 0 auto (resident, else fused, else generic), 1 generic only, 2 skip the resident path
 
 char g_detail[256] = "";
 
@@ -81,8 +81,8 @@ int vrwkv_workspace_status(const void* workspace, void* stream, unsigned* status
 
 size_t vrwkv_biwkv_forward_workspace_bytes(int B, int T, int C) {
     if (check_shape(B, T, C) != VRWKV_OK) return 0;
-    return std::max(biwkv::generic_forward_workspace(B, T, C) + 256,
-                    biwkv::fused::workspace_bytes(B, T, C, false));
+    return std::max({biwkv::generic_forward_workspace(B, T, C) + 256, biwkv::fused::workspace_bytes(B, T, C, false),
+                     biwkv::resident::workspace_bytes(B, T, C, false)});
 }
 
 int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
@@ -95,6 +95,8 @@ int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u,
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_forward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, y}, false))
+        return finish(biwkv::resident::forward(B, T, C, w, u, k, v, y, workspace, s));
     if (g_path.load() != 1 && biwkv::fused::eligible(B, T, C, {k, v, y}))
         return finish(biwkv::fused::forward(B, T, C, w, u, k, v, y, workspace, s));
     // generic path: status word (first 256 bytes) is cleared, scratch follows
@@ -104,8 +106,8 @@ int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u,
 
 size_t vrwkv_biwkv_backward_workspace_bytes(int B, int T, int C) {
     if (check_shape(B, T, C) != VRWKV_OK) return 0;
-    return std::max(biwkv::generic_backward_workspace(B, T, C) + 256,
-                    biwkv::fused::workspace_bytes(B, T, C, true));
+    return std::max({biwkv::generic_backward_workspace(B, T, C) + 256, biwkv::fused::workspace_bytes(B, T, C, true),
+                     biwkv::resident::workspace_bytes(B, T, C, true)});
 }
 
 int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
@@ -118,6 +120,8 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_backward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, gy, gk, gv}, true))
+        return finish(biwkv::resident::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s));
     if (g_path.load() != 1 && biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}))
         return finish(biwkv::fused::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s));
     cudaMemsetAsync(workspace, 0, 256, s);

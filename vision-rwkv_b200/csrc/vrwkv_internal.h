@@ -18,6 +18,17 @@ int generic_forward(int B, int T, int C, const float* w, const float* u, const f
 int generic_backward(int B, int T, int C, const float* w, const float* u, const float* k,
                      const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                      void* workspace, cudaStream_t stream);
+namespace resident {
+// Cluster-resident single-pass path (biwkv_resident.cu): float32, C % 4 == 0, 16-byte aligned
+// tensors, T <= 4096.  True when it can serve this call on the current device.
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd);
+size_t workspace_bytes(int B, int T, int C, bool bwd);
+int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+            float* y, void* workspace, cudaStream_t stream);
+int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+             const float* gy, float* gwgu, float* gk, float* gv, void* workspace,
+             cudaStream_t stream);
+}  // namespace resident
 namespace fused {
 // True when the fused TMA path can serve this call on the current device.
 bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bf16 = false);
