@@ -4,35 +4,37 @@
 // cluster's own CTAs ever has to be waited for.
 //
 // Work unit: one (sequence b, strip of kCs = 32 channels).  A cluster of `cluster` CTAs (1, 2, 4, 8
-// or 16) splits its T tokens into contiguous ranges of n_tok = 16 * n_warps tokens, one per CTA.
-// Inside a CTA warp s owns the sub-chunk of kL = 16 tokens [16 s, 16 s + 16), its lane the channel;
-// a thread walks its 16 tokens sequentially out of shared memory (rows of 32 floats: conflict-free).
-// One TMA box per tensor and CTA brings the range in (zero fill past T and C), outputs overwrite
-// the inputs in place and leave by TMA store (clipped).
+// or 16) splits its T tokens into contiguous ranges of n_tok = 32 * n_warps tokens, one per CTA.
+// Inside a CTA warp s owns the span of 32 tokens [32 s, 32 s + 32); its lower half-warp walks the
+// first kL = 16 tokens of the span, its upper half-warp the last 16; lane p of a half-warp owns the
+// channel pair (2p, 2p+1).  A thread walks its 16 tokens sequentially with 64-bit shared accesses
+// (a half-warp reads one whole 128-byte row), and carries its two channels packed in f32x2
+// registers, so one instruction serves both.  One TMA box per tensor and CTA brings the range in
+// (zero fill past T and C); outputs overwrite the inputs in place and leave by TMA store (clipped).
 //
 // A bidirectional scan needs, at each token, the decayed sum over all earlier and all later tokens.
 // Per scan level:
-//   1. every thread posts the aggregate of its sub-chunk (towards later tokens, and towards
-//      earlier ones) to shared memory;
-//   2. two warps walk the sub-chunk aggregates of the CTA serially (one per direction), leave in
-//      place the state entering each sub-chunk from the rest of the CTA, and put the CTA's own
-//      aggregate where the other CTAs of the cluster can read it;
-//   3. barrier.cluster; the same two warps read the aggregates of the lower / higher ranked CTAs
-//      through distributed shared memory (plain ld.shared::cluster, no multicast) and combine them;
+//   1. the two half-warps of a warp combine their sub-chunk aggregates by shuffles and post the
+//      aggregate of the 32-token span (towards later tokens, and towards earlier ones);
+//   2. two warps walk the span aggregates of the CTA serially (one per direction, lane = channel),
+//      leave in place the state entering each span from the rest of the CTA, and send the CTA's own
+//      aggregate to the CTAs that need it: st.async into their shared memory, completion counted
+//      in bytes on their mbarrier (one hop through the cluster network, no fence, no multicast);
+//   3. the same two warps wait (bounded) for the bytes of the other CTAs and combine them;
 //   4. every thread adds the outside state, moved to its own position, to its inside state.
 // Forward: one level (terms e^{k}[v, 1]).  Backward: a second level for the adjoint pairs
 // [gy / Den, gy y / Den]; nothing is kept from the forward, y and Den are recomputed.
 //
 // Arithmetic.  The fast path works on plain floats without any exponent shift: a term is
 // lambda e^{k} [v, 1] with lambda = e^{-w}, recurrences are one packed fused multiply-add per token
-// and direction (numerator | denominator in one f32x2 instruction).  That is exact enough whenever
-// 2 max|k| + |u| + |w| + max(-w, 0) T <= 60 (no overflow, no harmful underflow in float32).
-// Every thread checks its own tokens, the cluster takes the OR of all checks with the first
-// exchange, and if any thread saw otherwise the whole cluster redoes the unit with the per-token
-// max-shifted (value, exponent) arithmetic of biwkv_math.cuh (k and v are fetched again, since the
-// fast path overwrote them in place).  Decay over long distances never comes from repeated
-// multiplication by a rounded lambda: the per-channel factors for 16 and n_tok tokens are computed
-// once per CTA in double precision and applied as a (high, low) float pair.
+// and direction.  That is exact enough whenever 2 max|k| + |u| + |w| + max(-w, 0) T <= 60 (no
+// overflow, no harmful underflow in float32).  Every thread checks its own tokens, the cluster
+// takes the OR of all checks with the first exchange, and if any thread saw otherwise the whole
+// cluster redoes the unit with the per-token max-shifted (value, exponent) arithmetic of
+// biwkv_math.cuh (k and v are fetched again, since the fast path overwrote them in place).  Decay
+// over long distances never comes from repeated multiplication by a rounded lambda: the
+// per-channel factors for 16, 32 and n_tok tokens are computed once per CTA in double precision
+// and applied as a (high, low) float pair.
 //
 // Recurrence restated: classification/mmcls_custom/models/backbones/cuda_new/
 // bi_wkv_kernel.cu:21-116 (forward), :119-367 (gradients).
@@ -51,43 +53,50 @@ namespace biwkv {
 namespace resident {
 
 constexpr int kL = 16;            // tokens per thread
-constexpr int kCs = 32;           // channels per strip (= lanes)
-constexpr int kMaxWarps = 16;     // sub-chunks per CTA
+constexpr int kSpan = 2 * kL;     // tokens per warp
+constexpr int kCs = 32;           // channels per strip
+constexpr int kMaxWarps = 8;      // spans per CTA
 constexpr int kMaxCluster = 16;
 constexpr int kMaxThreads = kMaxWarps * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kSafeRange = 60.f;
-constexpr uint32_t kSpinLimit = 1u << 20;   // ~0.1 s of polling on a TMA barrier
-constexpr int kConstRows = 8;
+constexpr uint32_t kSpinLimit = 1u << 20;   // ~0.1 s of polling on a barrier
+
+// per-channel constants, computed once per CTA by warp 0 in double precision (rows of kCs floats)
+enum ConstRow {
+    kLam = 0, kWl2, kCuw, kInvLam, kLam16_hi, kLam16_lo, kLam32_hi, kLam32_lo, kLamC_hi, kLamC_lo, kConstRows
+};
 
 // rows of kCs floats in the record area behind the data slots
 template <bool kBwd>
 struct Rows {
     static constexpr int kF = kBwd ? 4 : 2;       // towards later tokens: a, b (, first moments)
     static constexpr int kR = 2;                  // towards earlier tokens: a, b
-    static constexpr int kSub = kF + kR;          // per sub-chunk
-    static constexpr int kAgg = kF + kR + 1;      // CTA aggregate + one row for the flag
+    static constexpr int kSub = kF + kR;          // per span
     static constexpr int kLevels = kBwd ? 2 : 1;
     static constexpr int kSlots = kBwd ? 3 : 2;
+    static constexpr int kPeerFloats = kMaxCluster * kCs * kF;   // one record slot per rank and channel
 };
 
 struct Params {
     int B, T, C;
     int n_strips;
     int cluster;      // CTAs per (sequence, strip)
-    int n_warps;      // sub-chunks per CTA
-    int n_tok;        // tokens per CTA = n_warps * kL
+    int n_warps;      // 32-token spans per CTA
+    int n_tok;        // tokens per CTA = n_warps * kSpan
     const float* w;
     const float* u;
     unsigned* status;   // device status word
     float* partial;     // backward: [grid][2][kCs]
 };
 
+// shared memory: data slots | span records | records received from the other CTAs | flags row |
+// state entering this CTA | constants | mbarriers
 template <bool kBwd>
 static inline size_t smem_bytes(int n_warps) {
     using R = Rows<kBwd>;
-    const size_t data = static_cast<size_t>(R::kSlots) * n_warps * kL * kCs * sizeof(float);
-    const size_t rec = (static_cast<size_t>(n_warps) * R::kSub + R::kLevels * R::kAgg + R::kAgg + kConstRows) * kCs * sizeof(float);
+    const size_t data = static_cast<size_t>(R::kSlots) * n_warps * kSpan * kCs * sizeof(float);
+    const size_t rec = (static_cast<size_t>(n_warps) * R::kSub * kCs + R::kPeerFloats + kCs + R::kSub * kCs + kConstRows * kCs) * sizeof(float);
     return data + rec + 64;
 }
 
@@ -103,9 +112,14 @@ __device__ __forceinline__ float rcp(float x) {
     return y;
 }
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 dup(float a) { return make_float2(a, a); }
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 shfl2(float2 a, int mask) {
+    return f2(__shfl_xor_sync(0xffffffffu, a.x, mask), __shfl_xor_sync(0xffffffffu, a.y, mask));
+}
+__device__ __forceinline__ float2 sel2(bool c, float2 a, float2 b) { return c ? a : b; }
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -113,6 +127,7 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     return r;
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // address of the same shared-memory location in the CTA of rank `rank` of this cluster
 __device__ __forceinline__ uint32_t peer_addr(const void* local, uint32_t rank) {
@@ -125,42 +140,107 @@ __device__ __forceinline__ float ld_peer(uint32_t addr) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
     return v;
 }
+// Asynchronous stores into another CTA's shared memory; the receiving CTA's mbarrier counts the
+// bytes, so data and notification travel together and the sender needs no fence.
+__device__ __forceinline__ void st_async4(uint32_t addr, float4 v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(addr),
+                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void st_async2(uint32_t addr, float2 v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(addr), "f"(v.x),
+                 "f"(v.y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void st_async1(uint32_t addr, uint32_t v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(bar)
+                 : "memory");
+}
+
+// Debug timeline: with -DVRWKV_TIMELINE lane 0 of warps 0 and 5 of the first kTlCtas CTAs and of
+// kTlCtas CTAs from the middle of the grid store clock64() at each phase boundary behind the
+// workspace's status block.  Compiled out otherwise.
+#ifdef VRWKV_TIMELINE
+constexpr int kTlCtas = 64, kTlMarks = 24;
+#define TL_MARK(m)                                                                                         \
+    do {                                                                                                   \
+        if (tl_slot >= 0 && lane == 0 && (warp == 0 || warp == 5))                                          \
+            tl_base[((tl_slot * 2 + (warp ? 1 : 0)) * kTlMarks) + (m)] = clock64();                         \
+    } while (0)
+#define TL_ARGS , long long* tl_base, int tl_slot
+#define TL_PASS , tl_base, tl_slot
+#else
+#define TL_MARK(m) do { } while (0)
+#define TL_ARGS
+#define TL_PASS
+#endif
 
 struct Ctx {
     float* sub;      // [n_warps][kSub][kCs]; rows 0..kF-1 towards later tokens, kF.. towards earlier
-    float* agg;      // [kLevels][kAgg][kCs]
-    float* cta;      // [kAgg][kCs]: state entering this CTA from the rest of the cluster
+    float* peers;    // [kMaxCluster][kCs][kF]: records received from the other CTAs (directly behind sub)
+    float* flags;    // [kCs] words: entry r = out-of-range flag of rank r
+    float* cta;      // [kSub][kCs]: state entering this CTA from the rest of the cluster
     float* consts;   // [kConstRows][kCs]
+    uint64_t* xbar;  // [kLevels] mbarriers counting the bytes the other CTAs send
+    unsigned* status;
     int warp, lane, n_warps, n_tok, cluster, rank;
 };
 
-// per-channel constants, computed once per CTA by warp 0 in double precision
-enum ConstRow { kLam = 0, kWl2 = 1, kCuw = 2, kInvLam = 3, kLamL_hi = 4, kLamL_lo = 5, kLamC_hi = 6, kLamC_lo = 7 };
-
+// a thread's two channels: numerators (n) and denominators (d) of a state, each packed (ch 2p, ch 2p+1)
+struct Pair2 {
+    float2 n, d;
+};
 struct Enter {
-    float2 P, MP, S;   // state (and first moment) entering at the first token; state entering at the last
+    Pair2 P, MP, S;   // state (and first moment) entering at the first token; state entering at the last
 };
 
-// One exchange level on plain floats (steps 1-4 of the file header).  F / MF: this sub-chunk's
-// aggregate relative to the first token after it (and its first moment in distance), R: relative
-// to the last token before it.  Returns with `unsafe` = OR over the cluster of `unsafe`.
+// x * (hi + lo) + y, both channels
+__device__ __forceinline__ float2 mulc_add(float2 x, float2 hi, float2 lo, float2 y) { return fma2(x, hi, fma2(x, lo, y)); }
+
+// One exchange level on plain floats (steps 1-4 of the file header).  F / MF: this thread's sub-chunk
+// aggregate relative to the first token after its 16 tokens (and its first moment in distance), R:
+// relative to the last token before them.  Returns with `unsafe` = OR over the cluster of `unsafe`
+// (level 0 only).
 template <bool kBwd>
-__device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, float2 F, float2 MF, float2 R, bool& unsafe) {
+__device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F, Pair2 MF, Pair2 R, bool& unsafe TL_ARGS) {
     using RW = Rows<kBwd>;
     constexpr bool kMom = kBwd;
     const int lane = c.lane, warp = c.warp, nw = c.n_warps;
+    const int p = lane & 15;
+    const bool upper = lane >= 16;
+    const float2 l16h = *reinterpret_cast<const float2*>(c.consts + kLam16_hi * kCs + 2 * p);
+    const float2 l16l = *reinterpret_cast<const float2*>(c.consts + kLam16_lo * kCs + 2 * p);
+    const float2 len16 = dup(static_cast<float>(kL));
+    // (1) the two halves of the span combine through shuffles; the lower half-warp posts the span record
+    Pair2 keepA, keepM;        // what this thread needs of its partner afterwards
     {
-        float* s = c.sub + warp * (RW::kSub * kCs) + lane;
-        s[0] = F.x; s[kCs] = F.y;
-        if (kMom) { s[2 * kCs] = MF.x; s[3 * kCs] = MF.y; }
-        s[RW::kF * kCs] = R.x; s[(RW::kF + 1) * kCs] = R.y;
+        const Pair2 oF{shfl2(F.n, 16), shfl2(F.d, 16)};
+        const Pair2 oR{shfl2(R.n, 16), shfl2(R.d, 16)};
+        Pair2 oMF{f2(0.f, 0.f), f2(0.f, 0.f)};
+        if (kMom) oMF = Pair2{shfl2(MF.n, 16), shfl2(MF.d, 16)};
+        keepA = upper ? oF : oR;      // upper half: the lower half's F; lower half: the upper half's R
+        keepM = oMF;                  // upper half: the lower half's first moments
+        if (!upper) {
+            // F, MF, R are the lower half's, oF, oMF, oR the upper half's
+            float* s = c.sub + warp * (RW::kSub * kCs) + 2 * p;
+            *reinterpret_cast<float2*>(s) = mulc_add(F.n, l16h, l16l, oF.n);
+            *reinterpret_cast<float2*>(s + kCs) = mulc_add(F.d, l16h, l16l, oF.d);
+            if (kMom) {
+                *reinterpret_cast<float2*>(s + 2 * kCs) = mulc_add(fma2(len16, F.n, MF.n), l16h, l16l, oMF.n);
+                *reinterpret_cast<float2*>(s + 3 * kCs) = mulc_add(fma2(len16, F.d, MF.d), l16h, l16l, oMF.d);
+            }
+            *reinterpret_cast<float2*>(s + RW::kF * kCs) = mulc_add(oR.n, l16h, l16l, R.n);
+            *reinterpret_cast<float2*>(s + (RW::kF + 1) * kCs) = mulc_add(oR.d, l16h, l16l, R.d);
+        }
     }
     const int any = __syncthreads_or(unsafe ? 1 : 0);
+    TL_MARK(12 + level * 5);
+    // (2) serial walk over the spans, one warp per direction, lane = channel, state = (a, b)
     const int scanF = 0, scanR = nw > 1 ? 1 : 0;
-    float* agg = c.agg + level * (RW::kAgg * kCs);
+    const uint32_t bar_delta = sm100::smem_u32(c.xbar + level) - sm100::smem_u32(c.peers);
     if (warp == scanF) {
-        const float hi = c.consts[kLamL_hi * kCs + lane], lo = c.consts[kLamL_lo * kCs + lane];
-        const float2 hi2 = f2(hi, hi), lo2 = f2(lo, lo), len2 = f2(static_cast<float>(kL), static_cast<float>(kL));
+        const float2 hi2 = dup(c.consts[kLam32_hi * kCs + lane]), lo2 = dup(c.consts[kLam32_lo * kCs + lane]);
+        const float2 len2 = dup(static_cast<float>(kSpan));
         float2 P = f2(0.f, 0.f), M = f2(0.f, 0.f);
 #pragma unroll 4
         for (int s = 0; s < nw; ++s) {
@@ -170,112 +250,114 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, float2 F
             if (kMom) {
                 const float2 mf = f2(q[2 * kCs], q[3 * kCs]);
                 q[2 * kCs] = M.x; q[3 * kCs] = M.y;
-                const float2 t = fma2(len2, P, M);
-                M = fma2(t, hi2, fma2(t, lo2, mf));
+                M = mulc_add(fma2(len2, P, M), hi2, lo2, mf);
             }
-            P = fma2(P, hi2, fma2(P, lo2, f));
+            P = mulc_add(P, hi2, lo2, f);
         }
-        agg[lane] = P.x; agg[kCs + lane] = P.y;
-        if (kMom) { agg[2 * kCs + lane] = M.x; agg[3 * kCs + lane] = M.y; }
-        if (lane == 0) agg[(RW::kF + RW::kR) * kCs] = __int_as_float(any);
+        // the CTA's aggregate goes to every higher rank; the flag to every other rank
+        for (int r = c.rank + 1; r < c.cluster; ++r) {
+            const uint32_t rb = peer_addr(c.peers, r);
+            const uint32_t dst = rb + static_cast<uint32_t>((c.rank * kCs + lane) * RW::kF) * 4u;
+            if (kMom) st_async4(dst, make_float4(P.x, P.y, M.x, M.y), rb + bar_delta);
+            else st_async2(dst, P, rb + bar_delta);
+        }
+        if (level == 0 && lane < c.cluster && lane != c.rank) {
+            const uint32_t rb = peer_addr(c.peers, lane);
+            st_async1(rb + (sm100::smem_u32(c.flags + c.rank) - sm100::smem_u32(c.peers)), static_cast<uint32_t>(any), rb + bar_delta);
+        }
     }
     if (warp == scanR) {
-        const float hi = c.consts[kLamL_hi * kCs + lane], lo = c.consts[kLamL_lo * kCs + lane];
-        const float2 hi2 = f2(hi, hi), lo2 = f2(lo, lo);
+        const float2 hi2 = dup(c.consts[kLam32_hi * kCs + lane]), lo2 = dup(c.consts[kLam32_lo * kCs + lane]);
         float2 S = f2(0.f, 0.f);
 #pragma unroll 4
         for (int s = nw - 1; s >= 0; --s) {
             float* q = c.sub + s * (RW::kSub * kCs) + RW::kF * kCs + lane;
             const float2 r = f2(q[0], q[kCs]);
             q[0] = S.x; q[kCs] = S.y;
-            S = fma2(S, hi2, fma2(S, lo2, r));
+            S = mulc_add(S, hi2, lo2, r);
         }
-        agg[RW::kF * kCs + lane] = S.x; agg[(RW::kF + 1) * kCs + lane] = S.y;
+        for (int r = 0; r < c.rank; ++r) {
+            const uint32_t rb = peer_addr(c.peers, r);
+            st_async2(rb + static_cast<uint32_t>((c.rank * kCs + lane) * RW::kF) * 4u, S, rb + bar_delta);
+        }
     }
-    if (c.cluster > 1) {
-        cluster_arrive();
-        cluster_wait();
+    TL_MARK(13 + level * 5);
+    // (3) wait for the other CTAs' bytes, combine them
+    if (c.cluster > 1 && (warp == scanF || warp == scanR)) {
+        if (!sm100::mbar_wait(c.xbar + level, 0, kSpinLimit) && lane == 0) atomicOr(c.status, 1u);
     }
+    TL_MARK(14 + level * 5);
     if (warp == scanF) {
         float2 X = f2(0.f, 0.f), MX = f2(0.f, 0.f);
-        int flag = 0;
+        int flag = any;
         if (c.cluster > 1) {
-            const float hi = c.consts[kLamC_hi * kCs + lane], lo = c.consts[kLamC_lo * kCs + lane];
-            const float2 hi2 = f2(hi, hi), lo2 = f2(lo, lo);
-            const float n = static_cast<float>(c.n_tok);
-            const float2 len2 = f2(n, n);
-            for (int r0 = 0; r0 < c.rank; r0 += 4) {
-                float2 f[4], mf[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    f[j] = f2(0.f, 0.f);
-                    mf[j] = f2(0.f, 0.f);
-                    if (r0 + j < c.rank) {
-                        const uint32_t a = peer_addr(agg + lane, r0 + j);
-                        f[j] = f2(ld_peer(a), ld_peer(a + kCs * 4));
-                        if (kMom) mf[j] = f2(ld_peer(a + 2 * kCs * 4), ld_peer(a + 3 * kCs * 4));
-                    }
+            const float2 hi2 = dup(c.consts[kLamC_hi * kCs + lane]), lo2 = dup(c.consts[kLamC_lo * kCs + lane]);
+            const float2 len2 = dup(static_cast<float>(c.n_tok));
+#pragma unroll 4
+            for (int r = 0; r < c.rank; ++r) {
+                const float* q = c.peers + (r * kCs + lane) * RW::kF;
+                float2 f, mf = f2(0.f, 0.f);
+                if (kMom) {
+                    const float4 t = *reinterpret_cast<const float4*>(q);
+                    f = f2(t.x, t.y);
+                    mf = f2(t.z, t.w);
+                    MX = mulc_add(fma2(len2, X, MX), hi2, lo2, mf);
+                } else {
+                    f = *reinterpret_cast<const float2*>(q);
                 }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (r0 + j < c.rank) {
-                        if (kMom) {
-                            const float2 t = fma2(len2, X, MX);
-                            MX = fma2(t, hi2, fma2(t, lo2, mf[j]));
-                        }
-                        X = fma2(X, hi2, fma2(X, lo2, f[j]));
-                    }
-                }
+                X = mulc_add(X, hi2, lo2, f);
             }
-            // one lane per rank fetches that rank's flag (all ranks: this warp decides for the CTA)
-            if (lane < c.cluster) flag = __float_as_int(ld_peer(peer_addr(agg + (RW::kF + RW::kR) * kCs, lane)));
-            flag = __any_sync(0xffffffffu, flag != 0) ? 1 : 0;
-        } else {
-            flag = any;
+            if (level == 0) {
+                int other = (lane < c.cluster && lane != c.rank) ? __float_as_int(c.flags[lane]) : 0;
+                flag = __any_sync(0xffffffffu, (other | any) != 0) ? 1 : 0;
+            }
         }
         c.cta[lane] = X.x; c.cta[kCs + lane] = X.y;
         if (kMom) { c.cta[2 * kCs + lane] = MX.x; c.cta[3 * kCs + lane] = MX.y; }
-        if (lane == 0) c.cta[(RW::kF + RW::kR) * kCs] = __int_as_float(flag);
+        if (lane == 0) c.flags[c.rank] = __int_as_float(flag);
     }
     if (warp == scanR) {
         float2 Y = f2(0.f, 0.f);
         if (c.cluster > 1) {
-            const float hi = c.consts[kLamC_hi * kCs + lane], lo = c.consts[kLamC_lo * kCs + lane];
-            const float2 hi2 = f2(hi, hi), lo2 = f2(lo, lo);
-            for (int r0 = c.cluster - 1; r0 > c.rank; r0 -= 4) {
-                float2 f[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    f[j] = f2(0.f, 0.f);
-                    if (r0 - j > c.rank) {
-                        const uint32_t a = peer_addr(agg + RW::kF * kCs + lane, r0 - j);
-                        f[j] = f2(ld_peer(a), ld_peer(a + kCs * 4));
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (r0 - j > c.rank) Y = fma2(Y, hi2, fma2(Y, lo2, f[j]));
-            }
+            const float2 hi2 = dup(c.consts[kLamC_hi * kCs + lane]), lo2 = dup(c.consts[kLamC_lo * kCs + lane]);
+#pragma unroll 4
+            for (int r = c.cluster - 1; r > c.rank; --r)
+                Y = mulc_add(Y, hi2, lo2, *reinterpret_cast<const float2*>(c.peers + (r * kCs + lane) * RW::kF));
         }
         c.cta[RW::kF * kCs + lane] = Y.x; c.cta[(RW::kF + 1) * kCs + lane] = Y.y;
     }
+    TL_MARK(15 + level * 5);
     __syncthreads();
+    TL_MARK(16 + level * 5);
+    // (4) outside state moved to this span's edges + inside state; then to this half's edges
     Enter e;
     {
-        const float wl2 = c.consts[kWl2 * kCs + lane];
-        const float dP = static_cast<float>(kL * warp), dS = static_cast<float>(kL * (nw - 1 - warp));
-        const float pP = ex2(-wl2 * dP), pS = ex2(-wl2 * dS);
-        const float* s = c.sub + warp * (RW::kSub * kCs) + lane;
-        const float2 X = f2(c.cta[lane], c.cta[kCs + lane]);
-        e.P = fma2(f2(pP, pP), X, f2(s[0], s[kCs]));
-        e.MP = f2(0.f, 0.f);
+        const float2 wl2 = *reinterpret_cast<const float2*>(c.consts + kWl2 * kCs + 2 * p);
+        const float dP = static_cast<float>(kSpan * warp), dS = static_cast<float>(kSpan * (nw - 1 - warp));
+        const float2 pP = f2(ex2(-wl2.x * dP), ex2(-wl2.y * dP)), pS = f2(ex2(-wl2.x * dS), ex2(-wl2.y * dS));
+        const float* s = c.sub + warp * (RW::kSub * kCs) + 2 * p;
+        const float* g = c.cta + 2 * p;
+        const float2 Xn = *reinterpret_cast<const float2*>(g), Xd = *reinterpret_cast<const float2*>(g + kCs);
+        Pair2 Pw{fma2(pP, Xn, *reinterpret_cast<const float2*>(s)), fma2(pP, Xd, *reinterpret_cast<const float2*>(s + kCs))};
+        Pair2 MPw{f2(0.f, 0.f), f2(0.f, 0.f)};
         if (kMom) {
-            const float2 MX = f2(c.cta[2 * kCs + lane], c.cta[3 * kCs + lane]);
-            e.MP = fma2(f2(pP, pP), fma2(f2(dP, dP), X, MX), f2(s[2 * kCs], s[3 * kCs]));
+            const float2 MXn = *reinterpret_cast<const float2*>(g + 2 * kCs), MXd = *reinterpret_cast<const float2*>(g + 3 * kCs);
+            MPw.n = fma2(pP, fma2(dup(dP), Xn, MXn), *reinterpret_cast<const float2*>(s + 2 * kCs));
+            MPw.d = fma2(pP, fma2(dup(dP), Xd, MXd), *reinterpret_cast<const float2*>(s + 3 * kCs));
         }
-        const float2 Y = f2(c.cta[RW::kF * kCs + lane], c.cta[(RW::kF + 1) * kCs + lane]);
-        e.S = fma2(f2(pS, pS), Y, f2(s[RW::kF * kCs], s[(RW::kF + 1) * kCs]));
-        unsafe = __float_as_int(c.cta[(RW::kF + RW::kR) * kCs]) != 0;
+        const float2 Yn = *reinterpret_cast<const float2*>(g + RW::kF * kCs), Yd = *reinterpret_cast<const float2*>(g + (RW::kF + 1) * kCs);
+        Pair2 Sw{fma2(pS, Yn, *reinterpret_cast<const float2*>(s + RW::kF * kCs)),
+                 fma2(pS, Yd, *reinterpret_cast<const float2*>(s + (RW::kF + 1) * kCs))};
+        if (upper) {
+            e.P = Pair2{mulc_add(Pw.n, l16h, l16l, keepA.n), mulc_add(Pw.d, l16h, l16l, keepA.d)};
+            e.MP = Pair2{mulc_add(fma2(len16, Pw.n, MPw.n), l16h, l16l, keepM.n), mulc_add(fma2(len16, Pw.d, MPw.d), l16h, l16l, keepM.d)};
+            e.S = Sw;
+        } else {
+            e.P = Pw;
+            e.MP = MPw;
+            e.S = Pair2{mulc_add(Sw.n, l16h, l16l, keepA.n), mulc_add(Sw.d, l16h, l16l, keepA.d)};
+        }
+        if (level == 0) unsafe = __float_as_int(c.flags[c.rank]) != 0;
     }
     return e;
 }
@@ -287,6 +369,7 @@ struct Entering {
 };
 
 __device__ __forceinline__ void cluster_or_cta_sync(const Ctx& c) {
+    __syncwarp();
     if (c.cluster > 1) {
         cluster_arrive();
         cluster_wait();
@@ -295,82 +378,87 @@ __device__ __forceinline__ void cluster_or_cta_sync(const Ctx& c) {
     }
 }
 
-// Two rounds (one per direction) over the same record area; every thread walks the records it
-// needs itself.  Slow and simple: this path only runs for inputs outside the fast path's range.
+// One channel per thread and call: sub = index of the thread's 16-token sub-chunk in the CTA, ch = its
+// channel within the strip.  Two rounds (one per direction) over the same record area (the span
+// records and the area behind them); every thread walks the records it needs itself and reads the
+// other CTAs' aggregates out of their shared memory.  Slow and simple: this path only runs for
+// inputs outside the fast path's range.
 // kMom = false (forward): the first moments are not carried, a record is 3 rows in both rounds.
 template <bool kMom>
-__device__ __noinline__ Entering exact_exchange(const Ctx& c, float w, const Acc4 own_right, const Acc2 own_left) {
-    const int lane = c.lane, warp = c.warp, nw = c.n_warps;
+__device__ __noinline__ Entering exact_exchange(const Ctx& c, int sub, int ch, float w, const Acc4 own_right, const Acc2 own_left) {
+    const int n_sub = 2 * c.n_warps;
     constexpr int kRec = kMom ? 5 : 3;
-    float* area = c.sub;      // [n_warps][kRec][kCs], then [n_warps][3][kCs]
-    float* agg = c.agg;       // kRec rows
+    float* area = c.sub;      // [n_sub][kRec][kCs], then [n_sub][3][kCs]
+    float* agg = c.cta;       // kRec rows
     Entering out;
     {
-        float* s = area + warp * kRec * kCs + lane;
+        float* s = area + sub * kRec * kCs + ch;
         s[0] = own_right.a; s[kCs] = own_right.b; s[(kRec - 1) * kCs] = own_right.o;
         if (kMom) { s[2 * kCs] = own_right.ma; s[3 * kCs] = own_right.mb; }
+        __syncwarp();
         __syncthreads();
         Acc4 X = acc4_zero();
-        for (int j = 0; j < warp; ++j) {
-            const float* q = area + j * kRec * kCs + lane;
+        for (int j = 0; j < sub; ++j) {
+            const float* q = area + j * kRec * kCs + ch;
             acc4_decay(X, w, static_cast<float>(kL));
             X = acc4_merge(X, Acc4{q[0], q[kCs], kMom ? q[2 * kCs] : 0.f, kMom ? q[3 * kCs] : 0.f, q[(kRec - 1) * kCs]});
         }
-        if (warp == nw - 1) {
+        if (sub == n_sub - 1) {
             Acc4 t = X;
             acc4_decay(t, w, static_cast<float>(kL));
             t = acc4_merge(t, own_right);
-            agg[lane] = t.a; agg[kCs + lane] = t.b; agg[(kRec - 1) * kCs + lane] = t.o;
-            if (kMom) { agg[2 * kCs + lane] = t.ma; agg[3 * kCs + lane] = t.mb; }
+            agg[ch] = t.a; agg[kCs + ch] = t.b; agg[(kRec - 1) * kCs + ch] = t.o;
+            if (kMom) { agg[2 * kCs + ch] = t.ma; agg[3 * kCs + ch] = t.mb; }
         }
         cluster_or_cta_sync(c);
         Acc4 Y = acc4_zero();
         for (int r = 0; r < c.rank; ++r) {
-            const uint32_t a = peer_addr(agg + lane, r);
+            const uint32_t a = peer_addr(agg + ch, r);
             acc4_decay(Y, w, static_cast<float>(c.n_tok));
             Y = acc4_merge(Y, Acc4{ld_peer(a), ld_peer(a + kCs * 4), kMom ? ld_peer(a + 2 * kCs * 4) : 0.f,
                                    kMom ? ld_peer(a + 3 * kCs * 4) : 0.f, ld_peer(a + (kRec - 1) * kCs * 4)});
         }
-        acc4_decay(Y, w, static_cast<float>(kL * warp));
+        acc4_decay(Y, w, static_cast<float>(kL * sub));
         out.left = acc4_merge(Y, X);
         cluster_or_cta_sync(c);
     }
     {
-        float* s = area + warp * 3 * kCs + lane;
+        float* s = area + sub * 3 * kCs + ch;
         s[0] = own_left.a; s[kCs] = own_left.b; s[2 * kCs] = own_left.o;
+        __syncwarp();
         __syncthreads();
         Acc2 Z = acc2_zero();
-        for (int j = nw - 1; j > warp; --j) {
-            const float* q = area + j * 3 * kCs + lane;
+        for (int j = n_sub - 1; j > sub; --j) {
+            const float* q = area + j * 3 * kCs + ch;
             acc2_decay(Z, w, static_cast<float>(kL));
             Z = acc2_merge(Z, Acc2{q[0], q[kCs], q[2 * kCs]});
         }
-        if (warp == 0) {
+        if (sub == 0) {
             Acc2 t = Z;
             acc2_decay(t, w, static_cast<float>(kL));
             t = acc2_merge(t, own_left);
-            agg[lane] = t.a; agg[kCs + lane] = t.b; agg[2 * kCs + lane] = t.o;
+            agg[ch] = t.a; agg[kCs + ch] = t.b; agg[2 * kCs + ch] = t.o;
         }
         cluster_or_cta_sync(c);
         Acc2 Y = acc2_zero();
         for (int r = c.cluster - 1; r > c.rank; --r) {
-            const uint32_t a = peer_addr(agg + lane, r);
+            const uint32_t a = peer_addr(agg + ch, r);
             acc2_decay(Y, w, static_cast<float>(c.n_tok));
             Y = acc2_merge(Y, Acc2{ld_peer(a), ld_peer(a + kCs * 4), ld_peer(a + 2 * kCs * 4)});
         }
-        acc2_decay(Y, w, static_cast<float>(kL * (nw - 1 - warp)));
+        acc2_decay(Y, w, static_cast<float>(kL * (n_sub - 1 - sub)));
         out.right = acc2_merge(Y, Z);
         cluster_or_cta_sync(c);
     }
     return out;
 }
 
-// One thread's sub-chunk on the exact path: ks / vs / gs point at its first token (stride kCs),
-// n = valid tokens.  Sweeps are position-anchored (biwkv_math.cuh).  Forward: y into ks.
-// Backward: gk into ks, gv into vs, the thread's gw / gu shares returned.
+// One channel of one thread's sub-chunk on the exact path: ks / vs / gs point at its first token
+// (stride kCs), n = valid tokens.  Sweeps are position-anchored (biwkv_math.cuh).  Forward: y into
+// ks.  Backward: gk into ks, gv into vs, the thread's gw / gu shares returned.
 template <bool kBwd>
-__device__ __noinline__ void exact_subchunk(const Ctx& c, float* ks, float* vs, float* gs, int n, float w, float u,
-                                            float& gw_out, float& gu_out) {
+__device__ __noinline__ void exact_subchunk(const Ctx& c, int sub, int ch, float* ks, float* vs, float* gs, int n, float w,
+                                            float u, float& gw_out, float& gu_out) {
     const float last = static_cast<float>(n - 1);
     Acc4 right = acc4_zero();
     Acc2 left = acc2_zero();
@@ -380,7 +468,7 @@ __device__ __noinline__ void exact_subchunk(const Ctx& c, float* ks, float* vs, 
     right.o -= w * static_cast<float>(n);
     acc4_decay(right, w, static_cast<float>(kL - n));
     left.o -= w;
-    const Entering e1 = exact_exchange<kBwd>(c, w, right, left);
+    const Entering e1 = exact_exchange<kBwd>(c, sub, ch, w, right, left);
     const Acc4 P4 = e1.left;                         // anchored at token 0
     Acc2 S = e1.right;
     acc2_decay(S, w, static_cast<float>(kL - n));   // given at position kL-1; anchor it at token n-1
@@ -421,7 +509,7 @@ __device__ __noinline__ void exact_subchunk(const Ctx& c, float* ks, float* vs, 
     later.o -= w * static_cast<float>(n);
     acc4_decay(later, w, static_cast<float>(kL - n));
     earlier.o -= w;
-    const Entering e2 = exact_exchange<kBwd>(c, w, later, earlier);
+    const Entering e2 = exact_exchange<kBwd>(c, sub, ch, w, later, earlier);
     Acc4 R = e2.left;                                // anchored at token 0
     Acc2 Q = e2.right;
     acc2_decay(Q, w, static_cast<float>(kL - n));   // anchored at token n-1
@@ -452,7 +540,7 @@ __device__ __noinline__ void exact_subchunk(const Ctx& c, float* ks, float* vs, 
 // kStash: tokens whose leftward state a thread keeps in registers at a time (16: one reverse sweep
 // per sub-chunk; 8: the second half is swept twice, for half the registers).
 template <bool kBwd, int kStash>
-__global__ void __launch_bounds__(kMaxThreads, 2)
+__global__ void __launch_bounds__(kMaxThreads, kBwd ? 2 : 3)
 biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __grid_constant__ CUtensorMap map_g,     // backward: gy
                       const __grid_constant__ CUtensorMap map_o0,    // forward: y ; backward: gk
@@ -461,6 +549,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     using RW = Rows<kBwd>;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pr = lane & 15, upper = lane >> 4;
     const int nw = p.n_warps;
     const int slot_floats = p.n_tok * kCs;
     float* slot_k = reinterpret_cast<float*>(smem_raw);
@@ -468,13 +557,33 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     float* slot_g = slot_v + slot_floats;                       // backward only
     Ctx c;
     c.sub = slot_k + RW::kSlots * slot_floats;
-    c.agg = c.sub + nw * (RW::kSub * kCs);
-    c.cta = c.agg + RW::kLevels * (RW::kAgg * kCs);
-    c.consts = c.cta + RW::kAgg * kCs;
+    c.peers = c.sub + nw * (RW::kSub * kCs);
+    c.flags = c.peers + RW::kPeerFloats;
+    c.cta = c.flags + kCs;
+    c.consts = c.cta + RW::kSub * kCs;
     uint64_t* full = reinterpret_cast<uint64_t*>(c.consts + kConstRows * kCs);
+    c.xbar = full + 1;
+    c.status = p.status;
     c.warp = warp; c.lane = lane; c.n_warps = nw; c.n_tok = p.n_tok; c.cluster = p.cluster;
     c.rank = p.cluster > 1 ? static_cast<int>(cluster_rank()) : 0;
 
+#ifdef VRWKV_TIMELINE
+    long long* tl_base = reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.status) + 256);
+    int tl_slot = -1;
+    {
+        const int mid = (static_cast<int>(gridDim.x) / 2 / p.cluster) * p.cluster;
+        if (static_cast<int>(blockIdx.x) < kTlCtas) tl_slot = blockIdx.x;
+        else if (static_cast<int>(blockIdx.x) >= mid && static_cast<int>(blockIdx.x) < mid + kTlCtas) tl_slot = kTlCtas + blockIdx.x - mid;
+        if (tl_slot >= 0 && threadIdx.x == 0) {
+            unsigned long long gt; unsigned smid;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            tl_base[(tl_slot * 2) * kTlMarks + 22] = static_cast<long long>(gt);
+            tl_base[(tl_slot * 2) * kTlMarks + 23] = smid;
+        }
+    }
+#endif
+    TL_MARK(0);
     const int unit = static_cast<int>(blockIdx.x) / p.cluster;
     const int b = unit / p.n_strips, strip = unit - b * p.n_strips;
     const int tok0 = c.rank * p.n_tok;
@@ -482,73 +591,108 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
     if (threadIdx.x == 0) {
         sm100::mbar_init(full, 1);
+        for (int l = 0; l < RW::kLevels; ++l) sm100::mbar_init(c.xbar + l, 1);
         sm100::mbar_init_fence();
         sm100::mbar_expect_tx(full, RW::kSlots * slot_bytes);
         sm100::tma_load_3d(slot_k, &map_k, full, strip * kCs, tok0, b);
         sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
         if (kBwd) sm100::tma_load_3d(slot_g, &map_g, full, strip * kCs, tok0, b);
-    }
-    const int ch = strip * kCs + lane;
-    const float w = (ch < p.C) ? p.w[ch] : 0.f;
-    const float u = (ch < p.C) ? p.u[ch] : 0.f;
-    if (warp == 0) {
-        // double precision once per channel: a rounded lambda multiplied up over thousands of tokens
-        // would drift by distance * 6e-8
-        const double wd = static_cast<double>(w), ud = static_cast<double>(u);
-        c.consts[kLam * kCs + lane] = static_cast<float>(exp(-wd));
-        c.consts[kWl2 * kCs + lane] = static_cast<float>(wd * 1.4426950408889634);
-        c.consts[kCuw * kCs + lane] = static_cast<float>(exp(ud + wd));
-        c.consts[kInvLam * kCs + lane] = static_cast<float>(exp(wd));
-        const double lL = exp(-wd * kL), lC = exp(-wd * p.n_tok);
-        const float lLh = static_cast<float>(lL), lCh = static_cast<float>(lC);
-        c.consts[kLamL_hi * kCs + lane] = lLh;
-        c.consts[kLamL_lo * kCs + lane] = static_cast<float>(lL - static_cast<double>(lLh));
-        c.consts[kLamC_hi * kCs + lane] = lCh;
-        c.consts[kLamC_lo * kCs + lane] = static_cast<float>(lC - static_cast<double>(lCh));
-    }
-    __syncthreads();
-    const float lam = c.consts[kLam * kCs + lane];
-    const float wl2 = c.consts[kWl2 * kCs + lane];
-    const float cuw = c.consts[kCuw * kCs + lane];
-    const float2 lam2 = f2(lam, lam), c2 = f2(cuw, cuw);
-
-    if (!sm100::mbar_wait(full, 0, kSpinLimit)) atomicOr(p.status, 2u);
-
-    const int n = max(0, min(kL, p.T - (tok0 + warp * kL)));      // valid tokens of this sub-chunk
-    float* ks = slot_k + (warp * kL) * kCs + lane;
-    float* vs = slot_v + (warp * kL) * kCs + lane;
-    float* gs = slot_g + (warp * kL) * kCs + lane;
-    // rows past T arrive as zeros; a k of -1e30 makes their terms vanish without any masking below
-    if (n < kL) {
-        for (int i = n; i < kL; ++i) ks[i * kCs] = -1e30f;
-        __syncwarp();
-    }
-
-    // ---- level 1, pass 1: terms z = lambda e^{k} [v, 1] in place of k, v; sub-chunk aggregates ----
-    float2 F = f2(0.f, 0.f), MF = f2(0.f, 0.f), R = f2(0.f, 0.f);
-    float kmax = 0.f;
-    {
-        float2 mu2 = f2(1.f, 1.f);
-#pragma unroll
-        for (int i = 0; i < kL; ++i) {
-            const float k = ks[i * kCs], v = vs[i * kCs];
-            if (i < n) kmax = fmaxf(kmax, fabsf(k));
-            const float e = ex2(fmaf(k, kLog2e, -wl2));
-            const float2 z = f2(e * v, e);
-            ks[i * kCs] = z.x;
-            vs[i * kCs] = z.y;
-            F = fma2(lam2, F, z);
-            if (kBwd) MF = fma2(lam2, MF, F);
-            R = fma2(mu2, z, R);
-            mu2 = mul2(mu2, lam2);
+        if (p.cluster > 1) {
+            // bytes the other CTAs will send per level: a record per channel from every lower rank
+            // (towards later tokens) and from every higher rank (towards earlier), + their flags once
+            const uint32_t rec = kCs * (static_cast<uint32_t>(c.rank) * RW::kF * 4u + static_cast<uint32_t>(p.cluster - 1 - c.rank) * 8u);
+            sm100::mbar_expect_tx(c.xbar, rec + static_cast<uint32_t>(p.cluster - 1) * 4u);
+            if (kBwd) sm100::mbar_expect_tx(c.xbar + 1, rec);
         }
     }
-    bool unsafe = 2.f * kmax + fabsf(u) + fabsf(w) + fmaxf(-w, 0.f) * static_cast<float>(p.T) > kSafeRange;
-    Enter e1 = fast_exchange<kBwd>(c, 0, F, MF, R, unsafe);
+    {
+        // double precision once per channel: a rounded lambda multiplied up over thousands of tokens
+        // would drift by distance * 6e-8.  Six exponentials, spread over the warps (lane = channel).
+        const int ch = strip * kCs + lane;
+        const double wd = (ch < p.C) ? static_cast<double>(p.w[ch]) : 0.0;
+        for (int task = warp; task < 6; task += nw) {
+            if (task == 0) {
+                c.consts[kLam * kCs + lane] = static_cast<float>(exp(-wd));
+                c.consts[kWl2 * kCs + lane] = static_cast<float>(wd * 1.4426950408889634);
+            } else if (task == 1) {
+                const double ud = (ch < p.C) ? static_cast<double>(p.u[ch]) : 0.0;
+                c.consts[kCuw * kCs + lane] = static_cast<float>(exp(ud + wd));
+            } else if (task == 2) {
+                c.consts[kInvLam * kCs + lane] = static_cast<float>(exp(wd));
+            } else {
+                const double x = exp(-wd * (task == 3 ? kL : task == 4 ? kSpan : p.n_tok));
+                const float hi = static_cast<float>(x);
+                const int row = task == 3 ? kLam16_hi : task == 4 ? kLam32_hi : kLamC_hi;
+                c.consts[row * kCs + lane] = hi;
+                c.consts[(row + 1) * kCs + lane] = static_cast<float>(x - static_cast<double>(hi));
+            }
+        }
+    }
+    __syncthreads();
+    // every CTA of the cluster has initialised its mbarriers before any other CTA sends to them:
+    // arrive here, wait once the tiles have landed (long since complete by then)
+    // (relaxed: the mbarrier-init fence above is what publishes the initialisation)
+    if (p.cluster > 1) cluster_arrive_relaxed();
+    const int ch0 = strip * kCs + 2 * pr;
+    const float2 w2 = (ch0 < p.C) ? *reinterpret_cast<const float2*>(p.w + ch0) : f2(0.f, 0.f);
+    const float2 u2 = (ch0 < p.C) ? *reinterpret_cast<const float2*>(p.u + ch0) : f2(0.f, 0.f);
+    const float2 lam2 = *reinterpret_cast<const float2*>(c.consts + kLam * kCs + 2 * pr);
+    const float2 wl2 = *reinterpret_cast<const float2*>(c.consts + kWl2 * kCs + 2 * pr);
+    const float2 c2 = *reinterpret_cast<const float2*>(c.consts + kCuw * kCs + 2 * pr);
 
-    float gw = 0.f, gu = 0.f;
+    TL_MARK(1);
+    if (!sm100::mbar_wait(full, 0, kSpinLimit)) atomicOr(p.status, 2u);
+    if (p.cluster > 1) cluster_wait();
+    TL_MARK(2);
+
+    const int row0 = warp * kSpan + upper * kL;
+    const int n = max(0, min(kL, p.T - (tok0 + row0)));      // valid tokens of this sub-chunk
+    constexpr int kRow = kCs / 2;                              // float2 per row
+    float2* k2 = reinterpret_cast<float2*>(slot_k + row0 * kCs) + pr;
+    float2* v2 = reinterpret_cast<float2*>(slot_v + row0 * kCs) + pr;
+    float2* g2 = reinterpret_cast<float2*>(slot_g + row0 * kCs) + pr;
+    // rows past T arrive as zeros; a k of -1e30 makes their terms vanish without any masking below
+    if (n < kL)
+        for (int i = n; i < kL; ++i) k2[i * kRow] = f2(-1e30f, -1e30f);
+    __syncwarp();
+
+    // ---- level 1, pass 1: terms z = lambda e^{k} [v, 1] in place of k, v; sub-chunk aggregates ----
+    Pair2 F{f2(0.f, 0.f), f2(0.f, 0.f)}, MF{f2(0.f, 0.f), f2(0.f, 0.f)}, R{f2(0.f, 0.f), f2(0.f, 0.f)};
+    float2 kmax = f2(0.f, 0.f);
+    {
+        float2 mu = f2(1.f, 1.f);
+        const float2 nwl2 = f2(-wl2.x, -wl2.y), l2e = dup(kLog2e);
+#pragma unroll
+        for (int i = 0; i < kL; ++i) {
+            const float2 k = k2[i * kRow], v = v2[i * kRow];
+            if (i < n) kmax = f2(fmaxf(kmax.x, fabsf(k.x)), fmaxf(kmax.y, fabsf(k.y)));
+            const float2 t = fma2(k, l2e, nwl2);
+            const float2 e = f2(ex2(t.x), ex2(t.y));
+            const float2 zx = mul2(e, v);
+            k2[i * kRow] = zx;
+            v2[i * kRow] = e;
+            F.n = fma2(lam2, F.n, zx);
+            F.d = fma2(lam2, F.d, e);
+            if (kBwd) {
+                MF.n = fma2(lam2, MF.n, F.n);
+                MF.d = fma2(lam2, MF.d, F.d);
+            }
+            R.n = fma2(mu, zx, R.n);
+            R.d = fma2(mu, e, R.d);
+            mu = mul2(mu, lam2);
+        }
+    }
+    const float Tf = static_cast<float>(p.T);
+    bool unsafe = (2.f * kmax.x + fabsf(u2.x) + fabsf(w2.x) + fmaxf(-w2.x, 0.f) * Tf > kSafeRange) ||
+                  (2.f * kmax.y + fabsf(u2.y) + fabsf(w2.y) + fmaxf(-w2.y, 0.f) * Tf > kSafeRange);
+    TL_MARK(3);
+    const Enter e1 = fast_exchange<kBwd>(c, 0, F, MF, R, unsafe TL_PASS);
+    TL_MARK(4);
+
+    float2 gw = f2(0.f, 0.f), gu = f2(0.f, 0.f);
     if (unsafe) {
-        // the whole cluster takes this branch together: fetch k and v again, then the exact path
+        // the whole cluster takes this branch together: fetch k and v again, then the exact path,
+        // one channel of the pair at a time
         sm100::fence_proxy_async_smem();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -557,113 +701,140 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
         }
         if (!sm100::mbar_wait(full, 1, kSpinLimit)) atomicOr(p.status, 2u);
-        exact_subchunk<kBwd>(c, ks, vs, gs, n, w, u, gw, gu);
+        const int sub = 2 * warp + upper;
+        float* ks = reinterpret_cast<float*>(k2);
+        float* vs = reinterpret_cast<float*>(v2);
+        float* gs = reinterpret_cast<float*>(g2);
+        exact_subchunk<kBwd>(c, sub, 2 * pr, ks, vs, gs, n, w2.x, u2.x, gw.x, gu.x);
+        exact_subchunk<kBwd>(c, sub, 2 * pr + 1, ks + 1, vs + 1, gs + 1, n, w2.y, u2.y, gw.y, gu.y);
     } else if (!kBwd) {
         // ---- forward, pass 2: y = (P + S + e^{u} x) ratio, in place of the numerator term ----
-        float2 P = e1.P;
+        Pair2 P = e1.P;
 #pragma unroll
         for (int blk = 0; blk < kL / kStash; ++blk) {
-            float2 S = e1.S;
-            float2 stash[kStash];
+            Pair2 S = e1.S;
+            float2 sn[kStash], sd[kStash];
 #pragma unroll
             for (int i = kL - 1; i >= blk * kStash; --i) {
-                if (i < (blk + 1) * kStash) stash[i - blk * kStash] = S;
-                S = fma2(lam2, S, f2(ks[i * kCs], vs[i * kCs]));
+                if (i < (blk + 1) * kStash) { sn[i - blk * kStash] = S.n; sd[i - blk * kStash] = S.d; }
+                S.n = fma2(lam2, S.n, k2[i * kRow]);
+                S.d = fma2(lam2, S.d, v2[i * kRow]);
             }
 #pragma unroll
             for (int j = 0; j < kStash; ++j) {
                 const int i = blk * kStash + j;
-                const float2 z = f2(ks[i * kCs], vs[i * kCs]);
-                const float2 nd = fma2(c2, z, add2(P, stash[j]));
-                ks[i * kCs] = __fdividef(nd.x, nd.y);
-                P = fma2(lam2, P, z);
+                const float2 zx = k2[i * kRow], zy = v2[i * kRow];
+                const float2 nn = fma2(c2, zx, add2(P.n, sn[j]));
+                const float2 dd = fma2(c2, zy, add2(P.d, sd[j]));
+                k2[i * kRow] = mul2(nn, f2(rcp(dd.x), rcp(dd.y)));
+                P.n = fma2(lam2, P.n, zx);
+                P.d = fma2(lam2, P.d, zy);
             }
         }
     } else {
-        // ---- backward, pass 2: recompute Den, y; G = gy / Den (in place of gy), H = G y (registers);
-        //      gu; gw from pairs (output later than input); aggregates of [G, H] ----
-        float hh[kL];
-        float2 rr = f2(0.f, 0.f), mr = f2(0.f, 0.f), q = f2(0.f, 0.f);
+        // the records the other CTAs sent for level 1 have been consumed: tell them (they wait for
+        // this before sending level 2 into the same slots).  The reads are complete: their values
+        // went into shared memory before the CTA barrier that precedes this point.
+        if (p.cluster > 1) cluster_arrive_relaxed();
+        // ---- backward, pass 2: recompute Den, y; G = gy / Den (in place of gy), -H = -G y (registers);
+        //      gu; gw from pairs (output later than input); aggregates of [G, -H] ----
+        float2 hn[kL];
+        Pair2 rr{f2(0.f, 0.f), f2(0.f, 0.f)}, mr{f2(0.f, 0.f), f2(0.f, 0.f)}, q{f2(0.f, 0.f), f2(0.f, 0.f)};
+        float2 gwa = f2(0.f, 0.f);
         {
-            float2 P = e1.P, PM = e1.MP, mu2 = lam2;
+            Pair2 P = e1.P, PM = e1.MP;
+            float2 mu = lam2;
 #pragma unroll
             for (int blk = 0; blk < kL / kStash; ++blk) {
-                float2 S = e1.S;
-                float2 stash[kStash];
+                Pair2 S = e1.S;
+                float2 sn[kStash], sd[kStash];
 #pragma unroll
                 for (int i = kL - 1; i >= blk * kStash; --i) {
-                    if (i < (blk + 1) * kStash) stash[i - blk * kStash] = S;
-                    S = fma2(lam2, S, f2(ks[i * kCs], vs[i * kCs]));
+                    if (i < (blk + 1) * kStash) { sn[i - blk * kStash] = S.n; sd[i - blk * kStash] = S.d; }
+                    S.n = fma2(lam2, S.n, k2[i * kRow]);
+                    S.d = fma2(lam2, S.d, v2[i * kRow]);
                 }
 #pragma unroll
                 for (int j = 0; j < kStash; ++j) {
                     const int i = blk * kStash + j;
-                    const float2 z = f2(ks[i * kCs], vs[i * kCs]);
-                    const float2 nd = fma2(c2, z, add2(P, stash[j]));
-                    const float inv = rcp(fmaxf(nd.y, 1e-37f));     // rows past T: gy = 0 must stay 0
-                    const float y = nd.x * inv;
-                    const float g = gs[i * kCs] * inv;
-                    const float h = g * y;
-                    gs[i * kCs] = g;
-                    hh[i] = h;
-                    gu = fmaf(z.x, g, gu);
-                    gu = fmaf(-z.y, h, gu);
-                    gw = fmaf(-g, PM.x, gw);
-                    gw = fmaf(h, PM.y, gw);
-                    P = fma2(lam2, P, z);
-                    PM = fma2(lam2, PM, P);
-                    const float2 gh = f2(g, h);
-                    rr = fma2(lam2, rr, gh);
-                    mr = fma2(lam2, mr, rr);
-                    q = fma2(mu2, gh, q);
-                    mu2 = mul2(mu2, lam2);
+                    const float2 zx = k2[i * kRow], zy = v2[i * kRow];
+                    const float2 nn = fma2(c2, zx, add2(P.n, sn[j]));
+                    const float2 dd = fma2(c2, zy, add2(P.d, sd[j]));
+                    // rows past T: gy = 0 must stay 0 whatever the denominator
+                    const float2 inv = f2(rcp(fmaxf(dd.x, 1e-37f)), rcp(fmaxf(dd.y, 1e-37f)));
+                    const float2 ny = f2(nn.x * -inv.x, nn.y * -inv.y);
+                    const float2 g = mul2(g2[i * kRow], inv);
+                    const float2 h = mul2(g, ny);                  // -H
+                    g2[i * kRow] = g;
+                    hn[i] = h;
+                    gu = fma2(zx, g, gu);
+                    gu = fma2(zy, h, gu);
+                    gwa = fma2(g, PM.n, gwa);
+                    gwa = fma2(h, PM.d, gwa);
+                    P.n = fma2(lam2, P.n, zx);
+                    P.d = fma2(lam2, P.d, zy);
+                    PM.n = fma2(lam2, PM.n, P.n);
+                    PM.d = fma2(lam2, PM.d, P.d);
+                    rr.n = fma2(lam2, rr.n, g);
+                    rr.d = fma2(lam2, rr.d, h);
+                    mr.n = fma2(lam2, mr.n, rr.n);
+                    mr.d = fma2(lam2, mr.d, rr.d);
+                    q.n = fma2(mu, g, q.n);
+                    q.d = fma2(mu, h, q.d);
+                    mu = mul2(mu, lam2);
                 }
             }
-            gu *= cuw;
-            rr = mul2(rr, lam2);
-            mr = mul2(mr, lam2);
+            gu = mul2(gu, c2);
+            rr.n = mul2(rr.n, lam2); rr.d = mul2(rr.d, lam2);
+            mr.n = mul2(mr.n, lam2); mr.d = mul2(mr.d, lam2);
         }
         bool ignored = false;
-        const Enter e2 = fast_exchange<kBwd>(c, 1, rr, mr, q, ignored);
+        TL_MARK(5);
+        if (p.cluster > 1) cluster_wait();
+        const Enter e2 = fast_exchange<kBwd>(c, 1, rr, mr, q, ignored TL_PASS);
+        TL_MARK(6);
         // ---- backward, pass 3: gk, gv in place of the terms; gw from pairs (output earlier than input).
-        //      Adjoint states are kept divided by lambda, so that [G, H] enter without a multiply. ----
+        //      Adjoint states are kept divided by lambda, so that [G, -H] enter without a multiply. ----
         {
-            const float il = c.consts[kInvLam * kCs + lane];
-            const float2 il2 = f2(il, il);
-            float2 Rp = mul2(e2.P, il2), MRp = mul2(e2.MP, il2);
-            const float2 Qin = mul2(e2.S, il2);
+            const float2 il2 = *reinterpret_cast<const float2*>(c.consts + kInvLam * kCs + 2 * pr);
+            Pair2 Rp{mul2(e2.P.n, il2), mul2(e2.P.d, il2)}, MRp{mul2(e2.MP.n, il2), mul2(e2.MP.d, il2)};
+            const Pair2 Qin{mul2(e2.S.n, il2), mul2(e2.S.d, il2)};
 #pragma unroll
             for (int blk = 0; blk < kL / kStash; ++blk) {
-                float2 Q = Qin;
-                float2 stash[kStash];
+                Pair2 Q = Qin;
+                float2 sn[kStash], sd[kStash];
 #pragma unroll
                 for (int i = kL - 1; i >= blk * kStash; --i) {
-                    if (i < (blk + 1) * kStash) stash[i - blk * kStash] = Q;
-                    Q = fma2(lam2, Q, f2(gs[i * kCs], hh[i]));
+                    if (i < (blk + 1) * kStash) { sn[i - blk * kStash] = Q.n; sd[i - blk * kStash] = Q.d; }
+                    Q.n = fma2(lam2, Q.n, g2[i * kRow]);
+                    Q.d = fma2(lam2, Q.d, hn[i]);
                 }
 #pragma unroll
                 for (int j = 0; j < kStash; ++j) {
                     const int i = blk * kStash + j;
-                    const float2 gh = f2(gs[i * kCs], hh[i]);
-                    const float2 z = f2(ks[i * kCs], vs[i * kCs]);
-                    const float2 A = fma2(c2, gh, add2(stash[j], Rp));
-                    vs[i * kCs] = z.y * A.x;
-                    ks[i * kCs] = fmaf(z.x, A.x, -z.y * A.y);
-                    gw = fmaf(-z.x, MRp.x, gw);
-                    gw = fmaf(z.y, MRp.y, gw);
-                    Rp = fma2(lam2, Rp, gh);
-                    MRp = fma2(lam2, MRp, Rp);
+                    const float2 g = g2[i * kRow], h = hn[i];
+                    const float2 zx = k2[i * kRow], zy = v2[i * kRow];
+                    const float2 AG = fma2(c2, g, add2(sn[j], Rp.n));
+                    const float2 AH = fma2(c2, h, add2(sd[j], Rp.d));      // -A^H
+                    v2[i * kRow] = mul2(zy, AG);
+                    k2[i * kRow] = fma2(zx, AG, mul2(zy, AH));
+                    gwa = fma2(zx, MRp.n, gwa);
+                    gwa = fma2(zy, MRp.d, gwa);
+                    Rp.n = fma2(lam2, Rp.n, g);
+                    Rp.d = fma2(lam2, Rp.d, h);
+                    MRp.n = fma2(lam2, MRp.n, Rp.n);
+                    MRp.d = fma2(lam2, MRp.d, Rp.d);
                 }
             }
         }
+        gw = f2(-gwa.x, -gwa.y);
     }
-    // after this point no CTA of the cluster reads another CTA's shared memory again
-    if (p.cluster > 1) cluster_arrive();
+    TL_MARK(7);
 
     if (kBwd) {
-        // this warp's own rows of the gy slot are free now: park its gw, gu there for the CTA sum
-        gs[0] = gw;
-        gs[kCs] = gu;
+        // this thread's own rows of the gy slot are free now: park its gw, gu there for the CTA sum
+        g2[0] = gw;
+        g2[kRow] = gu;
     }
     sm100::fence_proxy_async_smem();
     __syncthreads();
@@ -675,14 +846,14 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     if (kBwd && warp < 2) {
         for (int j = warp; j < 2; j += min(nw, 2)) {
             float acc = 0.f;
-            for (int s = 0; s < nw; ++s) acc += slot_g[(s * kL + j) * kCs + lane];
+            for (int s = 0; s < 2 * nw; ++s) acc += slot_g[(s * kL + j) * kCs + lane];
             p.partial[(static_cast<size_t>(blockIdx.x) * 2 + j) * kCs + lane] = acc;
         }
     }
+    TL_MARK(8);
     if (threadIdx.x == 0) sm100::tma_store_wait_all();
-    if (p.cluster > 1) cluster_wait();
+    TL_MARK(9);
 }
-
 // out[j][c] = sum over sequences and cluster ranks of partial[cta][j][c % 32], fixed order
 __global__ void __launch_bounds__(1024)
 reduce_partials(Params p, float* __restrict__ out) {
@@ -707,7 +878,7 @@ reduce_partials(Params p, float* __restrict__ out) {
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-constexpr int kFwdStash = 16;
+constexpr int kFwdStash = 8;
 constexpr int kBwdStash = 8;
 
 struct Plan {
@@ -716,12 +887,12 @@ struct Plan {
 
 static bool make_plan(int T, Plan& pl) {
     int cluster = 1;
-    while ((T + cluster - 1) / cluster > kMaxWarps * kL && cluster < kMaxCluster) cluster *= 2;
+    while ((T + cluster - 1) / cluster > kMaxWarps * kSpan && cluster < kMaxCluster) cluster *= 2;
     const int per = (T + cluster - 1) / cluster;
-    if (per > kMaxWarps * kL) return false;
+    if (per > kMaxWarps * kSpan) return false;
     pl.cluster = cluster;
-    pl.n_warps = (per + kL - 1) / kL;
-    pl.n_tok = pl.n_warps * kL;
+    pl.n_warps = (per + kSpan - 1) / kSpan;
+    pl.n_tok = pl.n_warps * kSpan;
     // every CTA of the cluster must own at least one token
     return static_cast<long long>(cluster - 1) * pl.n_tok < T;
 }
