@@ -44,8 +44,8 @@ enum vrwkv_status {
 int vrwkv_version(void);
 /* Human-readable text for a status code (static storage). */
 const char* vrwkv_status_string(int status);
-/* One line about the most recent non-zero status of this process (for instance the name of
- * the CUDA error behind VRWKV_ERR_LAUNCH).  Static storage, not thread-safe.  Diagnostic. */
+/* One line about the most recent non-zero status of the calling thread (for instance the name
+ * of the CUDA error behind VRWKV_ERR_LAUNCH).  Thread-local storage.  Diagnostic. */
 const char* vrwkv_last_error_detail(void);
 /* Number of kernels this library has launched in the calling process so far. */
 unsigned long long vrwkv_launch_count(void);
@@ -55,7 +55,10 @@ unsigned long long vrwkv_launch_count(void);
  * aligned, else the persistent tile kernels, else the generic multi-launch path), 1 = the
  * first-generation kernels (Bi-WKV: the generic multi-launch path; WKV6 tensor-core forward:
  * the serial-phase kernel instead of the warp-specialised one), 2 = Bi-WKV skips the
- * cluster-resident kernels (persistent tile kernels where eligible).  Process-wide.
+ * cluster-resident kernels (persistent tile kernels where eligible), 3 = test of the bounded
+ * device-side waits: as 0, but one CTA of every cluster withholds what it owes the others and
+ * the waits give up after about a thousand polls, so the call returns promptly with bit 0 of the
+ * status word set and meaningless results (nothing hangs, nothing faults).  Process-wide.
  * No reference counterpart. */
 int vrwkv_set_path(int path);
 /* Copies the device status word kept in the first 4 bytes of a workspace to *status_out

@@ -136,8 +136,8 @@ def test_outputs_do_not_spill_past_their_buffers(cuda_device):
 
 
 def test_fused_path_is_taken_when_eligible(cuda_device, kernel_path):
-    """One launch per forward and two per backward (kernel + gw/gu reduction) on the fused
-    path; three and six on the generic one."""
+    """Launches per forward / backward: cluster-resident path 2 / 3 (fast kernel, exact kernel for
+    what it left behind, gw/gu reduction), tile path 1 / 2, generic path 3 / 6."""
     from vision_rwkv_b200 import launch_count, ops
     w, u, k, v, gy = [x.float().to(cuda_device).contiguous() for x in O.make_inputs(2, 300, 64)]
     n0 = launch_count()
@@ -145,7 +145,7 @@ def test_fused_path_is_taken_when_eligible(cuda_device, kernel_path):
     n1 = launch_count()
     ops.biwkv_backward(w, u, k, v, gy)
     n2 = launch_count()
-    assert (n1 - n0, n2 - n1) == ((3, 6) if kernel_path == "generic" else (1, 2))
+    assert (n1 - n0, n2 - n1) == {"generic": (3, 6), "tiles": (1, 2), "auto": (2, 3)}[kernel_path]
     # C not a multiple of 4 cannot be described to TMA: generic kernels serve it
     w, u, k, v, gy = [x.float().to(cuda_device).contiguous() for x in O.make_inputs(2, 30, 6)]
     n0 = launch_count()
@@ -252,3 +252,26 @@ def test_full_size_properties(cuda_device):
     assert rel_err(y[:1, :, cs], O.biwkv_scan_forward(*sl[:4])) <= TOL
     _, _, gk_ref, gv_ref = O.biwkv_scan_backward(*sl)
     assert rel_err(gk[:1, :, cs], gk_ref) <= TOL and rel_err(gv[:1, :, cs], gv_ref) <= TOL
+
+
+def test_bounded_wait_runs_out_and_reports(cuda_device, kernel_path):
+    """A device-side wait that can never be satisfied gives up, sets the status word and lets the
+    call return: path 3 makes one CTA of every cluster withhold what it owes the others."""
+    if kernel_path != "auto":
+        pytest.skip("the withholding switch exists for the cluster-resident kernels")
+    from vision_rwkv_b200 import _lib, ops
+    lib = _lib.load()
+    w, u, k, v, gy = [x.float().to(cuda_device).contiguous() for x in O.make_inputs(1, 1000, 32, seed=2)]
+    assert lib.vrwkv_set_path(3) == 0
+    try:
+        ops.CHECK_STATUS = True
+        with pytest.raises(_lib.VrwkvError, match="status word"):
+            ops.biwkv_forward(w, u, k, v)
+        with pytest.raises(_lib.VrwkvError, match="status word"):
+            ops.biwkv_backward(w, u, k, v, gy)
+        torch.cuda.synchronize()
+    finally:
+        lib.vrwkv_set_path(0)
+    # the context is intact and the next call is right again
+    y = ops.biwkv_forward(w, u, k, v)
+    assert rel_err(y, O.biwkv_scan_forward(*[x.double().cpu() for x in (w, u, k, v)])) <= TOL

@@ -46,6 +46,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <initializer_list>
+#include <mutex>
 #include <type_traits>
 #include "biwkv_math.cuh"
 #include "sm100_async.cuh"
@@ -269,11 +270,9 @@ __device__ __forceinline__ Entering exchange_collect(const Params& p, float* ext
         Acc2 S = acc2_zero();
         for (int j0 = warp; j0 < p.n_chunks; j0 += 4 * kWarps) {
             // Poll the (up to four) flags of the batch together: independent relaxed loads, one
-            // round trip through L2 for all of them.  The record loads below take their address
-            // from the polled values (`dep`, always zero, but only known once the flags have come
-            // back), so they cannot be issued before the flags were seen set; the publisher put a
-            // fence between its record and its flag, and both sides go through L2 (ld.cg), so a
-            // set flag implies a visible record without an acquire fence in every warp.
+            // round trip through L2 for all of them; once all are set, one acquire load per flag
+            // (again together) orders the record loads behind the publishers' writes.  The
+            // publisher put a fence between its record and its flag.
             bool ok = true;
             const unsigned* fl[4];
 #pragma unroll
@@ -296,6 +295,14 @@ __device__ __forceinline__ Entering exchange_collect(const Params& p, float* ext
                     break;
                 }
                 __nanosleep(spins < 8 ? 32 : 128);
+            }
+            // the polls above are relaxed; one acquire load per flag, issued together, is what orders
+            // the record loads below after the publishers' writes (the address dependency through
+            // `dep` alone is not an ordering the PTX memory model gives)
+            if (ok) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (fl[q]) seen[q] |= sm100::flag_acquire(fl[q]);
             }
             const unsigned seen_all = seen[0] | seen[1] | seen[2] | seen[3];
             const size_t dep = seen_all >> 31;
@@ -993,6 +1000,14 @@ __device__ __forceinline__ Entering4 exchange_collect4(const Params& p, float* e
                 }
                 __nanosleep(spins < 8 ? 32 : 128);
             }
+            // the polls above are relaxed; one acquire load per flag, issued together, is what orders
+            // the record loads below after the publishers' writes (the address dependency through
+            // `dep` alone is not an ordering the PTX memory model gives)
+            if (ok) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (fl[q]) seen[q] |= sm100::flag_acquire(fl[q]);
+            }
             const unsigned seen_all = seen[0] | seen[1] | seen[2] | seen[3];
             const size_t dep = seen_all >> 31;
             if (!ok && lane == 0) atomicOr(p.status, 1u);
@@ -1320,10 +1335,13 @@ static bool configure_kernels(int (&resident)[2]) {
     return good && resident[0] > 0 && resident[1] > 0;
 }
 
+static std::mutex g_config_lock;
+
 static const DeviceInfo& device_info() {
     static DeviceInfo infos[64];
     int dev = 0;
     cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> guard(g_config_lock);
     DeviceInfo& d = infos[dev & 63];
     if (d.ok) return d;
     cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
@@ -1414,11 +1432,15 @@ static int launch(Layout& l, const float* w, const float* u, const E* k, const E
     void* fwd_kernel = reinterpret_cast<void*>(biwkv_forward_pipelined_kernel<E, false>);
     if constexpr (std::is_same<E, float>::value) {
         if (!kBwd && o1 != nullptr) {                 // forward that also writes log Den into o1
-            static bool configured = false;
-            if (!configured) {
+            // the attribute is per device: one flag per device, under the lock of device_info()
+            static bool configured[64] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            std::lock_guard<std::mutex> guard(g_config_lock);
+            if (!configured[dev & 63]) {
                 cudaFuncSetAttribute(biwkv_forward_pipelined_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(fwd_pipelined_smem_bytes<float>()));
-                configured = true;
+                configured[dev & 63] = true;
             }
             fwd_kernel = reinterpret_cast<void*>(biwkv_forward_pipelined_kernel<float, true>);
         }
@@ -1463,6 +1485,7 @@ static int saved_resident() {
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
+    std::lock_guard<std::mutex> guard(g_config_lock);
     if (!known[dev]) {
         int n = 0;
         if (cudaFuncSetAttribute(biwkv_backward_saved_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -18,8 +18,9 @@
 //      aggregate of the 32-token span (towards later tokens, and towards earlier ones);
 //   2. two warps walk the span aggregates of the CTA serially (one per direction, lane = channel),
 //      leave in place the state entering each span from the rest of the CTA, and send the CTA's own
-//      aggregate to the CTAs that need it: st.async into their shared memory, completion counted
-//      in bytes on their mbarrier (one hop through the cluster network, no fence, no multicast);
+//      aggregate to the CTAs that need it, all warps sharing the sends: st.async into their shared
+//      memory, completion counted in bytes on their mbarrier (one hop through the cluster network,
+//      no fence, no multicast);
 //   3. the same two warps wait (bounded) for the bytes of the other CTAs and combine them;
 //   4. every thread adds the outside state, moved to its own position, to its inside state.
 // Forward: one level (terms e^{k}[v, 1]).  Backward: a second level for the adjoint pairs
@@ -41,6 +42,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <initializer_list>
 #include <mutex>
@@ -54,6 +56,9 @@ namespace resident {
 
 constexpr int kL = 16;            // tokens per thread
 constexpr int kSpan = 2 * kL;     // tokens per warp
+constexpr int kGroup = 4;         // tokens whose loads are issued together (forward)
+constexpr int kGroupB = 4;        // ... backward
+constexpr int kBatch = 8;         // other CTAs' blocks read together when they are combined
 constexpr int kCs = 32;           // channels per strip
 constexpr int kMaxWarps = 8;      // spans per CTA
 constexpr int kMaxCluster = 16;
@@ -64,7 +69,7 @@ constexpr uint32_t kSpinLimit = 1u << 20;   // ~0.1 s of polling on a barrier
 
 // per-channel constants, computed once per CTA by warp 0 in double precision (rows of kCs floats)
 enum ConstRow {
-    kLam = 0, kWl2, kCuw, kInvLam, kLam16_hi, kLam16_lo, kLam32_hi, kLam32_lo, kLamC_hi, kLamC_lo, kConstRows
+    kLam = 0, kWl2, kCuw, kLam16_hi, kLam16_lo, kLam32_hi, kLam32_lo, kLamC_hi, kLamC_lo, kConstRows
 };
 
 // rows of kCs floats in the record area behind the data slots
@@ -75,7 +80,9 @@ struct Rows {
     static constexpr int kSub = kF + kR;          // per span
     static constexpr int kLevels = kBwd ? 2 : 1;
     static constexpr int kSlots = kBwd ? 3 : 2;
-    static constexpr int kPeerFloats = kMaxCluster * kCs * kF;   // one record slot per rank and channel
+    static constexpr int kBlockF = kCs * kF + 4;   // floats of a CTA aggregate towards later tokens + flag word (16-byte padded)
+    static constexpr int kBlockR = kCs * kR + 4;   // ... towards earlier tokens
+    static constexpr int kPeerFloats = kMaxCluster * kBlockF;    // one block slot per rank
 };
 
 struct Params {
@@ -88,15 +95,19 @@ struct Params {
     const float* u;
     unsigned* status;   // device status word
     float* partial;     // backward: [grid][2][kCs]
+    unsigned* redo_count;   // units the fast kernel left to the exact kernel ...
+    int* redo_list;         // ... and which
+    uint32_t spin_limit;  // polls before a wait for the other CTAs gives up
+    int withhold_rank;    // test only: this rank of every cluster sends nothing (-1: none)
 };
 
-// shared memory: data slots | span records | records received from the other CTAs | flags row |
-// state entering this CTA | constants | mbarriers
+// shared memory: data slots | span records | blocks received from the other CTAs | this CTA's two
+// outgoing blocks | state entering this CTA | constants | mbarriers and the flag word
 template <bool kBwd>
 static inline size_t smem_bytes(int n_warps) {
     using R = Rows<kBwd>;
     const size_t data = static_cast<size_t>(R::kSlots) * n_warps * kSpan * kCs * sizeof(float);
-    const size_t rec = (static_cast<size_t>(n_warps) * R::kSub * kCs + R::kPeerFloats + kCs + R::kSub * kCs + kConstRows * kCs) * sizeof(float);
+    const size_t rec = (static_cast<size_t>(n_warps) * R::kSub * kCs + R::kPeerFloats + R::kBlockF + R::kBlockR + R::kSub * kCs + kConstRows * kCs) * sizeof(float);
     return data + rec + 64;
 }
 
@@ -152,8 +163,8 @@ __device__ __forceinline__ void st_async2(uint32_t addr, float2 v, uint32_t bar)
                  "f"(v.y), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void st_async1(uint32_t addr, uint32_t v, uint32_t bar) {
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(bar)
+__device__ __forceinline__ void st_async1(uint32_t addr, float v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(addr), "f"(v), "r"(bar)
                  : "memory");
 }
 
@@ -161,7 +172,7 @@ __device__ __forceinline__ void st_async1(uint32_t addr, uint32_t v, uint32_t ba
 // kTlCtas CTAs from the middle of the grid store clock64() at each phase boundary behind the
 // workspace's status block.  Compiled out otherwise.
 #ifdef VRWKV_TIMELINE
-constexpr int kTlCtas = 64, kTlMarks = 24;
+constexpr int kTlCtas = 64, kTlMarks = 32;
 #define TL_MARK(m)                                                                                         \
     do {                                                                                                   \
         if (tl_slot >= 0 && lane == 0 && (warp == 0 || warp == 5))                                          \
@@ -177,12 +188,15 @@ constexpr int kTlCtas = 64, kTlMarks = 24;
 
 struct Ctx {
     float* sub;      // [n_warps][kSub][kCs]; rows 0..kF-1 towards later tokens, kF.. towards earlier
-    float* peers;    // [kMaxCluster][kCs][kF]: records received from the other CTAs (directly behind sub)
-    float* flags;    // [kCs] words: entry r = out-of-range flag of rank r
+    float* peers;    // [kMaxCluster][kBlockF]: blocks received from the other CTAs (directly behind sub)
+    float* stage;    // [kBlockF + kBlockR]: this CTA's outgoing blocks
+    unsigned* flag;  // the cluster's out-of-range flag, once known
     float* cta;      // [kSub][kCs]: state entering this CTA from the rest of the cluster
     float* consts;   // [kConstRows][kCs]
     uint64_t* xbar;  // [kLevels] mbarriers counting the bytes the other CTAs send
     unsigned* status;
+    uint32_t spin_limit;
+    bool withhold;   // test only: this CTA sends nothing to the others
     int warp, lane, n_warps, n_tok, cluster, rank;
 };
 
@@ -237,54 +251,93 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
     TL_MARK(12 + level * 5);
     // (2) serial walk over the spans, one warp per direction, lane = channel, state = (a, b)
     const int scanF = 0, scanR = nw > 1 ? 1 : 0;
-    const uint32_t bar_delta = sm100::smem_u32(c.xbar + level) - sm100::smem_u32(c.peers);
     if (warp == scanF) {
         const float2 hi2 = dup(c.consts[kLam32_hi * kCs + lane]), lo2 = dup(c.consts[kLam32_lo * kCs + lane]);
         const float2 len2 = dup(static_cast<float>(kSpan));
         float2 P = f2(0.f, 0.f), M = f2(0.f, 0.f);
-#pragma unroll 4
-        for (int s = 0; s < nw; ++s) {
-            float* q = c.sub + s * (RW::kSub * kCs) + lane;
-            const float2 f = f2(q[0], q[kCs]);
-            q[0] = P.x; q[kCs] = P.y;
-            if (kMom) {
-                const float2 mf = f2(q[2 * kCs], q[3 * kCs]);
-                q[2 * kCs] = M.x; q[3 * kCs] = M.y;
-                M = mulc_add(fma2(len2, P, M), hi2, lo2, mf);
+        // all loads first, then the dependent chain, storing as it goes: nothing waits on shared memory
+        float2 f[kMaxWarps], mf[kMaxWarps];
+#pragma unroll
+        for (int s = 0; s < kMaxWarps; ++s) {
+            f[s] = f2(0.f, 0.f);
+            mf[s] = f2(0.f, 0.f);
+            if (s < nw) {
+                const float* q = c.sub + s * (RW::kSub * kCs) + lane;
+                f[s] = f2(q[0], q[kCs]);
+                if (kMom) mf[s] = f2(q[2 * kCs], q[3 * kCs]);
             }
-            P = mulc_add(P, hi2, lo2, f);
         }
-        // the CTA's aggregate goes to every higher rank; the flag to every other rank
-        for (int r = c.rank + 1; r < c.cluster; ++r) {
-            const uint32_t rb = peer_addr(c.peers, r);
-            const uint32_t dst = rb + static_cast<uint32_t>((c.rank * kCs + lane) * RW::kF) * 4u;
-            if (kMom) st_async4(dst, make_float4(P.x, P.y, M.x, M.y), rb + bar_delta);
-            else st_async2(dst, P, rb + bar_delta);
+        if (level == 1) TL_MARK(22);
+#pragma unroll
+        for (int s = 0; s < kMaxWarps; ++s) {
+            if (s < nw) {
+                float* q = c.sub + s * (RW::kSub * kCs) + lane;
+                q[0] = P.x; q[kCs] = P.y;
+                if (kMom) {
+                    q[2 * kCs] = M.x; q[3 * kCs] = M.y;
+                    M = mulc_add(fma2(len2, P, M), hi2, lo2, mf[s]);
+                }
+                P = mulc_add(P, hi2, lo2, f[s]);
+            }
         }
-        if (level == 0 && lane < c.cluster && lane != c.rank) {
-            const uint32_t rb = peer_addr(c.peers, lane);
-            st_async1(rb + (sm100::smem_u32(c.flags + c.rank) - sm100::smem_u32(c.peers)), static_cast<uint32_t>(any), rb + bar_delta);
-        }
+        if (level == 1) TL_MARK(23);
+        // the CTA's aggregate (and its flag) for the higher ranks: into the outgoing block
+        float* st = c.stage;
+        if (kMom) *reinterpret_cast<float4*>(st + lane * 4) = make_float4(P.x, P.y, M.x, M.y);
+        else *reinterpret_cast<float2*>(st + lane * 2) = P;
+        if (lane == 0) st[kCs * RW::kF] = __int_as_float(any);
     }
     if (warp == scanR) {
         const float2 hi2 = dup(c.consts[kLam32_hi * kCs + lane]), lo2 = dup(c.consts[kLam32_lo * kCs + lane]);
         float2 S = f2(0.f, 0.f);
-#pragma unroll 4
-        for (int s = nw - 1; s >= 0; --s) {
-            float* q = c.sub + s * (RW::kSub * kCs) + RW::kF * kCs + lane;
-            const float2 r = f2(q[0], q[kCs]);
-            q[0] = S.x; q[kCs] = S.y;
-            S = mulc_add(S, hi2, lo2, r);
+        float2 r[kMaxWarps];
+#pragma unroll
+        for (int s = 0; s < kMaxWarps; ++s) {
+            r[s] = f2(0.f, 0.f);
+            if (s < nw) {
+                const float* q = c.sub + s * (RW::kSub * kCs) + RW::kF * kCs + lane;
+                r[s] = f2(q[0], q[kCs]);
+            }
         }
-        for (int r = 0; r < c.rank; ++r) {
+#pragma unroll
+        for (int s = kMaxWarps - 1; s >= 0; --s) {
+            if (s < nw) {
+                float* q = c.sub + s * (RW::kSub * kCs) + RW::kF * kCs + lane;
+                q[0] = S.x; q[kCs] = S.y;
+                S = mulc_add(S, hi2, lo2, r[s]);
+            }
+        }
+        float* st = c.stage + RW::kBlockF;
+        *reinterpret_cast<float2*>(st + lane * 2) = S;
+        if (lane == 0) st[kCs * RW::kR] = __int_as_float(any);
+    }
+    // every warp sends the blocks to its share of the other CTAs (rank = warp, warp + n_warps, ...):
+    // lane = channel, one record per lane, lane 0 also the flag word
+    if (level == 1) TL_MARK(24);
+    if (c.cluster > 1) {
+        __syncthreads();
+    }
+    if (level == 1) TL_MARK(25);
+    if (c.cluster > 1 && !c.withhold) {
+        const uint32_t bar_off = sm100::smem_u32(c.xbar + level) - sm100::smem_u32(c.peers);
+        for (int r = warp; r < c.cluster; r += nw) {
+            if (r == c.rank) continue;
             const uint32_t rb = peer_addr(c.peers, r);
-            st_async2(rb + static_cast<uint32_t>((c.rank * kCs + lane) * RW::kF) * 4u, S, rb + bar_delta);
+            const uint32_t slot = rb + static_cast<uint32_t>(c.rank * RW::kBlockF) * 4u;
+            if (r > c.rank) {
+                if (kMom) st_async4(slot + lane * 16u, *reinterpret_cast<const float4*>(c.stage + lane * 4), rb + bar_off);
+                else st_async2(slot + lane * 8u, *reinterpret_cast<const float2*>(c.stage + lane * 2), rb + bar_off);
+                if (lane == 0) st_async1(slot + kCs * RW::kF * 4u, c.stage[kCs * RW::kF], rb + bar_off);
+            } else {
+                st_async2(slot + lane * 8u, *reinterpret_cast<const float2*>(c.stage + RW::kBlockF + lane * 2), rb + bar_off);
+                if (lane == 0) st_async1(slot + kCs * RW::kR * 4u, c.stage[RW::kBlockF + kCs * RW::kR], rb + bar_off);
+            }
         }
     }
     TL_MARK(13 + level * 5);
     // (3) wait for the other CTAs' bytes, combine them
     if (c.cluster > 1 && (warp == scanF || warp == scanR)) {
-        if (!sm100::mbar_wait(c.xbar + level, 0, kSpinLimit) && lane == 0) atomicOr(c.status, 1u);
+        if (!sm100::mbar_wait(c.xbar + level, 0, c.spin_limit) && lane == 0) atomicOr(c.status, 1u);
     }
     TL_MARK(14 + level * 5);
     if (warp == scanF) {
@@ -293,36 +346,56 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
         if (c.cluster > 1) {
             const float2 hi2 = dup(c.consts[kLamC_hi * kCs + lane]), lo2 = dup(c.consts[kLamC_lo * kCs + lane]);
             const float2 len2 = dup(static_cast<float>(c.n_tok));
-#pragma unroll 4
-            for (int r = 0; r < c.rank; ++r) {
-                const float* q = c.peers + (r * kCs + lane) * RW::kF;
-                float2 f, mf = f2(0.f, 0.f);
-                if (kMom) {
-                    const float4 t = *reinterpret_cast<const float4*>(q);
-                    f = f2(t.x, t.y);
-                    mf = f2(t.z, t.w);
-                    MX = mulc_add(fma2(len2, X, MX), hi2, lo2, mf);
-                } else {
-                    f = *reinterpret_cast<const float2*>(q);
+            for (int r0 = 0; r0 < c.rank; r0 += kBatch) {
+                float2 f[kBatch], mf[kBatch];
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j) {
+                    f[j] = f2(0.f, 0.f);
+                    mf[j] = f2(0.f, 0.f);
+                    if (r0 + j < c.rank) {
+                        const float* q = c.peers + (r0 + j) * RW::kBlockF + lane * RW::kF;
+                        if (kMom) {
+                            const float4 t = *reinterpret_cast<const float4*>(q);
+                            f[j] = f2(t.x, t.y);
+                            mf[j] = f2(t.z, t.w);
+                        } else {
+                            f[j] = *reinterpret_cast<const float2*>(q);
+                        }
+                    }
                 }
-                X = mulc_add(X, hi2, lo2, f);
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j) {
+                    if (r0 + j < c.rank) {
+                        if (kMom) MX = mulc_add(fma2(len2, X, MX), hi2, lo2, mf[j]);
+                        X = mulc_add(X, hi2, lo2, f[j]);
+                    }
+                }
             }
             if (level == 0) {
-                int other = (lane < c.cluster && lane != c.rank) ? __float_as_int(c.flags[lane]) : 0;
+                const int other = (lane < c.cluster && lane != c.rank)
+                                      ? __float_as_int(c.peers[lane * RW::kBlockF + kCs * (lane < c.rank ? RW::kF : RW::kR)]) : 0;
                 flag = __any_sync(0xffffffffu, (other | any) != 0) ? 1 : 0;
             }
         }
         c.cta[lane] = X.x; c.cta[kCs + lane] = X.y;
         if (kMom) { c.cta[2 * kCs + lane] = MX.x; c.cta[3 * kCs + lane] = MX.y; }
-        if (lane == 0) c.flags[c.rank] = __int_as_float(flag);
+        if (lane == 0) *c.flag = static_cast<unsigned>(flag);
     }
     if (warp == scanR) {
         float2 Y = f2(0.f, 0.f);
         if (c.cluster > 1) {
             const float2 hi2 = dup(c.consts[kLamC_hi * kCs + lane]), lo2 = dup(c.consts[kLamC_lo * kCs + lane]);
-#pragma unroll 4
-            for (int r = c.cluster - 1; r > c.rank; --r)
-                Y = mulc_add(Y, hi2, lo2, *reinterpret_cast<const float2*>(c.peers + (r * kCs + lane) * RW::kF));
+            for (int r0 = c.cluster - 1; r0 > c.rank; r0 -= kBatch) {
+                float2 f[kBatch];
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j) {
+                    f[j] = f2(0.f, 0.f);
+                    if (r0 - j > c.rank) f[j] = *reinterpret_cast<const float2*>(c.peers + (r0 - j) * RW::kBlockF + lane * 2);
+                }
+#pragma unroll
+                for (int j = 0; j < kBatch; ++j)
+                    if (r0 - j > c.rank) Y = mulc_add(Y, hi2, lo2, f[j]);
+            }
         }
         c.cta[RW::kF * kCs + lane] = Y.x; c.cta[(RW::kF + 1) * kCs + lane] = Y.y;
     }
@@ -357,7 +430,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
             e.MP = MPw;
             e.S = Pair2{mulc_add(Sw.n, l16h, l16l, keepA.n), mulc_add(Sw.d, l16h, l16l, keepA.d)};
         }
-        if (level == 0) unsafe = __float_as_int(c.flags[c.rank]) != 0;
+        if (level == 0) unsafe = *c.flag != 0u;
     }
     return e;
 }
@@ -558,14 +631,18 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     Ctx c;
     c.sub = slot_k + RW::kSlots * slot_floats;
     c.peers = c.sub + nw * (RW::kSub * kCs);
-    c.flags = c.peers + RW::kPeerFloats;
-    c.cta = c.flags + kCs;
+    c.stage = c.peers + RW::kPeerFloats;
+    c.cta = c.stage + RW::kBlockF + RW::kBlockR;
     c.consts = c.cta + RW::kSub * kCs;
     uint64_t* full = reinterpret_cast<uint64_t*>(c.consts + kConstRows * kCs);
     c.xbar = full + 1;
+    uint64_t* gfull = full + 3;          // backward: gy arrives on a barrier of its own (first needed in pass 2)
+    c.flag = reinterpret_cast<unsigned*>(full + 4);
     c.status = p.status;
     c.warp = warp; c.lane = lane; c.n_warps = nw; c.n_tok = p.n_tok; c.cluster = p.cluster;
     c.rank = p.cluster > 1 ? static_cast<int>(cluster_rank()) : 0;
+    c.spin_limit = p.spin_limit;
+    c.withhold = c.rank == p.withhold_rank;
 
 #ifdef VRWKV_TIMELINE
     long long* tl_base = reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.status) + 256);
@@ -578,8 +655,8 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             unsigned long long gt; unsigned smid;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            tl_base[(tl_slot * 2) * kTlMarks + 22] = static_cast<long long>(gt);
-            tl_base[(tl_slot * 2) * kTlMarks + 23] = smid;
+            tl_base[(tl_slot * 2) * kTlMarks + 30] = static_cast<long long>(gt);
+            tl_base[(tl_slot * 2) * kTlMarks + 31] = smid;
         }
     }
 #endif
@@ -592,17 +669,21 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     if (threadIdx.x == 0) {
         sm100::mbar_init(full, 1);
         for (int l = 0; l < RW::kLevels; ++l) sm100::mbar_init(c.xbar + l, 1);
+        if (kBwd) sm100::mbar_init(gfull, 1);
         sm100::mbar_init_fence();
-        sm100::mbar_expect_tx(full, RW::kSlots * slot_bytes);
+        sm100::mbar_expect_tx(full, 2 * slot_bytes);
         sm100::tma_load_3d(slot_k, &map_k, full, strip * kCs, tok0, b);
         sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
-        if (kBwd) sm100::tma_load_3d(slot_g, &map_g, full, strip * kCs, tok0, b);
+        if (kBwd) {
+            sm100::mbar_expect_tx(gfull, slot_bytes);
+            sm100::tma_load_3d(slot_g, &map_g, gfull, strip * kCs, tok0, b);
+        }
         if (p.cluster > 1) {
-            // bytes the other CTAs will send per level: a record per channel from every lower rank
-            // (towards later tokens) and from every higher rank (towards earlier), + their flags once
-            const uint32_t rec = kCs * (static_cast<uint32_t>(c.rank) * RW::kF * 4u + static_cast<uint32_t>(p.cluster - 1 - c.rank) * 8u);
-            sm100::mbar_expect_tx(c.xbar, rec + static_cast<uint32_t>(p.cluster - 1) * 4u);
-            if (kBwd) sm100::mbar_expect_tx(c.xbar + 1, rec);
+            // bytes the other CTAs will send per level: a block from every lower rank (towards later
+            // tokens) and from every higher rank (towards earlier ones)
+            const uint32_t bytes = static_cast<uint32_t>(c.rank) * (kCs * RW::kF + 1) * 4u + static_cast<uint32_t>(p.cluster - 1 - c.rank) * (kCs * RW::kR + 1) * 4u;
+            sm100::mbar_expect_tx(c.xbar, bytes);
+            if (kBwd) sm100::mbar_expect_tx(c.xbar + 1, bytes);
         }
     }
     {
@@ -610,22 +691,16 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         // would drift by distance * 6e-8.  Six exponentials, spread over the warps (lane = channel).
         const int ch = strip * kCs + lane;
         const double wd = (ch < p.C) ? static_cast<double>(p.w[ch]) : 0.0;
-        for (int task = warp; task < 6; task += nw) {
-            if (task == 0) {
-                c.consts[kLam * kCs + lane] = static_cast<float>(exp(-wd));
-                c.consts[kWl2 * kCs + lane] = static_cast<float>(wd * 1.4426950408889634);
-            } else if (task == 1) {
-                const double ud = (ch < p.C) ? static_cast<double>(p.u[ch]) : 0.0;
-                c.consts[kCuw * kCs + lane] = static_cast<float>(exp(ud + wd));
-            } else if (task == 2) {
-                c.consts[kInvLam * kCs + lane] = static_cast<float>(exp(wd));
-            } else {
-                const double x = exp(-wd * (task == 3 ? kL : task == 4 ? kSpan : p.n_tok));
-                const float hi = static_cast<float>(x);
-                const int row = task == 3 ? kLam16_hi : task == 4 ? kLam32_hi : kLamC_hi;
-                c.consts[row * kCs + lane] = hi;
-                c.consts[(row + 1) * kCs + lane] = static_cast<float>(x - static_cast<double>(hi));
-            }
+        const double ud = (ch < p.C) ? static_cast<double>(p.u[ch]) : 0.0;
+        // tasks: 0 lambda (+ w log2 e), 1 e^{u+w}, 2..4 lambda^16, lambda^32, lambda^n_tok as (high, low)
+        for (int task = warp; task < 5; task += nw) {
+            const double arg = task == 0 ? -wd : task == 1 ? ud + wd : -wd * (task == 2 ? kL : task == 3 ? kSpan : p.n_tok);
+            const double x = exp(arg);
+            const float hi = static_cast<float>(x);
+            const int row = task == 0 ? kLam : task == 1 ? kCuw : task == 2 ? kLam16_hi : task == 3 ? kLam32_hi : kLamC_hi;
+            c.consts[row * kCs + lane] = hi;
+            if (task >= 2) c.consts[(row + 1) * kCs + lane] = static_cast<float>(x - static_cast<double>(hi));
+            if (task == 0) c.consts[kWl2 * kCs + lane] = static_cast<float>(wd * 1.4426950408889634);
         }
     }
     __syncthreads();
@@ -662,24 +737,33 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     {
         float2 mu = f2(1.f, 1.f);
         const float2 nwl2 = f2(-wl2.x, -wl2.y), l2e = dup(kLog2e);
+        // loads of a group of tokens go first: a store into one slot may not be moved past a later load
+        // from another slot by the compiler, so token-by-token code would expose every load's latency
 #pragma unroll
-        for (int i = 0; i < kL; ++i) {
-            const float2 k = k2[i * kRow], v = v2[i * kRow];
-            if (i < n) kmax = f2(fmaxf(kmax.x, fabsf(k.x)), fmaxf(kmax.y, fabsf(k.y)));
-            const float2 t = fma2(k, l2e, nwl2);
-            const float2 e = f2(ex2(t.x), ex2(t.y));
-            const float2 zx = mul2(e, v);
-            k2[i * kRow] = zx;
-            v2[i * kRow] = e;
-            F.n = fma2(lam2, F.n, zx);
-            F.d = fma2(lam2, F.d, e);
-            if (kBwd) {
-                MF.n = fma2(lam2, MF.n, F.n);
-                MF.d = fma2(lam2, MF.d, F.d);
+        for (int g = 0; g < kL; g += kGroup) {
+            float2 kk[kGroup], vv[kGroup];
+#pragma unroll
+            for (int j = 0; j < kGroup; ++j) { kk[j] = k2[(g + j) * kRow]; vv[j] = v2[(g + j) * kRow]; }
+#pragma unroll
+            for (int j = 0; j < kGroup; ++j) {
+                const int i = g + j;
+                const float2 k = kk[j], v = vv[j];
+                if (i < n) kmax = f2(fmaxf(kmax.x, fabsf(k.x)), fmaxf(kmax.y, fabsf(k.y)));
+                const float2 t = fma2(k, l2e, nwl2);
+                const float2 e = f2(ex2(t.x), ex2(t.y));
+                const float2 zx = mul2(e, v);
+                k2[i * kRow] = zx;
+                v2[i * kRow] = e;
+                F.n = fma2(lam2, F.n, zx);
+                F.d = fma2(lam2, F.d, e);
+                if (kBwd) {
+                    MF.n = fma2(lam2, MF.n, F.n);
+                    MF.d = fma2(lam2, MF.d, F.d);
+                }
+                R.n = fma2(mu, zx, R.n);
+                R.d = fma2(mu, e, R.d);
+                mu = mul2(mu, lam2);
             }
-            R.n = fma2(mu, zx, R.n);
-            R.d = fma2(mu, e, R.d);
-            mu = mul2(mu, lam2);
         }
     }
     const float Tf = static_cast<float>(p.T);
@@ -690,24 +774,15 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     TL_MARK(4);
 
     float2 gw = f2(0.f, 0.f), gu = f2(0.f, 0.f);
+    if (kBwd && !sm100::mbar_wait(gfull, 0, kSpinLimit)) atomicOr(p.status, 2u);
     if (unsafe) {
-        // the whole cluster takes this branch together: fetch k and v again, then the exact path,
-        // one channel of the pair at a time
-        sm100::fence_proxy_async_smem();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            sm100::mbar_expect_tx(full, 2 * slot_bytes);
-            sm100::tma_load_3d(slot_k, &map_k, full, strip * kCs, tok0, b);
-            sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
-        }
-        if (!sm100::mbar_wait(full, 1, kSpinLimit)) atomicOr(p.status, 2u);
-        const int sub = 2 * warp + upper;
-        float* ks = reinterpret_cast<float*>(k2);
-        float* vs = reinterpret_cast<float*>(v2);
-        float* gs = reinterpret_cast<float*>(g2);
-        exact_subchunk<kBwd>(c, sub, 2 * pr, ks, vs, gs, n, w2.x, u2.x, gw.x, gu.x);
-        exact_subchunk<kBwd>(c, sub, 2 * pr + 1, ks + 1, vs + 1, gs + 1, n, w2.y, u2.y, gw.y, gu.y);
-    } else if (!kBwd) {
+        // the whole cluster takes this branch together: the unit is left to the exact kernel, which
+        // runs right after this one (nothing of this CTA is in flight any more: its tiles have
+        // landed and everything the other CTAs sent has been waited for)
+        if (c.rank == 0 && threadIdx.x == 0) p.redo_list[atomicAdd(p.redo_count, 1u)] = unit;
+        return;
+    }
+    if (!kBwd) {
         // ---- forward, pass 2: y = (P + S + e^{u} x) ratio, in place of the numerator term ----
         Pair2 P = e1.P;
 #pragma unroll
@@ -721,14 +796,20 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 S.d = fma2(lam2, S.d, v2[i * kRow]);
             }
 #pragma unroll
-            for (int j = 0; j < kStash; ++j) {
-                const int i = blk * kStash + j;
-                const float2 zx = k2[i * kRow], zy = v2[i * kRow];
-                const float2 nn = fma2(c2, zx, add2(P.n, sn[j]));
-                const float2 dd = fma2(c2, zy, add2(P.d, sd[j]));
-                k2[i * kRow] = mul2(nn, f2(rcp(dd.x), rcp(dd.y)));
-                P.n = fma2(lam2, P.n, zx);
-                P.d = fma2(lam2, P.d, zy);
+            for (int g = 0; g < kStash; g += kGroup) {
+                float2 zxs[kGroup], zys[kGroup];
+#pragma unroll
+                for (int j = 0; j < kGroup; ++j) { zxs[j] = k2[(blk * kStash + g + j) * kRow]; zys[j] = v2[(blk * kStash + g + j) * kRow]; }
+#pragma unroll
+                for (int j = 0; j < kGroup; ++j) {
+                    const int i = blk * kStash + g + j;
+                    const float2 zx = zxs[j], zy = zys[j];
+                    const float2 nn = fma2(c2, zx, add2(P.n, sn[g + j]));
+                    const float2 dd = fma2(c2, zy, add2(P.d, sd[g + j]));
+                    k2[i * kRow] = mul2(nn, f2(rcp(dd.x), rcp(dd.y)));
+                    P.n = fma2(lam2, P.n, zx);
+                    P.d = fma2(lam2, P.d, zy);
+                }
             }
         }
     } else {
@@ -755,33 +836,42 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                     S.d = fma2(lam2, S.d, v2[i * kRow]);
                 }
 #pragma unroll
-                for (int j = 0; j < kStash; ++j) {
-                    const int i = blk * kStash + j;
-                    const float2 zx = k2[i * kRow], zy = v2[i * kRow];
-                    const float2 nn = fma2(c2, zx, add2(P.n, sn[j]));
-                    const float2 dd = fma2(c2, zy, add2(P.d, sd[j]));
-                    // rows past T: gy = 0 must stay 0 whatever the denominator
-                    const float2 inv = f2(rcp(fmaxf(dd.x, 1e-37f)), rcp(fmaxf(dd.y, 1e-37f)));
-                    const float2 ny = f2(nn.x * -inv.x, nn.y * -inv.y);
-                    const float2 g = mul2(g2[i * kRow], inv);
-                    const float2 h = mul2(g, ny);                  // -H
-                    g2[i * kRow] = g;
-                    hn[i] = h;
-                    gu = fma2(zx, g, gu);
-                    gu = fma2(zy, h, gu);
-                    gwa = fma2(g, PM.n, gwa);
-                    gwa = fma2(h, PM.d, gwa);
-                    P.n = fma2(lam2, P.n, zx);
-                    P.d = fma2(lam2, P.d, zy);
-                    PM.n = fma2(lam2, PM.n, P.n);
-                    PM.d = fma2(lam2, PM.d, P.d);
-                    rr.n = fma2(lam2, rr.n, g);
-                    rr.d = fma2(lam2, rr.d, h);
-                    mr.n = fma2(lam2, mr.n, rr.n);
-                    mr.d = fma2(lam2, mr.d, rr.d);
-                    q.n = fma2(mu, g, q.n);
-                    q.d = fma2(mu, h, q.d);
-                    mu = mul2(mu, lam2);
+                for (int g = 0; g < kStash; g += kGroupB) {
+                    float2 zxs[kGroupB], zys[kGroupB], gys[kGroupB];
+#pragma unroll
+                    for (int j = 0; j < kGroupB; ++j) {
+                        const int i = blk * kStash + g + j;
+                        zxs[j] = k2[i * kRow]; zys[j] = v2[i * kRow]; gys[j] = g2[i * kRow];
+                    }
+#pragma unroll
+                    for (int j = 0; j < kGroupB; ++j) {
+                        const int i = blk * kStash + g + j;
+                        const float2 zx = zxs[j], zy = zys[j];
+                        const float2 nn = fma2(c2, zx, add2(P.n, sn[g + j]));
+                        const float2 dd = fma2(c2, zy, add2(P.d, sd[g + j]));
+                        // rows past T: gy = 0 must stay 0 whatever the denominator
+                        const float2 inv = f2(rcp(fmaxf(dd.x, 1e-37f)), rcp(fmaxf(dd.y, 1e-37f)));
+                        const float2 ny = f2(nn.x * -inv.x, nn.y * -inv.y);
+                        const float2 g_ = mul2(gys[j], inv);
+                        const float2 h = mul2(g_, ny);                  // -H
+                        g2[i * kRow] = g_;
+                        hn[i] = h;
+                        gu = fma2(zx, g_, gu);
+                        gu = fma2(zy, h, gu);
+                        gwa = fma2(g_, PM.n, gwa);
+                        gwa = fma2(h, PM.d, gwa);
+                        P.n = fma2(lam2, P.n, zx);
+                        P.d = fma2(lam2, P.d, zy);
+                        PM.n = fma2(lam2, PM.n, P.n);
+                        PM.d = fma2(lam2, PM.d, P.d);
+                        rr.n = fma2(lam2, rr.n, g_);
+                        rr.d = fma2(lam2, rr.d, h);
+                        mr.n = fma2(lam2, mr.n, rr.n);
+                        mr.d = fma2(lam2, mr.d, rr.d);
+                        q.n = fma2(mu, g_, q.n);
+                        q.d = fma2(mu, h, q.d);
+                        mu = mul2(mu, lam2);
+                    }
                 }
             }
             gu = mul2(gu, c2);
@@ -796,7 +886,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         // ---- backward, pass 3: gk, gv in place of the terms; gw from pairs (output earlier than input).
         //      Adjoint states are kept divided by lambda, so that [G, -H] enter without a multiply. ----
         {
-            const float2 il2 = *reinterpret_cast<const float2*>(c.consts + kInvLam * kCs + 2 * pr);
+            const float2 il2 = f2(rcp(lam2.x), rcp(lam2.y));
             Pair2 Rp{mul2(e2.P.n, il2), mul2(e2.P.d, il2)}, MRp{mul2(e2.MP.n, il2), mul2(e2.MP.d, il2)};
             const Pair2 Qin{mul2(e2.S.n, il2), mul2(e2.S.d, il2)};
 #pragma unroll
@@ -810,20 +900,29 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                     Q.d = fma2(lam2, Q.d, hn[i]);
                 }
 #pragma unroll
-                for (int j = 0; j < kStash; ++j) {
-                    const int i = blk * kStash + j;
-                    const float2 g = g2[i * kRow], h = hn[i];
-                    const float2 zx = k2[i * kRow], zy = v2[i * kRow];
-                    const float2 AG = fma2(c2, g, add2(sn[j], Rp.n));
-                    const float2 AH = fma2(c2, h, add2(sd[j], Rp.d));      // -A^H
-                    v2[i * kRow] = mul2(zy, AG);
-                    k2[i * kRow] = fma2(zx, AG, mul2(zy, AH));
-                    gwa = fma2(zx, MRp.n, gwa);
-                    gwa = fma2(zy, MRp.d, gwa);
-                    Rp.n = fma2(lam2, Rp.n, g);
-                    Rp.d = fma2(lam2, Rp.d, h);
-                    MRp.n = fma2(lam2, MRp.n, Rp.n);
-                    MRp.d = fma2(lam2, MRp.d, Rp.d);
+                for (int g = 0; g < kStash; g += kGroupB) {
+                    float2 zxs[kGroupB], zys[kGroupB], gs_[kGroupB];
+#pragma unroll
+                    for (int j = 0; j < kGroupB; ++j) {
+                        const int i = blk * kStash + g + j;
+                        zxs[j] = k2[i * kRow]; zys[j] = v2[i * kRow]; gs_[j] = g2[i * kRow];
+                    }
+#pragma unroll
+                    for (int j = 0; j < kGroupB; ++j) {
+                        const int i = blk * kStash + g + j;
+                        const float2 g_ = gs_[j], h = hn[i];
+                        const float2 zx = zxs[j], zy = zys[j];
+                        const float2 AG = fma2(c2, g_, add2(sn[g + j], Rp.n));
+                        const float2 AH = fma2(c2, h, add2(sd[g + j], Rp.d));      // -A^H
+                        v2[i * kRow] = mul2(zy, AG);
+                        k2[i * kRow] = fma2(zx, AG, mul2(zy, AH));
+                        gwa = fma2(zx, MRp.n, gwa);
+                        gwa = fma2(zy, MRp.d, gwa);
+                        Rp.n = fma2(lam2, Rp.n, g_);
+                        Rp.d = fma2(lam2, Rp.d, h);
+                        MRp.n = fma2(lam2, MRp.n, Rp.n);
+                        MRp.d = fma2(lam2, MRp.d, Rp.d);
+                    }
                 }
             }
         }
@@ -851,9 +950,100 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         }
     }
     TL_MARK(8);
-    if (threadIdx.x == 0) sm100::tma_store_wait_all();
+    if (threadIdx.x == 0) sm100::tma_store_wait_read();   // shared memory may go once the stores have read it
     TL_MARK(9);
 }
+
+// ---- the exact kernel ----------------------------------------------------------------------------
+// Runs after the fast kernel with a small persistent grid of clusters and serves the units it left
+// behind (normally none: one load and out).  Same shared-memory layout, same tiles, same work split
+// between the CTAs of a cluster, per-token max-shifted arithmetic.
+template <bool kBwd>
+__global__ void __launch_bounds__(kMaxThreads, 1)
+biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_o0,
+                   const __grid_constant__ CUtensorMap map_o1, const Params p) {
+    using RW = Rows<kBwd>;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pr = lane & 15, upper = lane >> 4;
+    const int nw = p.n_warps;
+    const int slot_floats = p.n_tok * kCs;
+    float* slot_k = reinterpret_cast<float*>(smem_raw);
+    float* slot_v = slot_k + slot_floats;
+    float* slot_g = slot_v + slot_floats;
+    Ctx c;
+    c.sub = slot_k + RW::kSlots * slot_floats;
+    c.peers = c.sub + nw * (RW::kSub * kCs);
+    c.stage = c.peers + RW::kPeerFloats;
+    c.cta = c.stage + RW::kBlockF + RW::kBlockR;
+    c.consts = c.cta + RW::kSub * kCs;
+    uint64_t* full = reinterpret_cast<uint64_t*>(c.consts + kConstRows * kCs);
+    c.xbar = full + 1;
+    c.flag = reinterpret_cast<unsigned*>(full + 4);
+    c.status = p.status;
+    c.spin_limit = kSpinLimit;
+    c.withhold = false;
+    c.warp = warp; c.lane = lane; c.n_warps = nw; c.n_tok = p.n_tok; c.cluster = p.cluster;
+    c.rank = p.cluster > 1 ? static_cast<int>(cluster_rank()) : 0;
+
+    const unsigned n_redo = *reinterpret_cast<volatile unsigned*>(p.redo_count);
+    const int n_clusters = static_cast<int>(gridDim.x) / p.cluster, mine = static_cast<int>(blockIdx.x) / p.cluster;
+    if (static_cast<unsigned>(mine) >= n_redo) return;       // the same for every CTA of a cluster
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(full, 1);
+        sm100::mbar_init_fence();
+    }
+    __syncthreads();
+    const int tok0 = c.rank * p.n_tok;
+    const uint32_t slot_bytes = static_cast<uint32_t>(slot_floats) * 4u;
+    const int row0 = warp * kSpan + upper * kL;
+    const int n = max(0, min(kL, p.T - (tok0 + row0)));
+    float* ks = slot_k + row0 * kCs + 2 * pr;
+    float* vs = slot_v + row0 * kCs + 2 * pr;
+    float* gs = slot_g + row0 * kCs + 2 * pr;
+    uint32_t phase = 0;
+    for (unsigned j = mine; j < n_redo; j += n_clusters) {
+        const int unit = p.redo_list[j];
+        const int b = unit / p.n_strips, strip = unit - b * p.n_strips;
+        if (threadIdx.x == 0) {
+            sm100::mbar_expect_tx(full, RW::kSlots * slot_bytes);
+            sm100::tma_load_3d(slot_k, &map_k, full, strip * kCs, tok0, b);
+            sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
+            if (kBwd) sm100::tma_load_3d(slot_g, &map_g, full, strip * kCs, tok0, b);
+        }
+        const int ch0 = strip * kCs + 2 * pr;
+        const float2 w2 = (ch0 < p.C) ? *reinterpret_cast<const float2*>(p.w + ch0) : f2(0.f, 0.f);
+        const float2 u2 = (ch0 < p.C) ? *reinterpret_cast<const float2*>(p.u + ch0) : f2(0.f, 0.f);
+        if (!sm100::mbar_wait(full, phase, kSpinLimit)) atomicOr(p.status, 2u);
+        phase ^= 1u;
+        float2 gw = f2(0.f, 0.f), gu = f2(0.f, 0.f);
+        const int sub = 2 * warp + upper;
+        exact_subchunk<kBwd>(c, sub, 2 * pr, ks, vs, gs, n, w2.x, u2.x, gw.x, gu.x);
+        exact_subchunk<kBwd>(c, sub, 2 * pr + 1, ks + 1, vs + 1, gs + 1, n, w2.y, u2.y, gw.y, gu.y);
+        if (kBwd) {
+            *reinterpret_cast<float2*>(gs) = gw;
+            *reinterpret_cast<float2*>(gs + kCs) = gu;
+        }
+        sm100::fence_proxy_async_smem();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            sm100::tma_store_3d(&map_o0, slot_k, strip * kCs, tok0, b);
+            if (kBwd) sm100::tma_store_3d(&map_o1, slot_v, strip * kCs, tok0, b);
+            sm100::tma_store_commit();
+        }
+        if (kBwd && warp < 2) {
+            for (int jj = warp; jj < 2; jj += min(nw, 2)) {
+                float acc = 0.f;
+                for (int s = 0; s < 2 * nw; ++s) acc += slot_g[(s * kL + jj) * kCs + lane];
+                p.partial[((static_cast<size_t>(unit) * p.cluster + c.rank) * 2 + jj) * kCs + lane] = acc;
+            }
+        }
+        if (threadIdx.x == 0) sm100::tma_store_wait_read();
+        __syncthreads();      // the slots are free for the next unit
+    }
+}
+
 // out[j][c] = sum over sequences and cluster ranks of partial[cta][j][c % 32], fixed order
 __global__ void __launch_bounds__(1024)
 reduce_partials(Params p, float* __restrict__ out) {
@@ -880,6 +1070,11 @@ reduce_partials(Params p, float* __restrict__ out) {
 // ---- host side ------------------------------------------------------------------------------------
 constexpr int kFwdStash = 8;
 constexpr int kBwdStash = 8;
+
+// test mode: rank 1 of every cluster withholds its sends and waits give up after 2^10 polls, so that
+// the bounded waits can be seen to run out (status bit 0) without anything hanging
+static std::atomic<bool> g_withhold{false};
+void set_withhold_test(bool on) { g_withhold.store(on); }
 
 struct Plan {
     int cluster = 0, n_warps = 0, n_tok = 0;
@@ -927,6 +1122,12 @@ static bool fits(const Plan& pl) {
                                             static_cast<int>(smem_bytes<true>(kMaxWarps))) == cudaSuccess;
         good = good && cudaFuncSetAttribute(kernel_ptr<false>(), cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         good = good && cudaFuncSetAttribute(kernel_ptr<true>(), cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        const void* ex[2] = {reinterpret_cast<const void*>(biwkv_exact_kernel<false>), reinterpret_cast<const void*>(biwkv_exact_kernel<true>)};
+        for (int i = 0; i < 2; ++i) {
+            good = good && cudaFuncSetAttribute(ex[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(i ? smem_bytes<true>(kMaxWarps) : smem_bytes<false>(kMaxWarps))) == cudaSuccess;
+            good = good && cudaFuncSetAttribute(ex[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        }
         if (!good) cudaGetLastError();
         d.ok = good;
     }
@@ -967,8 +1168,8 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 size_t workspace_bytes(int B, int T, int C, bool bwd) {
     Plan pl;
     if (!make_plan(T, pl)) return 256;
-    const size_t ctas = static_cast<size_t>(B) * ((C + kCs - 1) / kCs) * pl.cluster;
-    return 256 + (bwd ? align_up(ctas * 2 * kCs * sizeof(float), 256) : 0);
+    const size_t units = static_cast<size_t>(B) * ((C + kCs - 1) / kCs);
+    return 256 + align_up(units * sizeof(int), 256) + (bwd ? align_up(units * pl.cluster * 2 * kCs * sizeof(float), 256) : 0);
 }
 
 template <bool kBwd>
@@ -983,7 +1184,12 @@ static int launch(int B, int T, int C, const float* w, const float* u, const flo
     p.w = w; p.u = u;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     p.status = reinterpret_cast<unsigned*>(ws);
-    p.partial = reinterpret_cast<float*>(ws + 256);
+    const size_t units = static_cast<size_t>(B) * p.n_strips;
+    p.redo_count = reinterpret_cast<unsigned*>(ws) + 1;
+    p.redo_list = reinterpret_cast<int*>(ws + 256);
+    p.partial = reinterpret_cast<float*>(ws + 256 + align_up(units * sizeof(int), 256));
+    p.spin_limit = g_withhold.load() ? (1u << 10) : kSpinLimit;
+    p.withhold_rank = g_withhold.load() ? 1 : -1;
     cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
     CUtensorMap mk, mv, mg, m0, m1;
     bool ok = tensor_map::make_btc_f32(&mk, k, B, T, C, kCs, pl.n_tok) && tensor_map::make_btc_f32(&mv, v, B, T, C, kCs, pl.n_tok) &&
@@ -1009,7 +1215,14 @@ static int launch(int B, int T, int C, const float* w, const float* u, const flo
         set_error_detail(cudaGetErrorName(err));
         return -1;
     }
-    int launched = 1;
+    // the exact kernel: a few clusters that serve whatever the fast kernel left behind
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>(units, 16)) * pl.cluster);
+    const cudaError_t err2 = cudaLaunchKernelEx(&cfg, biwkv_exact_kernel<kBwd>, mk, mv, mg, m0, m1, p);
+    if (err2 != cudaSuccess) {
+        set_error_detail(cudaGetErrorName(err2));
+        return -1;
+    }
+    int launched = 2;
     if (kBwd) {
         reduce_partials<<<dim3(p.n_strips, 2), dim3(32, 32), 0, stream>>>(p, gwgu);
         ++launched;

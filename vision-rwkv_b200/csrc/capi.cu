@@ -11,7 +11,7 @@ namespace {
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_path{0};   // 0 auto (resident, else fused, else generic), 1 generic only, 2 skip the resident path
 
-char g_detail[256] = "";
+thread_local char g_detail[256] = "";   // per calling thread: no lock needed
 
 inline bool misaligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) != 0; }
 
@@ -63,8 +63,9 @@ const char* vrwkv_status_string(int status) {
 unsigned long long vrwkv_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int vrwkv_set_path(int path) {
-    if (path < 0 || path > 2) return VRWKV_ERR_SHAPE;
-    g_path.store(path);
+    if (path < 0 || path > 3) return VRWKV_ERR_SHAPE;
+    biwkv::resident::set_withhold_test(path == 3);
+    g_path.store(path == 3 ? 0 : path);
     return VRWKV_OK;
 }
 
@@ -182,7 +183,7 @@ int vrwkv_biwkv_backward_bf16(int B, int T, int C, const float* w, const float* 
 static int check_wkv6(int B, int T, int C, int H) {
     if (B <= 0 || T <= 0 || C <= 0 || H <= 0) return VRWKV_ERR_SHAPE;
     if (C != 64 * H) return VRWKV_ERR_HEAD_SIZE;
-    if (static_cast<long long>(B) * H > 2000000000LL || T > 4000000) return VRWKV_ERR_SHAPE;
+    if (static_cast<long long>(B) * H > 1000000000LL || T > 4000000) return VRWKV_ERR_SHAPE;   // 2*B*H is a grid dimension
     return VRWKV_OK;
 }
 static inline bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }

@@ -22,6 +22,7 @@ namespace resident {
 // Cluster-resident single-pass path (biwkv_resident.cu): float32, C % 4 == 0, 16-byte aligned
 // tensors, T <= 4096.  True when it can serve this call on the current device.
 bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd);
+void set_withhold_test(bool on);   // test only: one rank per cluster sends nothing, waits give up early
 size_t workspace_bytes(int B, int T, int C, bool bwd);
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
             float* y, void* workspace, cudaStream_t stream);

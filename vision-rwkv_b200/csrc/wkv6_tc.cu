@@ -36,6 +36,7 @@
 // Reference being replaced: classification/mmcls_custom/models/backbones/cuda_v6/wkv6_cuda.cu:6-97.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <mutex>
 #include <cstdint>
 #include "sm100_async.cuh"
 #include "tensor_map.h"
@@ -832,8 +833,14 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
 }
 
+// cudaFuncSetAttribute applies to the current device only: one flag per device, under a lock
 static bool configure_once() {
-    static bool configured = false;
+    static std::mutex lock;
+    static bool done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    std::lock_guard<std::mutex> guard(lock);
+    bool& configured = done[dev & 63];
     if (!configured) {
         if (cudaFuncSetAttribute(wkv6_tc_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(sizeof(Smem))) != cudaSuccess ||
