@@ -82,7 +82,7 @@ struct Rows {
     static constexpr int kSlots = kBwd ? 3 : 2;
     static constexpr int kBlockF = kCs * kF + 4;   // floats of a CTA aggregate towards later tokens + flag word (16-byte padded)
     static constexpr int kBlockR = kCs * kR + 4;   // ... towards earlier tokens
-    static constexpr int kPeerFloats = kMaxCluster * kBlockF;    // one block slot per rank
+    static constexpr int kPeerFloats = (kMaxCluster - 1) * kBlockF;   // one block slot per other rank (ranks above this CTA's shift down by one)
 };
 
 struct Params {
@@ -108,7 +108,7 @@ static inline size_t smem_bytes(int n_warps) {
     using R = Rows<kBwd>;
     const size_t data = static_cast<size_t>(R::kSlots) * n_warps * kSpan * kCs * sizeof(float);
     const size_t rec = (static_cast<size_t>(n_warps) * R::kSub * kCs + R::kPeerFloats + R::kBlockF + R::kBlockR + R::kSub * kCs + kConstRows * kCs) * sizeof(float);
-    return data + rec + 64;
+    return data + rec + 192;
 }
 
 // ---- small device helpers -----------------------------------------------------------------------
@@ -323,7 +323,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
         for (int r = warp; r < c.cluster; r += nw) {
             if (r == c.rank) continue;
             const uint32_t rb = peer_addr(c.peers, r);
-            const uint32_t slot = rb + static_cast<uint32_t>(c.rank * RW::kBlockF) * 4u;
+            const uint32_t slot = rb + static_cast<uint32_t>((c.rank - (c.rank > r ? 1 : 0)) * RW::kBlockF) * 4u;
             if (r > c.rank) {
                 if (kMom) st_async4(slot + lane * 16u, *reinterpret_cast<const float4*>(c.stage + lane * 4), rb + bar_off);
                 else st_async2(slot + lane * 8u, *reinterpret_cast<const float2*>(c.stage + lane * 2), rb + bar_off);
@@ -353,7 +353,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
                     f[j] = f2(0.f, 0.f);
                     mf[j] = f2(0.f, 0.f);
                     if (r0 + j < c.rank) {
-                        const float* q = c.peers + (r0 + j) * RW::kBlockF + lane * RW::kF;
+                        const float* q = c.peers + (r0 + j) * RW::kBlockF + lane * RW::kF;      // lower ranks: slot = rank
                         if (kMom) {
                             const float4 t = *reinterpret_cast<const float4*>(q);
                             f[j] = f2(t.x, t.y);
@@ -373,7 +373,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
             }
             if (level == 0) {
                 const int other = (lane < c.cluster && lane != c.rank)
-                                      ? __float_as_int(c.peers[lane * RW::kBlockF + kCs * (lane < c.rank ? RW::kF : RW::kR)]) : 0;
+                                      ? __float_as_int(c.peers[(lane - (lane > c.rank ? 1 : 0)) * RW::kBlockF + kCs * (lane < c.rank ? RW::kF : RW::kR)]) : 0;
                 flag = __any_sync(0xffffffffu, (other | any) != 0) ? 1 : 0;
             }
         }
@@ -390,7 +390,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
 #pragma unroll
                 for (int j = 0; j < kBatch; ++j) {
                     f[j] = f2(0.f, 0.f);
-                    if (r0 - j > c.rank) f[j] = *reinterpret_cast<const float2*>(c.peers + (r0 - j) * RW::kBlockF + lane * 2);
+                    if (r0 - j > c.rank) f[j] = *reinterpret_cast<const float2*>(c.peers + (r0 - j - 1) * RW::kBlockF + lane * 2);
                 }
 #pragma unroll
                 for (int j = 0; j < kBatch; ++j)
@@ -634,10 +634,10 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     c.stage = c.peers + RW::kPeerFloats;
     c.cta = c.stage + RW::kBlockF + RW::kBlockR;
     c.consts = c.cta + RW::kSub * kCs;
-    uint64_t* full = reinterpret_cast<uint64_t*>(c.consts + kConstRows * kCs);
-    c.xbar = full + 1;
-    uint64_t* gfull = full + 3;          // backward: gy arrives on a barrier of its own (first needed in pass 2)
-    c.flag = reinterpret_cast<unsigned*>(full + 4);
+    uint64_t* full = reinterpret_cast<uint64_t*>(c.consts + kConstRows * kCs);   // [kMaxWarps]: k, v of one span each
+    uint64_t* gfull = full + kMaxWarps;  // [kMaxWarps]: backward, gy of one span each (first needed in pass 2)
+    c.xbar = gfull + kMaxWarps;
+    c.flag = reinterpret_cast<unsigned*>(c.xbar + 2);
     c.status = p.status;
     c.warp = warp; c.lane = lane; c.n_warps = nw; c.n_tok = p.n_tok; c.cluster = p.cluster;
     c.rank = p.cluster > 1 ? static_cast<int>(cluster_rank()) : 0;
@@ -666,18 +666,24 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int tok0 = c.rank * p.n_tok;
     const uint32_t slot_bytes = static_cast<uint32_t>(slot_floats) * 4u;
 
-    if (threadIdx.x == 0) {
-        sm100::mbar_init(full, 1);
-        for (int l = 0; l < RW::kLevels; ++l) sm100::mbar_init(c.xbar + l, 1);
-        if (kBwd) sm100::mbar_init(gfull, 1);
+    if (lane == 0) {
+        // every warp fetches its own span: one box per tensor, k and v on one barrier, gy on another;
+        // the warp starts as soon as its own 32 tokens are there
+        constexpr uint32_t kSpanBytes = kSpan * kCs * 4u;
+        sm100::mbar_init(full + warp, 1);
+        if (kBwd) sm100::mbar_init(gfull + warp, 1);
         sm100::mbar_init_fence();
-        sm100::mbar_expect_tx(full, 2 * slot_bytes);
-        sm100::tma_load_3d(slot_k, &map_k, full, strip * kCs, tok0, b);
-        sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
+        sm100::mbar_expect_tx(full + warp, 2 * kSpanBytes);
+        sm100::tma_load_3d(slot_k + warp * kSpan * kCs, &map_k, full + warp, strip * kCs, tok0 + warp * kSpan, b);
+        sm100::tma_load_3d(slot_v + warp * kSpan * kCs, &map_v, full + warp, strip * kCs, tok0 + warp * kSpan, b);
         if (kBwd) {
-            sm100::mbar_expect_tx(gfull, slot_bytes);
-            sm100::tma_load_3d(slot_g, &map_g, gfull, strip * kCs, tok0, b);
+            sm100::mbar_expect_tx(gfull + warp, kSpanBytes);
+            sm100::tma_load_3d(slot_g + warp * kSpan * kCs, &map_g, gfull + warp, strip * kCs, tok0 + warp * kSpan, b);
         }
+    }
+    if (threadIdx.x == 0) {
+        for (int l = 0; l < RW::kLevels; ++l) sm100::mbar_init(c.xbar + l, 1);
+        sm100::mbar_init_fence();
         if (p.cluster > 1) {
             // bytes the other CTAs will send per level: a block from every lower rank (towards later
             // tokens) and from every higher rank (towards earlier ones)
@@ -716,7 +722,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const float2 c2 = *reinterpret_cast<const float2*>(c.consts + kCuw * kCs + 2 * pr);
 
     TL_MARK(1);
-    if (!sm100::mbar_wait(full, 0, kSpinLimit)) atomicOr(p.status, 2u);
+    if (!sm100::mbar_wait(full + warp, 0, kSpinLimit)) atomicOr(p.status, 2u);
     if (p.cluster > 1) cluster_wait();
     TL_MARK(2);
 
@@ -774,7 +780,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     TL_MARK(4);
 
     float2 gw = f2(0.f, 0.f), gu = f2(0.f, 0.f);
-    if (kBwd && !sm100::mbar_wait(gfull, 0, kSpinLimit)) atomicOr(p.status, 2u);
+    if (kBwd && !sm100::mbar_wait(gfull + warp, 0, kSpinLimit)) atomicOr(p.status, 2u);
     if (unsafe) {
         // the whole cluster takes this branch together: the unit is left to the exact kernel, which
         // runs right after this one (nothing of this CTA is in flight any more: its tiles have
@@ -1008,9 +1014,11 @@ biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const int b = unit / p.n_strips, strip = unit - b * p.n_strips;
         if (threadIdx.x == 0) {
             sm100::mbar_expect_tx(full, RW::kSlots * slot_bytes);
-            sm100::tma_load_3d(slot_k, &map_k, full, strip * kCs, tok0, b);
-            sm100::tma_load_3d(slot_v, &map_v, full, strip * kCs, tok0, b);
-            if (kBwd) sm100::tma_load_3d(slot_g, &map_g, full, strip * kCs, tok0, b);
+            for (int sp = 0; sp < nw; ++sp) {            // the load maps describe one span per box
+                sm100::tma_load_3d(slot_k + sp * kSpan * kCs, &map_k, full, strip * kCs, tok0 + sp * kSpan, b);
+                sm100::tma_load_3d(slot_v + sp * kSpan * kCs, &map_v, full, strip * kCs, tok0 + sp * kSpan, b);
+                if (kBwd) sm100::tma_load_3d(slot_g + sp * kSpan * kCs, &map_g, full, strip * kCs, tok0 + sp * kSpan, b);
+            }
         }
         const int ch0 = strip * kCs + 2 * pr;
         const float2 w2 = (ch0 < p.C) ? *reinterpret_cast<const float2*>(p.w + ch0) : f2(0.f, 0.f);
@@ -1192,9 +1200,10 @@ static int launch(int B, int T, int C, const float* w, const float* u, const flo
     p.withhold_rank = g_withhold.load() ? 1 : -1;
     cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
     CUtensorMap mk, mv, mg, m0, m1;
-    bool ok = tensor_map::make_btc_f32(&mk, k, B, T, C, kCs, pl.n_tok) && tensor_map::make_btc_f32(&mv, v, B, T, C, kCs, pl.n_tok) &&
+    // loads: one box per 32-token span; stores: one box per CTA
+    bool ok = tensor_map::make_btc_f32(&mk, k, B, T, C, kCs, kSpan) && tensor_map::make_btc_f32(&mv, v, B, T, C, kCs, kSpan) &&
               tensor_map::make_btc_f32(&m0, o0, B, T, C, kCs, pl.n_tok);
-    ok = ok && tensor_map::make_btc_f32(&mg, kBwd ? gy : k, B, T, C, kCs, pl.n_tok) &&
+    ok = ok && tensor_map::make_btc_f32(&mg, kBwd ? gy : k, B, T, C, kCs, kSpan) &&
          tensor_map::make_btc_f32(&m1, kBwd ? o1 : o0, B, T, C, kCs, pl.n_tok);
     if (!ok) {
         set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
