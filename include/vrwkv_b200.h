@@ -186,13 +186,32 @@ int vrwkv_wkv6_forward_tc_bf16(int B, int T, int C, int H, const uint16_t* r, co
  *       CLS/cuda_v6/wkv6_op.cpp:5,10-12 (kernels CLS/cuda_v6/wkv6_cuda.cu:99-346,355-362)
  * without its T <= 256 limit.  gw is the gradient w.r.t. w_raw (as in the reference, whose
  * kernels multiply by -exp(w_raw)); gu is already summed over batch (the reference returns
- * (B, C) and sums in Python, CLS/vrwkv6.py:69).
+ * (B, C) and sums in Python, CLS/vrwkv6.py:69).  gv may be NULL: the value gradient is then left
+ * out (a third of the work); by the symmetry of the operator it equals the forward applied to
+ * (r, k, v) := (k, r, gy), which a half-precision caller can take from vrwkv_wkv6_forward_tc_*.
  */
 size_t vrwkv_wkv6_backward_workspace_bytes(int B, int T, int C, int H);
 int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
                             const float* w_raw, const float* u, const float* gy, float* gr, float* gk,
                             float* gv, float* gw, float* gu, void* workspace, size_t workspace_bytes,
                             void* stream);
+
+/* The same gradients on the tensor cores (tcgen05, states in tensor memory), for callers whose
+ * activations are half precision anyway: r, k, v, gy enter the matrix products rounded to bfloat16,
+ * sums are fp32; results agree with vrwkv_wkv6_backward_f32 to about 1e-2 of each tensor's maximum.
+ * gv is the forward kernel applied to (k, r, gy); gr and gk come from a second kernel of the same
+ * block structure; gw and gu from their one-sided sums.  vrwkv_wkv6_backward_tc_bf16 reads r, k, v,
+ * gy as bfloat16 bit patterns directly (the reference hands whatever dtype the projections produced
+ * to kernels that read float, CLS/vrwkv6.py:60-70, so a half-precision caller pays widening passes
+ * there).  All gradients are float32; gw is w.r.t. w_raw; gu is summed over batch.  They stand in for
+ * the same reference entry point as vrwkv_wkv6_backward_f32 (CLS/cuda_v6/wkv6_op.cpp:5,10-12). */
+size_t vrwkv_wkv6_backward_tc_workspace_bytes(int B, int T, int C, int H);
+int vrwkv_wkv6_backward_tc_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                               const float* w_raw, const float* u, const float* gy, float* gr, float* gk, float* gv,
+                               float* gw, float* gu, void* workspace, size_t workspace_bytes, void* stream);
+int vrwkv_wkv6_backward_tc_bf16(int B, int T, int C, int H, const uint16_t* r, const uint16_t* k, const uint16_t* v,
+                                const float* w_raw, const float* u, const uint16_t* gy, float* gr, float* gk, float* gv,
+                                float* gw, float* gu, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- Q-Shift + token-mix interpolation (the step in front of the K/V/R projections) ----
  * x is (B, H*W, C), tokens in raster order.  xx = x with channel group g (`group` channels

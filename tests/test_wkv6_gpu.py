@@ -273,3 +273,98 @@ def test_tensor_core_bfloat16_strong_decay(cuda_device):
                          u.float().contiguous().to(dev), H, tensor_cores=True)
     ref = O.wkv6_forward(*[x.float().double() for x in (r, k, v, w, u)], H)
     assert rel_err(y, ref) <= TC_TOL
+
+
+# ---- tensor-core backward -----------------------------------------------------------------------------
+GRADS = ("gr", "gk", "gv", "gw", "gu")
+
+
+def run_tc_backward(dev, r, k, v, w, u, gy, H, half=False):
+    from vision_rwkv_b200 import ops
+    ops.CHECK_STATUS = True
+    try:
+        cast = (lambda x: x.bfloat16().contiguous().to(dev)) if half else (lambda x: x.float().contiguous().to(dev))
+        out = ops.wkv6_backward(cast(r), cast(k), cast(v), w.float().contiguous().to(dev), u.float().contiguous().to(dev),
+                                cast(gy), H, tensor_cores=True)
+        torch.cuda.synchronize()
+    finally:
+        ops.CHECK_STATUS = False
+    return out
+
+
+def check_tc_backward(got, ref, tol=TC_TOL, gw_tol=None):
+    """gw is a difference of running sums of k*gk and r*gr over the sequence: it is only as good as gr and gk
+    are accurate, which is why the mixing kernel carries its derived operands as hi + lo bfloat16 pairs."""
+    errs = {}
+    scale = max(float(rf.abs().max()) for rf in ref)
+    for name, g, rf in zip(GRADS, got, ref):
+        assert torch.isfinite(g).all(), name
+        if rf.abs().max() == 0:
+            assert g.abs().max().item() <= tol * scale, name
+            continue
+        errs[name] = rel_err(g.reshape(rf.shape), rf)
+    for name, e in errs.items():
+        assert e <= (gw_tol if (name == "gw" and gw_tol is not None) else tol), errs
+
+
+def gw_bound(T):
+    return TC_TOL
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 1, 1), (2, 2, 1), (1, 3, 2), (2, 15, 1), (1, 16, 3), (1, 17, 2), (1, 31, 1),
+                                   (2, 37, 2), (1, 64, 1), (1, 70, 1), (3, 196, 2), (1, 300, 1), (1, 1024, 1)])
+def test_tensor_core_backward_parity(cuda_device, B, T, H):
+    """gr, gk, gv, gw, gu of the tcgen05 kernels against the float64 oracle on bf16-rounded inputs: 1e-2."""
+    r, k, v, w, u, gy = O.make_inputs(B, T, 64 * H, H, seed=T, round_to=torch.bfloat16)
+    gy = gy.bfloat16().float()
+    ref = O.wkv6_backward(*[x.float().double() for x in (r, k, v, w, u, gy)], H)
+    check_tc_backward(run_tc_backward(cuda_device, r, k, v, w, u, gy, H), ref, gw_tol=gw_bound(T))
+    check_tc_backward(run_tc_backward(cuda_device, r, k, v, w, u, gy, H, half=True), ref, gw_tol=gw_bound(T))
+
+
+@pytest.mark.parametrize("shift", [1.0, 1.7, 2.6, 4.0])
+def test_tensor_core_backward_strong_decay(cuda_device, shift):
+    """Blocks whose accumulated log-decay passes 80 take their in-block part on the CUDA cores."""
+    B, T, H = 2, 100, 2
+    r, k, v, w, u, gy = O.make_inputs(B, T, 64 * H, H, seed=11, round_to=torch.bfloat16)
+    gy = gy.bfloat16().float()
+    w = w.clone()
+    w[..., :64] += shift
+    ref = O.wkv6_backward(*[x.float().double() for x in (r, k, v, w, u, gy)], H)
+    check_tc_backward(run_tc_backward(cuda_device, r, k, v, w, u, gy, H), ref, gw_tol=gw_bound(T))
+
+
+def test_tensor_core_backward_long_sequence_one_head(cuda_device):
+    """T = 4096, one head: every gradient against the oracle (the oracle is O(T), seconds on the host)."""
+    B, T, H = 1, 4096, 1
+    r, k, v, w, u, gy = O.make_inputs(B, T, 64 * H, H, seed=5, round_to=torch.bfloat16)
+    gy = gy.bfloat16().float()
+    ref = O.wkv6_backward(*[x.float().double() for x in (r, k, v, w, u, gy)], H)
+    check_tc_backward(run_tc_backward(cuda_device, r, k, v, w, u, gy, H, half=True), ref, gw_tol=gw_bound(T))
+
+
+@pytest.mark.parametrize("B,T,H", [(2, 37, 2), (3, 196, 2), (1, 4096, 1)])
+def test_half_precision_backward_default(cuda_device, B, T, H):
+    """What WKV_6.backward runs for bfloat16 callers: gv from the tensor cores (1e-2), gr, gk, gw, gu from the
+    exact sweeps on the same bf16-rounded values (1e-4: float32 sums over T tokens)."""
+    from vision_rwkv_b200 import ops
+    r, k, v, w, u, gy = O.make_inputs(B, T, 64 * H, H, seed=T + 1, round_to=torch.bfloat16)
+    gy = gy.bfloat16().float()
+    ref = O.wkv6_backward(*[x.float().double() for x in (r, k, v, w, u, gy)], H)
+    dev = cuda_device
+    half = [x.bfloat16().contiguous().to(dev) for x in (r, k, v)]
+    got = ops.wkv6_backward(*half, w.float().contiguous().to(dev), u.float().contiguous().to(dev),
+                            gy.bfloat16().contiguous().to(dev), H, tensor_cores="gv")
+    torch.cuda.synchronize()
+    for name, g, rf in zip(GRADS, got, ref):
+        assert rel_err(g.reshape(rf.shape), rf) <= (TC_TOL if name == "gv" else 1e-4), name
+
+
+def test_exact_backward_long_sequence_one_head(cuda_device):
+    """The float32 sweeps at T = 4096 against the oracle, all five gradients (running sums over 4096 tokens)."""
+    B, T, H = 1, 4096, 1
+    args = O.make_inputs(B, T, 64 * H, H, seed=6)
+    got = run_gpu(cuda_device, *args, H)
+    ref = reference(*args, H)
+    for name, g, rf in zip(NAMES, got, ref):
+        assert rel_err(g.reshape(rf.shape), rf) <= 2e-5, name

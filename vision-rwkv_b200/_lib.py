@@ -36,6 +36,9 @@ SIGNATURES = {
     "vrwkv_wkv6_forward_tc_bf16": (_c_int, [_c_int] * 4 + [_ptr] * 7 + [_c_size_t, _ptr]),
     "vrwkv_wkv6_backward_workspace_bytes": (_c_size_t, [_c_int] * 4),
     "vrwkv_wkv6_backward_f32": (_c_int, [_c_int] * 4 + [_ptr] * 12 + [_c_size_t, _ptr]),
+    "vrwkv_wkv6_backward_tc_workspace_bytes": (_c_size_t, [_c_int] * 4),
+    "vrwkv_wkv6_backward_tc_f32": (_c_int, [_c_int] * 4 + [_ptr] * 12 + [_c_size_t, _ptr]),
+    "vrwkv_wkv6_backward_tc_bf16": (_c_int, [_c_int] * 4 + [_ptr] * 12 + [_c_size_t, _ptr]),
     "vrwkv_qshift_mix_forward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 4),
     "vrwkv_qshift_mix_backward_workspace_bytes": (_c_size_t, [_c_int] * 5),
     "vrwkv_qshift_mix_backward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 6 + [_c_size_t, _ptr]),

@@ -234,7 +234,7 @@ int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const fl
                             float* gv, float* gw, float* gu, void* workspace, size_t workspace_bytes,
                             void* stream) {
     if (int st = check_wkv6(B, T, C, H)) return st;
-    if (!r || !k || !v || !w_raw || !u || !gy || !gr || !gk || !gv || !gw || !gu || !workspace)
+    if (!r || !k || !v || !w_raw || !u || !gy || !gr || !gk || !gw || !gu || !workspace)      // gv may be NULL
         return VRWKV_ERR_NULL;
     if (misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(w_raw) || misaligned16(gy) ||
         misaligned4(u) || misaligned4(gr) || misaligned4(gk) || misaligned4(gv) || misaligned4(gw) ||
@@ -243,6 +243,37 @@ int vrwkv_wkv6_backward_f32(int B, int T, int C, int H, const float* r, const fl
     if (workspace_bytes < wkv6::backward_workspace(B, T, H)) return VRWKV_ERR_WORKSPACE;
     return finish(wkv6::backward(B, T, H, r, k, v, w_raw, u, gy, gr, gk, gv, gw, gu, workspace,
                                  static_cast<cudaStream_t>(stream)));
+}
+
+size_t vrwkv_wkv6_backward_tc_workspace_bytes(int B, int T, int C, int H) {
+    if (check_wkv6(B, T, C, H) != VRWKV_OK) return 0;
+    return wkv6tc::backward_workspace(B, T, H);
+}
+
+static int wkv6_backward_tc(int B, int T, int C, int H, const void* r, const void* k, const void* v, const float* w_raw,
+                            const float* u, const void* gy, float* gr, float* gk, float* gv, float* gw, float* gu,
+                            void* workspace, size_t workspace_bytes, void* stream, bool half_in) {
+    if (int st = check_wkv6(B, T, C, H)) return st;
+    if (!r || !k || !v || !w_raw || !u || !gy || !gr || !gk || !gv || !gw || !gu || !workspace) return VRWKV_ERR_NULL;
+    if (misaligned16(r) || misaligned16(k) || misaligned16(v) || misaligned16(w_raw) || misaligned16(gy) || misaligned4(u) ||
+        misaligned16(gr) || misaligned16(gk) || misaligned16(gv) || misaligned4(gw) || misaligned4(gu) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return VRWKV_ERR_ALIGNMENT;
+    if (workspace_bytes < wkv6tc::backward_workspace(B, T, H)) return VRWKV_ERR_WORKSPACE;
+    return finish(wkv6tc::backward(B, T, H, r, k, v, w_raw, u, gy, gr, gk, gv, gw, gu, workspace, half_in,
+                                   static_cast<cudaStream_t>(stream)));
+}
+
+int vrwkv_wkv6_backward_tc_f32(int B, int T, int C, int H, const float* r, const float* k, const float* v,
+                               const float* w_raw, const float* u, const float* gy, float* gr, float* gk, float* gv,
+                               float* gw, float* gu, void* workspace, size_t workspace_bytes, void* stream) {
+    return wkv6_backward_tc(B, T, C, H, r, k, v, w_raw, u, gy, gr, gk, gv, gw, gu, workspace, workspace_bytes, stream, false);
+}
+
+int vrwkv_wkv6_backward_tc_bf16(int B, int T, int C, int H, const uint16_t* r, const uint16_t* k, const uint16_t* v,
+                                const float* w_raw, const float* u, const uint16_t* gy, float* gr, float* gk, float* gv,
+                                float* gw, float* gu, void* workspace, size_t workspace_bytes, void* stream) {
+    return wkv6_backward_tc(B, T, C, H, r, k, v, w_raw, u, gy, gr, gk, gv, gw, gu, workspace, workspace_bytes, stream, true);
 }
 
 }  // extern "C"

@@ -72,4 +72,11 @@ int forward(int B, int T, int H, const float* r, const float* k, const float* v,
 // r, k, v in bfloat16 (read as such by the kernel: no widening pass), w_raw, u, y float32.
 int forward_bf16in(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw,
                    const float* u, float* y, unsigned* status, cudaStream_t stream);
+// Tensor-core backward: gv through the forward kernel with permuted operands, gr and gk through a
+// token-mixing kernel of the same structure, gw and gu from their one-sided sums.  half_in: r, k, v, gy
+// point at bfloat16 (read as such).  Gradients are float32.
+size_t backward_workspace(int B, int T, int H);
+int backward(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw, const float* u,
+             const void* gy, float* gr, float* gk, float* gv, float* gw, float* gu, void* workspace, bool half_in,
+             cudaStream_t stream);
 }  // namespace wkv6tc

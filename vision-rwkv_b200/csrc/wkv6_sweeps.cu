@@ -324,13 +324,14 @@ int backward(int B, int T, int H, const float* r, const float* k, const float* v
     a.out[KIND_GR] = gr; a.out[KIND_GK] = gk; a.out[KIND_GV] = gv;
     for (int i = 0; i < 4; ++i) a.cum[i] = ws + i * E;
     a.gu_part = ws + 4 * E;
-    if (split_directions(3 * B * H)) {
+    const int kinds = gv ? 3 : 2;      // gv == nullptr: the caller gets gv elsewhere (the kinds are gr, gk, gv in this order)
+    if (split_directions(kinds * B * H)) {
         cudaMemsetAsync(gr, 0, E * sizeof(float), stream);
         cudaMemsetAsync(gk, 0, E * sizeof(float), stream);
-        cudaMemsetAsync(gv, 0, E * sizeof(float), stream);
-        wkv6_sweep_kernel<true, true><<<dim3(B * H, 3, 2), N, 2 * sizeof(Batch), stream>>>(a);
+        if (gv) cudaMemsetAsync(gv, 0, E * sizeof(float), stream);
+        wkv6_sweep_kernel<true, true><<<dim3(B * H, kinds, 2), N, 2 * sizeof(Batch), stream>>>(a);
     } else {
-        wkv6_sweep_kernel<true, false><<<dim3(B * H, 3), N, 2 * sizeof(Batch), stream>>>(a);
+        wkv6_sweep_kernel<true, false><<<dim3(B * H, kinds), N, 2 * sizeof(Batch), stream>>>(a);
     }
     const int blocks = static_cast<int>(std::min<size_t>((E + 255) / 256, 148 * 16));
     wkv6_decay_grad_kernel<<<blocks, 256, 0, stream>>>(B, T, C, w_raw, a.cum[0], a.cum[1], a.cum[2], a.cum[3], gw);

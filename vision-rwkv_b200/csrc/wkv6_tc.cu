@@ -126,6 +126,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&p);
 }
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -833,6 +834,506 @@ wkv6_tc_pipelined_kernel(const Args a, const __grid_constant__ CUtensorMap map_r
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
 }
 
+
+// ---- backward building block ----------------------------------------------------------------------
+// With D_i(t, s) = product of the decays of channel i over the tokens strictly between s and t, the
+// gradients of the bidirectional WKV6 are three applications of two token-mixing forms:
+//   gv   = forward(k, r, gy)                            (the forward itself, operands permuted)
+//   gr_t = sum_{s != t} D(t, s) (.) k_s (v_s . gy_t)   + u (.) k_t (v_t . gy_t)
+//   gk_t = sum_{s != t} D(t, s) (.) r_s (gy_s . v_t)   + u (.) r_t (gy_t . v_t)
+// The last two are  G(a, p, q)_t[i] = sum_{s != t} D_i(t, s) a_s[i] (p_s . q_t): the decay sits on the
+// OUTPUT channel, the contraction runs over the value index.  wkv6_tc_mix_kernel evaluates G without
+// its diagonal term, one CTA per (batch, head, direction), the rightward sum (s < t) and the
+// leftward sum (s > t) into separate tensors, because the decay gradient needs them apart:
+//   g log w_m = sum_{s<m} k_s (.) gk>_s - sum_{t<=m} r_t (.) gr>_t + sum_{s>m} k_s (.) gk<_s - sum_{t>=m} r_t (.) gr<_t
+// (">": pairs whose output token is the later one).  Per 16-token block, state Z[i][j] = key x value in
+// tensor memory (lane = key channel), a_t = log-decay accumulated over the block's tokens before t:
+//   B (16 x 16)      = Q (16 x 64) . P^T                      no decay inside: plain bf16 tiles
+//   out'^T (64 x 16) = Z (64 x 64, bf16 copy) . Q^T  +  At^T (64 x 16) . Bm^T     At[s][i] = a_s[i] e^{-a_{s+1}[i]}, Bm = B masked to s < t
+//   out_t[i]         = e^{a_t[i]} out'_t[i]                    scaled in fp32 on the way out
+//   Z (64 x 64)      = e^{A[i]} Z  +  Ah^T (64 x 16) . P      Ah[s][i] = a_s[i] e^{A[i] - a_{s+1}[i]}
+// A block whose accumulated log-decay exceeds 80 in any channel (e^{-a} would overflow) takes its
+// in-block part on the CUDA cores with non-positive exponents instead.
+struct MixArgs {
+    int B, T, H;
+    const void* a;       // the tensor that carries the decay's channel index (k for gr, r for gk)
+    const void* p;       // paired with a at the source token (v for gr, gy for gk)
+    const void* q;       // taken at the output token (gy for gr, v for gk)
+    const float* w;      // raw decay input
+    float* out_right;    // sums over earlier source tokens
+    float* out_left;     // sums over later source tokens
+    float* dots;         // (B, T, H): p_t . q_t, written by the rightward CTAs when not null
+    unsigned* status;
+};
+
+struct __align__(1024) SmemMix {
+    __nv_bfloat16 opS[128 * 64];      // A: rows 0..63 = Z (key x value), rows 64..79 = Q (token x value)
+    // 64-row A operands of M = 128 products: the tensor core also reads "rows 64..127", which with this k-group
+    // stride are the next k-group's rows (or the next array): finite values whose products land in TMEM lanes
+    // 64..127, which nobody reads in these columns
+    __nv_bfloat16 opAt[64 * 16];      // A of the in-block part: At^T, rows = key channel, K = token
+    __nv_bfloat16 opAh[64 * 16];      // A of the update: Ah^T
+    __nv_bfloat16 opQ[16 * 64];       // B of the read-out: rows = token, K = value
+    __nv_bfloat16 opPb[16 * 64];      // B of the scores: rows = token s, K = value
+    __nv_bfloat16 opPt[64 * 16];      // B of the update: rows = value, K = token
+    __nv_bfloat16 opBm[16 * 16];      // B of the in-block part: rows = token t, K = token s
+    // low halves: every operand that is not a bfloat16 input is carried as hi + lo (lo = x - bf16(x)), and a
+    // product of two such operands as hi.hi + hi.lo + lo.hi, which brings the sums to float32 accuracy
+    __nv_bfloat16 opSlo[64 * 64];     // Z - bf16(Z)
+    __nv_bfloat16 opAtlo[64 * 16];
+    __nv_bfloat16 opAhlo[64 * 16];
+    __nv_bfloat16 opBmlo[16 * 16];
+    __nv_bfloat16 tail_pad[64 * 8];   // what the last k-group of the array before it runs into: zeros
+    float raw[4][SC][N];              // a, p, q, w of the block as the copy engine delivers them
+    float otile[SC][N];
+    float acum[SC + 1][N];
+    float scores[SC][SC + 1];         // fp32 copy of B for the strong-decay path
+    float dots[SC];
+    float dtot[N];
+    uint64_t bar_main;
+    uint64_t bar_score;
+    uint64_t bar_load;
+    uint32_t tmem_base;
+};
+
+template <bool kHalfIn>
+__global__ void __launch_bounds__(kThreads, 4)
+wkv6_tc_mix_kernel(const MixArgs a, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_p,
+                   const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_w,
+                   const __grid_constant__ CUtensorMap map_or, const __grid_constant__ CUtensorMap map_ol) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    SmemMix& s = *reinterpret_cast<SmemMix*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int unit = blockIdx.x >> 1;
+    const bool rightward = (blockIdx.x & 1) == 0;
+    const int b = unit / a.H, h = unit % a.H;
+    const int T = a.T, C = a.H * N;
+    const size_t base = static_cast<size_t>(b) * T * C + static_cast<size_t>(h) * N;
+    const int n_blocks = (T + SC - 1) / SC;
+    float* out = rightward ? a.out_right : a.out_left;
+    const CUtensorMap* map_o = rightward ? &map_or : &map_ol;
+
+    // first token (memory order) of the 16-row tile that holds block `blk`; negative for a ragged last leftward block
+    auto tile_start = [&](int blk) { return rightward ? blk * SC : T - SC * (blk + 1); };
+    auto issue_loads = [&](int blk) {
+        const int y0 = tile_start(blk);
+        constexpr uint32_t kIn = SC * N * (kHalfIn ? 2 : 4);
+        sm100::mbar_expect_tx(&s.bar_load, 3 * kIn + SC * N * 4);
+        sm100::tma_load_3d(&s.raw[0][0][0], &map_a, &s.bar_load, h * N, y0, b);
+        sm100::tma_load_3d(&s.raw[1][0][0], &map_p, &s.bar_load, h * N, y0, b);
+        sm100::tma_load_3d(&s.raw[2][0][0], &map_q, &s.bar_load, h * N, y0, b);
+        sm100::tma_load_3d(&s.raw[3][0][0], &map_w, &s.bar_load, h * N, y0, b);
+    };
+
+    if (tid == kIssuer) {
+        sm100::mbar_init(&s.bar_main, 1);
+        sm100::mbar_init(&s.bar_score, 1);
+        sm100::mbar_init(&s.bar_load, 1);
+        sm100::mbar_init_fence();
+        issue_loads(0);
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)),
+                     "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    // rows of the A operands that carry no data are still read by the tensor core: keep them finite
+    for (int i = tid; i < 128 * 64; i += kThreads) s.opS[i] = __float2bfloat16(0.f);
+    for (int i = tid; i < 64 * 64; i += kThreads) s.opSlo[i] = __float2bfloat16(0.f);
+    for (int i = tid; i < 64 * 16; i += kThreads) {
+        s.opAt[i] = __float2bfloat16(0.f); s.opAh[i] = __float2bfloat16(0.f);
+        s.opAtlo[i] = __float2bfloat16(0.f); s.opAhlo[i] = __float2bfloat16(0.f);
+    }
+    for (int i = tid; i < 16 * 16; i += kThreads) { s.opBm[i] = __float2bfloat16(0.f); s.opBmlo[i] = __float2bfloat16(0.f); }
+    for (int i = tid; i < 64 * 8; i += kThreads) s.tail_pad[i] = __float2bfloat16(0.f);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s.tmem_base;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+    uint32_t phase_main = 0, phase_score = 0, phase_load = 0;
+    bool failed = false;
+    auto wait_on = [&](uint64_t* bar, uint32_t parity) {
+        if (!failed && !sm100::mbar_wait(bar, parity, kWaitLimit)) { failed = true; atomicExch(a.status, 1u); }
+    };
+
+    for (int blk = 0; blk < n_blocks; ++blk) {
+        auto row_of = [&](int t) { return rightward ? t : SC - 1 - t; };   // block order -> tile row
+
+        wait_on(&s.bar_load, phase_load);
+        phase_load ^= 1u;
+        if (tid == 0) sm100::tma_store_wait_read();        // the previous output tile has left shared memory
+
+        // ---- phase A: log-decays and their running sums; thread = (key channel, half of the block) ----
+        {
+            const int c = tid & 63, half = tid >> 6;
+            float wv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wv[j] = s.raw[3][row_of(half * 8 + j)][c];
+            float run = 0.f;
+            if (half == 0) s.acum[0][c] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = half * 8 + j;
+                run += (blk * SC + t < T) ? -__expf(wv[j]) : 0.f;
+                s.acum[t + 1][c] = run;
+            }
+        }
+        __syncthreads();
+        // a_t[c] = acum[t][c] (+ acum[8][c] for t > 8);  A[c] = a_16[c]
+        // ---- phase B, job 1: thread = (token t, 8 value channels): Q (twice), P as the scores' B operand, p . q ----
+        {
+            const int t = tid >> 3, c0 = (tid & 7) * 8, row = row_of(t);
+            float qv[8], pv[8];
+            *reinterpret_cast<float4*>(&qv[0]) = raw_ld4<kHalfIn>(&s.raw[2][0][0], row, c0);
+            *reinterpret_cast<float4*>(&qv[4]) = raw_ld4<kHalfIn>(&s.raw[2][0][0], row, c0 + 4);
+            *reinterpret_cast<float4*>(&pv[0]) = raw_ld4<kHalfIn>(&s.raw[1][0][0], row, c0);
+            *reinterpret_cast<float4*>(&pv[4]) = raw_ld4<kHalfIn>(&s.raw[1][0][0], row, c0 + 4);
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot += qv[i] * pv[i];
+            const uint4 q_packed = make_uint4(pack_bf16(qv[0], qv[1]), pack_bf16(qv[2], qv[3]), pack_bf16(qv[4], qv[5]),
+                                              pack_bf16(qv[6], qv[7]));
+            *reinterpret_cast<uint4*>(&s.opQ[op_index(16, t, c0)]) = q_packed;
+            *reinterpret_cast<uint4*>(&s.opS[op_index(128, 64 + t, c0)]) = q_packed;
+            *reinterpret_cast<uint4*>(&s.opPb[op_index(16, t, c0)]) =
+                make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if ((tid & 7) == 0) s.dots[t] = dot;
+        }
+        // ---- phase B, job 2: thread = (channel, half of the block): At, Ah (key channel), P^T (value channel), e^A ----
+        bool big;
+        {
+            const int c = tid & 63, half = tid >> 6;
+            const float a8 = s.acum[8][c];
+            const float A = s.acum[16][c] + a8;
+            big = A < -kMaxLogDecay;
+            float av[8], pv[8], a1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = half * 8 + j, row = row_of(t);
+                a1[j] = s.acum[t + 1][c] + (t + 1 > 8 ? a8 : 0.f);      // a_{t+1}
+                av[j] = raw_ld1<kHalfIn>(&s.raw[0][0][0], row, c);
+                pv[j] = raw_ld1<kHalfIn>(&s.raw[1][0][0], row, c);
+            }
+            if (half == 0) s.dtot[c] = __expf(A);
+            float at[8], ah[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                at[j] = big ? 0.f : av[j] * __expf(-a1[j]);
+                ah[j] = av[j] * __expf(A - a1[j]);
+            }
+            *reinterpret_cast<uint4*>(&s.opAt[op_index(64, c, half * 8)]) =
+                make_uint4(pack_bf16(at[0], at[1]), pack_bf16(at[2], at[3]), pack_bf16(at[4], at[5]), pack_bf16(at[6], at[7]));
+            *reinterpret_cast<uint4*>(&s.opAh[op_index(64, c, half * 8)]) =
+                make_uint4(pack_bf16(ah[0], ah[1]), pack_bf16(ah[2], ah[3]), pack_bf16(ah[4], ah[5]), pack_bf16(ah[6], ah[7]));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                at[j] -= bf16_round(at[j]);
+                ah[j] -= bf16_round(ah[j]);
+            }
+            *reinterpret_cast<uint4*>(&s.opAtlo[op_index(64, c, half * 8)]) =
+                make_uint4(pack_bf16(at[0], at[1]), pack_bf16(at[2], at[3]), pack_bf16(at[4], at[5]), pack_bf16(at[6], at[7]));
+            *reinterpret_cast<uint4*>(&s.opAhlo[op_index(64, c, half * 8)]) =
+                make_uint4(pack_bf16(ah[0], ah[1]), pack_bf16(ah[2], ah[3]), pack_bf16(ah[4], ah[5]), pack_bf16(ah[6], ah[7]));
+            *reinterpret_cast<uint4*>(&s.opPt[op_index(64, c, half * 8)]) =
+                make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        const bool pairwise = __syncthreads_or(big) != 0;      // CTA-uniform
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        // ---- scores on the tensor core: rows 64..79 of (opS . opPb^T), lane 64 + t <- B[t][.] ----
+        if (tid == kIssuer) {
+#pragma unroll
+            for (int ks = 0; ks < N / 16; ++ks) {
+                const uint64_t da = make_desc(smem_u32(s.opS) + ks * 2 * (128 * 16), 128 * 16, 128);
+                const uint64_t db = make_desc(smem_u32(s.opPb) + ks * 2 * (16 * 16), 16 * 16, 128);
+                umma_bf16(tmem + 80, da, db, instr_desc(128, 16), ks > 0 ? 1u : 0u);
+            }
+            tc_commit(&s.bar_score);
+        }
+        // ---- state round trip (warps 0, 1; lane = key channel): bf16 copy for the read-out, decay in place ----
+        if (tid < N) {
+            uint32_t x[4][16];
+            if (blk > 0) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) tmem_ld16_issue(lane_addr + g * 16, x[g]);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) x[g][i] = 0u;
+            }
+            const float decay = s.dtot[tid];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                float f[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(x[g][i]);
+                *reinterpret_cast<uint4*>(&s.opS[op_index(128, tid, g * 16)]) =
+                    make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                *reinterpret_cast<uint4*>(&s.opS[op_index(128, tid, g * 16 + 8)]) =
+                    make_uint4(pack_bf16(f[8], f[9]), pack_bf16(f[10], f[11]), pack_bf16(f[12], f[13]), pack_bf16(f[14], f[15]));
+                float lo[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) lo[i] = f[i] - bf16_round(f[i]);
+                *reinterpret_cast<uint4*>(&s.opSlo[op_index(64, tid, g * 16)]) =
+                    make_uint4(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]), pack_bf16(lo[4], lo[5]), pack_bf16(lo[6], lo[7]));
+                *reinterpret_cast<uint4*>(&s.opSlo[op_index(64, tid, g * 16 + 8)]) =
+                    make_uint4(pack_bf16(lo[8], lo[9]), pack_bf16(lo[10], lo[11]), pack_bf16(lo[12], lo[13]), pack_bf16(lo[14], lo[15]));
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x[g][i] = __float_as_uint(f[i] * decay);
+                tmem_st16(lane_addr + g * 16, x[g]);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+        if (warp == 2) {
+            // ---- warp 2 owns TMEM lanes 64..79: row t of the scores, masked to s < t ----
+            wait_on(&s.bar_score, phase_score);
+            phase_score ^= 1u;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t x[16];
+            tmem_ld16_issue(lane_addr + 80, x);
+            tmem_ld_wait();
+            if (lane < 16) {
+                float pr[16];
+#pragma unroll
+                for (int q = 0; q < SC; ++q) {
+                    pr[q] = q < lane ? __uint_as_float(x[q]) : 0.f;
+                    s.scores[lane][q] = pr[q];
+                }
+                *reinterpret_cast<uint4*>(&s.opBm[op_index(16, lane, 0)]) =
+                    make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
+                *reinterpret_cast<uint4*>(&s.opBm[op_index(16, lane, 8)]) =
+                    make_uint4(pack_bf16(pr[8], pr[9]), pack_bf16(pr[10], pr[11]), pack_bf16(pr[12], pr[13]), pack_bf16(pr[14], pr[15]));
+#pragma unroll
+                for (int q = 0; q < SC; ++q) pr[q] -= bf16_round(pr[q]);
+                *reinterpret_cast<uint4*>(&s.opBmlo[op_index(16, lane, 0)]) =
+                    make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
+                *reinterpret_cast<uint4*>(&s.opBmlo[op_index(16, lane, 8)]) =
+                    make_uint4(pack_bf16(pr[8], pr[9]), pack_bf16(pr[10], pr[11]), pack_bf16(pr[12], pr[13]), pack_bf16(pr[14], pr[15]));
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        // ---- tensor core: read-out against the old state, in-block part, state update ----
+        if (tid == kIssuer) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int ks = 0; ks < N / 16; ++ks) {
+                const uint64_t da = make_desc(smem_u32(s.opS) + ks * 2 * (128 * 16), 128 * 16, 128);
+                const uint64_t db = make_desc(smem_u32(s.opQ) + ks * 2 * (16 * 16), 16 * 16, 128);
+                umma_bf16(tmem + 64, da, db, instr_desc(128, 16), ks > 0 ? 1u : 0u);
+            }
+#pragma unroll
+            for (int ks = 0; ks < N / 16; ++ks) {                 // the state's low half against the same Q
+                const uint64_t da = make_desc(smem_u32(s.opSlo) + ks * 2 * (64 * 16), 64 * 16, 128);
+                const uint64_t db = make_desc(smem_u32(s.opQ) + ks * 2 * (16 * 16), 16 * 16, 128);
+                umma_bf16(tmem + 64, da, db, instr_desc(128, 16), 1u);
+            }
+            if (!pairwise) {
+                const uint64_t at_hi = make_desc(smem_u32(s.opAt), 64 * 16, 128), at_lo = make_desc(smem_u32(s.opAtlo), 64 * 16, 128);
+                const uint64_t bm_hi = make_desc(smem_u32(s.opBm), 16 * 16, 128), bm_lo = make_desc(smem_u32(s.opBmlo), 16 * 16, 128);
+                umma_bf16(tmem + 64, at_hi, bm_hi, instr_desc(128, 16), 1u);
+                umma_bf16(tmem + 64, at_hi, bm_lo, instr_desc(128, 16), 1u);
+                umma_bf16(tmem + 64, at_lo, bm_hi, instr_desc(128, 16), 1u);
+            }
+            umma_bf16(tmem, make_desc(smem_u32(s.opAh), 64 * 16, 128), make_desc(smem_u32(s.opPt), 64 * 16, 128),
+                      instr_desc(128, 64), 1u);
+            umma_bf16(tmem, make_desc(smem_u32(s.opAhlo), 64 * 16, 128), make_desc(smem_u32(s.opPt), 64 * 16, 128),
+                      instr_desc(128, 64), 1u);
+            tc_commit(&s.bar_main);
+        }
+        // ---- strong decay: in-block part per channel in fp32, every exponent <= 0 (added on the way out) ----
+        float extra[SC];
+#pragma unroll
+        for (int t = 0; t < SC; ++t) extra[t] = 0.f;
+        if (pairwise && tid < N) {
+            const float a8 = s.acum[8][tid];
+            for (int t = 1; t < SC; ++t) {
+                const float a_t = s.acum[t][tid] + (t > 8 ? a8 : 0.f);
+                float acc = 0.f;
+                for (int q = 0; q < t; ++q) {
+                    const float a_q1 = s.acum[q + 1][tid] + (q + 1 > 8 ? a8 : 0.f);
+                    acc += s.scores[t][q] * raw_ld1<kHalfIn>(&s.raw[0][0][0], row_of(q), tid) * __expf(a_t - a_q1);
+                }
+                extra[t] = acc;
+            }
+        }
+        float scale[SC];
+        if (tid < N) {
+            const float a8 = s.acum[8][tid];
+#pragma unroll
+            for (int t = 0; t < SC; ++t) scale[t] = __expf(s.acum[t][tid] + (t > 8 ? a8 : 0.f));
+        }
+        const int y0 = tile_start(blk);
+        if (tid < SC && rightward && a.dots != nullptr && blk * SC + tid < T)
+            a.dots[(static_cast<size_t>(b) * T + blk * SC + tid) * a.H + h] = s.dots[tid];
+        // ---- everyone waits for the tensor core (the operands are rewritten next); warps 0, 1 send this block's output ----
+        wait_on(&s.bar_main, phase_main);
+        phase_main ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // the strong-decay path reads the staging tiles until just now: everyone must be past them before they are refilled
+        if (pairwise) __syncthreads();
+        if (tid == kIssuer && blk + 1 < n_blocks) issue_loads(blk + 1);
+        if (tid < N) {
+            uint32_t ot[16];
+            tmem_ld16_issue(lane_addr + 64, ot);
+            tmem_ld_wait();
+            if (y0 >= 0) {
+#pragma unroll
+                for (int t = 0; t < SC; ++t)
+                    s.otile[row_of(t)][tid] = pairwise ? scale[t] * __uint_as_float(ot[t]) + extra[t] : scale[t] * __uint_as_float(ot[t]);
+                sm100::fence_proxy_async_smem();
+                sm100::named_bar_sync(1, N);
+                if (tid == 0) {
+                    sm100::tma_store_3d(map_o, &s.otile[0][0], h * N, y0, b);        // rows past T are clipped
+                    sm100::tma_store_commit();
+                }
+            } else {
+                // ragged last block of the leftward walk: its tile would start before token 0
+#pragma unroll
+                for (int t = 0; t < SC; ++t) {
+                    const int t_seq = blk * SC + t;
+                    if (t_seq < T)
+                        out[base + static_cast<size_t>(T - 1 - t_seq) * C + tid] =
+                            pairwise ? scale[t] * __uint_as_float(ot[t]) + extra[t] : scale[t] * __uint_as_float(ot[t]);
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+    }
+    if (tid == 0) sm100::tma_store_wait_all();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+}
+
+
+// ---- backward: combining the four one-sided sums --------------------------------------------------
+// gr> = G(k, v, gy) over earlier tokens, gr< over later ones; gk< = G(r, gy, v) over earlier tokens,
+// gk> over later ones (">" = pairs whose output token is the later one); dots_t = v_t . gy_t per head.
+//   gr = gr> + gr< + u k dots        gk = gk> + gk< + u r dots        gu = sum_{b,t} r k dots
+//   x>_t = k_t gk>_t - r_t gr>_t     g log w_m = (sum_{t<m} x>_t) - r_m gr>_m + (sum_{t>m} x<_t) - r_m gr<_m
+//   gw_raw = g log w * (-exp(w_raw))
+// The sums along T are taken per segment of kSeg tokens: totals (first kernel), their exclusive
+// prefix / suffix over the segments (second), the walk inside each segment (third).
+constexpr int kSeg = 128;
+
+template <bool kHalfIn>
+__device__ __forceinline__ float in_ld(const void* base, size_t idx) {
+    if (kHalfIn) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+    return static_cast<const float*>(base)[idx];
+}
+
+struct FinArgs {
+    int B, T, H, n_seg;
+    const void* r;
+    const void* k;
+    const float* w;
+    const float* u;
+    const float* gr_right;   // gr>
+    const float* gr_left;    // gr<
+    const float* gk_right;   // G(r, gy, v) over earlier tokens = gk<
+    const float* gk_left;    // = gk>
+    const float* dots;       // (B, T, H)
+    float* gr;
+    float* gk;
+    float* gw;
+    float* gu;               // (H, 64)
+    float* tot;              // [3][B][n_seg][C]: x> totals, x< totals, gu parts
+};
+
+// grid (n_seg, H, B), 64 threads: thread = channel of the head
+template <bool kHalfIn>
+__global__ void __launch_bounds__(N) wkv6_bwd_combine_kernel(const FinArgs a) {
+    const int seg = blockIdx.x, h = blockIdx.y, b = blockIdx.z, c = h * N + threadIdx.x;
+    const int C = a.H * N;
+    const int t0 = seg * kSeg, t1 = min(a.T, t0 + kSeg);
+    const float u = a.u[c];
+    float sx_r = 0.f, sx_l = 0.f, sgu = 0.f;
+    for (int t = t0; t < t1; ++t) {
+        const size_t i = (static_cast<size_t>(b) * a.T + t) * C + c;
+        const float r = in_ld<kHalfIn>(a.r, i), k = in_ld<kHalfIn>(a.k, i);
+        const float grr = a.gr_right[i], grl = a.gr_left[i], gkl = a.gk_right[i], gkr = a.gk_left[i];
+        const float d = a.dots[(static_cast<size_t>(b) * a.T + t) * a.H + h];
+        a.gr[i] = grr + grl + u * k * d;
+        a.gk[i] = gkr + gkl + u * r * d;
+        sx_r += k * gkr - r * grr;
+        sx_l += k * gkl - r * grl;
+        sgu += r * k * d;
+    }
+    const size_t j = (static_cast<size_t>(b) * a.n_seg + seg) * C + c;
+    const size_t plane = static_cast<size_t>(a.B) * a.n_seg * C;
+    a.tot[j] = sx_r;
+    a.tot[plane + j] = sx_l;
+    a.tot[2 * plane + j] = sgu;
+}
+
+// grid (ceil(C / 128), B + 1): rows b < B turn the totals of batch entry b into exclusive prefix (x>) /
+// suffix (x<) sums over its segments; the last row sums the gu parts over batch and segments, fixed order
+__global__ void __launch_bounds__(128) wkv6_bwd_carry_kernel(const FinArgs a) {
+    const int C = a.H * N;
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c >= C) return;
+    const size_t plane = static_cast<size_t>(a.B) * a.n_seg * C;
+    if (static_cast<int>(blockIdx.y) < a.B) {
+        const int b = blockIdx.y;
+        float run = 0.f;
+        for (int s = 0; s < a.n_seg; ++s) {
+            float* q = a.tot + (static_cast<size_t>(b) * a.n_seg + s) * C + c;
+            const float x = *q;
+            *q = run;
+            run += x;
+        }
+        run = 0.f;
+        for (int s = a.n_seg - 1; s >= 0; --s) {
+            float* q = a.tot + plane + (static_cast<size_t>(b) * a.n_seg + s) * C + c;
+            const float x = *q;
+            *q = run;
+            run += x;
+        }
+    } else {
+        float acc = 0.f;
+        for (int i = 0; i < a.B * a.n_seg; ++i) acc += a.tot[2 * plane + static_cast<size_t>(i) * C + c];
+        a.gu[c] = acc;
+    }
+}
+
+// grid (n_seg, H, B), 64 threads: the walk inside a segment, rightward part parked in shared memory
+template <bool kHalfIn>
+__global__ void __launch_bounds__(N) wkv6_bwd_decay_kernel(const FinArgs a) {
+    __shared__ float part[kSeg][N];
+    const int seg = blockIdx.x, h = blockIdx.y, b = blockIdx.z, lane = threadIdx.x, c = h * N + lane;
+    const int C = a.H * N;
+    const int t0 = seg * kSeg, t1 = min(a.T, t0 + kSeg);
+    const size_t plane = static_cast<size_t>(a.B) * a.n_seg * C;
+    const size_t j = (static_cast<size_t>(b) * a.n_seg + seg) * C + c;
+    float run = a.tot[j];
+    for (int t = t0; t < t1; ++t) {
+        const size_t i = (static_cast<size_t>(b) * a.T + t) * C + c;
+        const float r = in_ld<kHalfIn>(a.r, i), k = in_ld<kHalfIn>(a.k, i);
+        const float p = r * a.gr_right[i];
+        part[t - t0][lane] = run - p;
+        run += k * a.gk_left[i] - p;
+    }
+    run = a.tot[plane + j];
+    for (int t = t1 - 1; t >= t0; --t) {
+        const size_t i = (static_cast<size_t>(b) * a.T + t) * C + c;
+        const float r = in_ld<kHalfIn>(a.r, i), k = in_ld<kHalfIn>(a.k, i);
+        const float p = r * a.gr_left[i];
+        a.gw[i] = (part[t - t0][lane] + run - p) * -__expf(a.w[i]);
+        run += k * a.gk_right[i] - p;
+    }
+}
+
 // cudaFuncSetAttribute applies to the current device only: one flag per device, under a lock
 static bool configure_once() {
     static std::mutex lock;
@@ -847,7 +1348,11 @@ static bool configure_once() {
             cudaFuncSetAttribute(wkv6_tc_pipelined_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(sizeof(SmemP))) != cudaSuccess ||
             cudaFuncSetAttribute(wkv6_tc_pipelined_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(sizeof(SmemP))) != cudaSuccess)
+                                 static_cast<int>(sizeof(SmemP))) != cudaSuccess ||
+            cudaFuncSetAttribute(wkv6_tc_mix_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(SmemMix))) != cudaSuccess ||
+            cudaFuncSetAttribute(wkv6_tc_mix_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(SmemMix))) != cudaSuccess)
             return false;
         configured = true;
     }
@@ -889,6 +1394,70 @@ int forward(int B, int T, int H, const float* r, const float* k, const float* v,
 int forward_bf16in(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw, const float* u,
                    float* y, unsigned* status, cudaStream_t stream) {
     return launch(B, T, H, r, k, v, w_raw, u, y, status, true, true, stream);
+}
+
+// G(a, p, q) without its diagonal, the two one-sided sums into out_right / out_left (see wkv6_tc_mix_kernel)
+static int launch_mix(int B, int T, int H, const void* a_, const void* p_, const void* q_, const float* w_raw, float* out_right,
+                      float* out_left, float* dots, unsigned* status, bool half_in, cudaStream_t stream) {
+    const int C = H * N;
+    CUtensorMap ma, mp, mq, mw, mor, mol;
+    if (!(tensor_map::make_btc(&ma, a_, B, T, C, N, SC, half_in) && tensor_map::make_btc(&mp, p_, B, T, C, N, SC, half_in) &&
+          tensor_map::make_btc(&mq, q_, B, T, C, N, SC, half_in) && tensor_map::make_btc_f32(&mw, w_raw, B, T, C, N, SC) &&
+          tensor_map::make_btc_f32(&mor, out_right, B, T, C, N, SC) && tensor_map::make_btc_f32(&mol, out_left, B, T, C, N, SC))) {
+        set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
+        return -1;
+    }
+    MixArgs m{B, T, H, a_, p_, q_, w_raw, out_right, out_left, dots, status};
+    if (half_in) wkv6_tc_mix_kernel<true><<<2 * B * H, kThreads, sizeof(SmemMix), stream>>>(m, ma, mp, mq, mw, mor, mol);
+    else wkv6_tc_mix_kernel<false><<<2 * B * H, kThreads, sizeof(SmemMix), stream>>>(m, ma, mp, mq, mw, mor, mol);
+    return 1;
+}
+
+size_t backward_workspace(int B, int T, int H) {
+    const size_t C = static_cast<size_t>(H) * N, E = static_cast<size_t>(B) * T * C;
+    const size_t n_seg = (static_cast<size_t>(T) + kSeg - 1) / kSeg;
+    return 256 + (4 * E + static_cast<size_t>(B) * T * H + 3 * static_cast<size_t>(B) * n_seg * C) * sizeof(float);
+}
+
+// gv through the forward kernel with permuted operands, gr and gk through the mixing kernel, the
+// decay and bonus gradients from their one-sided sums.  half_in: r, k, v, gy point at bfloat16.
+int backward(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw, const float* u,
+             const void* gy, float* gr, float* gk, float* gv, float* gw, float* gu, void* workspace, bool half_in,
+             cudaStream_t stream) {
+    if (!configure_once()) return -1;
+    cudaFree(nullptr);
+    const size_t C = static_cast<size_t>(H) * N, E = static_cast<size_t>(B) * T * C;
+    unsigned* status = static_cast<unsigned*>(workspace);
+    float* ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
+    float* gr_right = ws;
+    float* gr_left = ws + E;
+    float* gk_right = ws + 2 * E;
+    float* gk_left = ws + 3 * E;
+    float* dots = ws + 4 * E;
+    float* tot = dots + static_cast<size_t>(B) * T * H;
+    int launched = 0;
+    // gv_s = sum_t A(t, s) gy_t with A symmetric under r <-> k: the forward with (r, k, v) := (k, r, gy)
+    int n = launch(B, T, H, k, r, gy, w_raw, u, gv, status, half_in, true, stream);
+    if (n < 0) return -1;
+    launched += n;
+    n = launch_mix(B, T, H, k, v, gy, w_raw, gr_right, gr_left, dots, status, half_in, stream);
+    if (n < 0) return -1;
+    launched += n;
+    n = launch_mix(B, T, H, r, gy, v, w_raw, gk_right, gk_left, nullptr, status, half_in, stream);
+    if (n < 0) return -1;
+    launched += n;
+    FinArgs f{};
+    f.B = B; f.T = T; f.H = H; f.n_seg = (T + kSeg - 1) / kSeg;
+    f.r = r; f.k = k; f.w = w_raw; f.u = u;
+    f.gr_right = gr_right; f.gr_left = gr_left; f.gk_right = gk_right; f.gk_left = gk_left; f.dots = dots;
+    f.gr = gr; f.gk = gk; f.gw = gw; f.gu = gu; f.tot = tot;
+    const dim3 grid(f.n_seg, H, B);
+    if (half_in) wkv6_bwd_combine_kernel<true><<<grid, N, 0, stream>>>(f);
+    else wkv6_bwd_combine_kernel<false><<<grid, N, 0, stream>>>(f);
+    wkv6_bwd_carry_kernel<<<dim3((static_cast<unsigned>(C) + 127) / 128, B + 1), 128, 0, stream>>>(f);
+    if (half_in) wkv6_bwd_decay_kernel<true><<<grid, N, 0, stream>>>(f);
+    else wkv6_bwd_decay_kernel<false><<<grid, N, 0, stream>>>(f);
+    return launched + 3;
 }
 
 }  // namespace wkv6tc

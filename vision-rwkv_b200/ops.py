@@ -247,12 +247,25 @@ def wkv6_forward(r, k, v, w, u, H, tensor_cores=False):
     return y
 
 
-def wkv6_backward(r, k, v, w, u, gy, H):
-    """(gr, gk, gv, gw, gu); gw w.r.t. the raw decay input, gu of shape (H, 64)."""
+def wkv6_backward(r, k, v, w, u, gy, H, tensor_cores=False, _skip_gv=False):
+    """(gr, gk, gv, gw, gu), float32; gw w.r.t. the raw decay input, gu of shape (H, 64).
+    tensor_cores=True runs everything on the tcgen05 kernels: gv with bf16 operand rounding (about 4e-3 of
+    its maximum); gr, gk, and gw (a difference of long running sums of those) from a kernel that carries
+    its derived operands as hi + lo bfloat16 pairs, accurate to about 1e-4 when r, k, v, gy are bfloat16
+    values.  tensor_cores="gv" takes only gv from the tensor cores and the rest from the exact float32
+    sweeps.  Both accept r, k, v, gy in bfloat16 (w, u float32) and read them without a widening pass."""
+    if tensor_cores == "gv":
+        # gv = forward(k, r, gy) on the tensor cores (bfloat16 read as it is); gr, gk, gw, gu from the exact sweeps
+        gv = wkv6_forward(k, r, gy, w, u, H, tensor_cores=True)
+        gr, gk, _, gw, gu = wkv6_backward(r.float(), k.float(), v.float(), w, u, gy.float(), H, _skip_gv=True)
+        return gr, gk, gv, gw, gu
+    if tensor_cores:
+        return _wkv6_backward_tc(r, k, v, w, u, gy, H)
     dev = _check_inputs((("r", r), ("k", k), ("v", v), ("w", w), ("u", u), ("gy", gy)))
     B, T, C = _wkv6_shapes(r, k, v, w, u, H, gy)
     lib = _lib.load()
-    gr, gk, gv, gw = (torch.empty((B, T, C), device=dev, dtype=torch.float32) for _ in range(4))
+    gr, gk, gw = (torch.empty((B, T, C), device=dev, dtype=torch.float32) for _ in range(3))
+    gv = None if _skip_gv else torch.empty((B, T, C), device=dev, dtype=torch.float32)
     gu = torch.empty((H, C // H), device=dev, dtype=torch.float32)
     if gr.numel() == 0:
         return gr, gk, gv, gw, gu.zero_()
@@ -260,10 +273,31 @@ def wkv6_backward(r, k, v, w, u, gy, H):
         ws = _workspace(lib.vrwkv_wkv6_backward_workspace_bytes(B, T, C, H), dev)
         st = lib.vrwkv_wkv6_backward_f32(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(),
                                          w.data_ptr(), u.data_ptr(), gy.data_ptr(), gr.data_ptr(),
-                                         gk.data_ptr(), gv.data_ptr(), gw.data_ptr(), gu.data_ptr(),
+                                         gk.data_ptr(), gv.data_ptr() if gv is not None else None, gw.data_ptr(), gu.data_ptr(),
                                          ws.data_ptr(), ws.numel(),
                                          torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_wkv6_backward_f32")
+    return gr, gk, gv, gw, gu
+
+
+def _wkv6_backward_tc(r, k, v, w, u, gy, H):
+    half_in = all(_is_bf16(t) for t in (r, k, v, gy))
+    dev = _check_inputs((("w", w), ("u", u)))
+    _check_inputs((("r", r), ("k", k), ("v", v), ("gy", gy)), torch.bfloat16 if half_in else torch.float32, dev)
+    B, T, C = _wkv6_shapes(r, k, v, w, u, H, gy)
+    lib = _lib.load()
+    gr, gk, gv, gw = (torch.empty((B, T, C), device=dev, dtype=torch.float32) for _ in range(4))
+    gu = torch.empty((H, C // H), device=dev, dtype=torch.float32)
+    if gr.numel() == 0:
+        return gr, gk, gv, gw, gu.zero_()
+    name = "vrwkv_wkv6_backward_tc_bf16" if half_in else "vrwkv_wkv6_backward_tc_f32"
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_wkv6_backward_tc_workspace_bytes(B, T, C, H), dev)
+        st = getattr(lib, name)(B, T, C, H, r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), u.data_ptr(),
+                                gy.data_ptr(), gr.data_ptr(), gk.data_ptr(), gv.data_ptr(), gw.data_ptr(), gu.data_ptr(),
+                                ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+        _lib.check(st, name)
+        _check_status(lib, ws, name)
     return gr, gk, gv, gw, gu
 
 

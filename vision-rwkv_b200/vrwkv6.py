@@ -27,6 +27,10 @@ HEAD_SIZE = 64
 FORWARD_PATH = os.environ.get("VRWKV6_FORWARD_PATH", "auto")
 
 
+BACKWARD_TC = "full"    # half-precision callers: "full" = every gradient from the tcgen05 kernels (bfloat16 read as it is;
+                        # measured faster than widening + exact sweeps); "gv" = only the value gradient there, rest exact
+
+
 def _use_tensor_cores(r, k, v):
     if FORWARD_PATH == "tensor_cores":
         return True
@@ -66,8 +70,18 @@ class WKV_6(torch.autograd.Function):
         with torch.no_grad():
             assert gy.is_contiguous()
             r, k, v, w, u = ctx.saved_tensors
-            gr, gk, gv, gw, gu = ops.wkv6_backward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u),
-                                                   _f32(gy), ctx.H)
+            if _use_tensor_cores(r, k, v):
+                # half-precision callers: the tcgen05 kernels, bfloat16 read as it is (BACKWARD_TC = "gv" keeps the
+                # decay-carrying gradients on the exact sweeps)
+                if all(x.dtype == torch.bfloat16 for x in (r, k, v)):
+                    gr, gk, gv, gw, gu = ops.wkv6_backward(r, k, v, _f32(w), _f32(u), gy.bfloat16().contiguous(), ctx.H,
+                                                           tensor_cores=True if BACKWARD_TC == "full" else "gv")
+                else:
+                    gr, gk, gv, gw, gu = ops.wkv6_backward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u), _f32(gy), ctx.H,
+                                                           tensor_cores=True if BACKWARD_TC == "full" else "gv")
+            else:
+                gr, gk, gv, gw, gu = ops.wkv6_backward(_f32(r), _f32(k), _f32(v), _f32(w), _f32(u),
+                                                       _f32(gy), ctx.H)
             return (None, None, None, None, gr, gk, gv, gw, gu.view(ctx.H, ctx.C // ctx.H))
 
 
