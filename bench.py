@@ -5,17 +5,25 @@
 
 One step = one Bi-WKV forward and one backward over a synthetic batch at the shape
 the headline metric is quoted on (B=64 per GPU, T=4096, C=768, fp32), plus, with more
-than one GPU, the single all-reduce of the (2, C) gw/gu buffer.  Ranks shard by batch
-(weak scaling: every GPU holds its own 64 sequences; no collective on the data path).
+than one GPU, the single all-reduce of the (2, C) gw/gu buffer, launched on a side stream
+and waited for only where the next step would overwrite it.  Ranks shard by batch (weak
+scaling: every GPU holds its own 64 sequences; no collective on the data path).  The pair
+timed is the one the autograd surface runs by default: nothing is kept between forward
+and backward (--saved times the pair that keeps y and log Den instead).
 
 The metric is algorithmic HBM throughput: 32 bytes per (batch, token, channel) element
 (forward reads k, v and writes y; backward reads k, v, gy and writes gk, gv) divided by
-the step time, summed over GPUs.  Prints ONE JSON line on rank 0.
+the step time, summed over GPUs.  Prints ONE JSON line on rank 0.  `secondary` in that
+line holds the other shapes of the same path (strong scaling, the backbones, the
+sequence-length sweep, WKV6), each timed over about a second; --only NAME runs one of them,
+--batch/--tokens/--channels shrink the headline shape for a profiler capture.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -35,15 +43,28 @@ BYTES_BWD = 20          # k, v, gy read; gk, gv written
 METRIC = "biwkv_fwd_bwd_algorithmic_hbm_throughput"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the backward kernel, from an ncu capture
+# of `bench.py --batch 8 --steps 1 --warmup 3 --no-secondary --no-cpu-baseline --e2e-steps 0`
+# (B=8, T=4096, C=768: 25.2 M elements); the traffic is proportional to the element count.
+NCU_BACKWARD_DRAM_BYTES = {"recompute": 471.7e6, "saved": 694.5e6}
+NCU_CAPTURE_ELEMENTS = 8 * 4096 * 768
 
 
-def measured_peak():
+def measured_peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s sustained, which) from the file the pool's driver writes, else the fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+def measured_peak():
+    hbm, _, kind = measured_peaks()
+    return hbm, kind
 
 
 class ClockSampler:
@@ -118,29 +139,109 @@ def cpu_recurrence_seconds(B, T, C, threads, repeats=1):
     return best
 
 
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _event_ms(fn, min_ms=300.0, warm=2):
+    """Mean ms per call of fn on the current stream, over as many calls as fill `min_ms`."""
+    for _ in range(warm):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    fn()
+    b.record()
+    torch.cuda.synchronize()
+    iters = max(3, min(2000, int(math.ceil(min_ms / max(a.elapsed_time(b), 1e-3)))))
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def reference_cuda_kernels():
+    """The reference's own CUDA kernels, compiled for sm_100a from its sources into oracle/_ref/ (see
+    oracle/build_ref.py), timed on this box's GPU at the headline Bi-WKV shape and at the WKV6 shape its
+    backward supports (T <= 256).  Reported beside the CPU figure of the reference arm; None without a GPU or
+    without the compiled libraries."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    bi, v6 = os.path.join(ref_dir, "libref_biwkv.so"), os.path.join(ref_dir, "libref_wkv6.so")
+    if not torch.cuda.is_available() or not (os.path.exists(bi) or os.path.exists(v6)):
+        return None
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peak, kind = measured_peak()
+    out = {"timing": "CUDA events, mean over >= 0.3 s of back-to-back launches, inputs resident in HBM",
+           "hbm_peak_GBps": peak, "hbm_peak_source": kind}
+    g = torch.Generator(device=dev).manual_seed(0)
+    if os.path.exists(bi):
+        lib = ctypes.CDLL(bi)
+        B, T, C = WORKLOAD["B"], WORKLOAD["T"], WORKLOAD["C"]
+        k, v, gy = (torch.randn(B, T, C, device=dev, generator=g) for _ in range(3))
+        w = (torch.rand(C, device=dev, generator=g) * 2 - 1) / T
+        u = (torch.rand(C, device=dev, generator=g) * 2 - 1) / T
+        y, gk, gv = torch.empty_like(k), torch.empty_like(k), torch.empty_like(k)
+        gw, gu = torch.zeros(B, C, device=dev), torch.zeros(B, C, device=dev)
+        E = B * T * C
+        f = _event_ms(lambda: lib.ref_biwkv_forward(B, T, C, _ptr(w), _ptr(u), _ptr(k), _ptr(v), _ptr(y)))
+        b = _event_ms(lambda: lib.ref_biwkv_backward(B, T, C, _ptr(w), _ptr(u), _ptr(k), _ptr(v), _ptr(gy),
+                                                     _ptr(gw), _ptr(gu), _ptr(gk), _ptr(gv)))
+        gbs = (BYTES_FWD + BYTES_BWD) * E / ((f + b) * 1e-3) / 1e9
+        out["biwkv"] = {"source": "classification/mae/vrwkv/cuda/wkv_cuda.cu, Tmax=4096", "shape": [B, T, C],
+                        "fwd_ms": f, "bwd_ms": b, "algorithmic_GBps": gbs, "frac_of_hbm_peak": gbs / peak}
+        del k, v, gy, y, gk, gv
+    if os.path.exists(v6):
+        lib = ctypes.CDLL(v6)
+        B, T, H = 32, 196, 12
+        C = 64 * H
+        r, k, v, gy = (torch.randn(B, T, C, device=dev, generator=g) for _ in range(4))
+        ew = -torch.exp(torch.randn(B, T, C, device=dev, generator=g) * 0.5 - 0.6)
+        u6 = torch.randn(H, 64, device=dev, generator=g) * 0.1
+        y = torch.empty_like(r)
+        gr, gk, gv, gw = (torch.empty_like(r) for _ in range(4))
+        gu = torch.empty(B, C, device=dev)
+        f = _event_ms(lambda: lib.ref_wkv6_forward(B, T, C, H, _ptr(r), _ptr(k), _ptr(v), _ptr(ew), _ptr(u6), _ptr(y)))
+        b = _event_ms(lambda: lib.ref_wkv6_backward(B, T, C, H, _ptr(r), _ptr(k), _ptr(v), _ptr(ew), _ptr(u6), _ptr(gy),
+                                                    _ptr(gr), _ptr(gk), _ptr(gv), _ptr(gw), _ptr(gu)))
+        out["wkv6"] = {"source": "classification/mmcls_custom/models/backbones/cuda_v6/wkv6_cuda.cu, _N_=64 _T_=256 "
+                                 "(its backward holds T-2 floats per thread: longer sequences are outside what it was built for)",
+                       "shape": [B, T, C], "heads": H, "dtype": "f32", "fwd_ms": f, "bwd_ms": b,
+                       "elements_per_s": B * T * C / ((f + b) * 1e-3)}
+    return out
+
+
 def run_reference_arm(args):
     """The reference's recurrence on the host cores (it has no CPU code of its own: this is
-    the PyTorch restatement under oracle/), on a bounded batch sample of the workload."""
+    the PyTorch restatement under oracle/), on a bounded batch sample of the workload.  Where the
+    reference's CUDA kernels were compiled into oracle/_ref/, their same-box GPU times ride along."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     T, C = WORKLOAD["T"], WORKLOAD["C"]
-    # size the per-step sample like the cpu_baseline leg does: as many sequences as take about 5 s, so that
-    # every host thread has work (one sequence alone leaves most of them idle) and the run stays bounded
+    # size the per-step sample so that every host thread has work (one sequence alone leaves most of them idle)
+    # and the whole run stays near two minutes whatever K and W are: at most 5 s of host work per step
     probe = cpu_recurrence_seconds(1, T, C, threads)
-    sample_B = max(1, min(WORKLOAD["B"], int(5.0 / probe)))
+    steps, warmup = args.steps, args.warmup
+    budget = min(5.0, 120.0 / max(steps + warmup, 1))
+    sample_B = max(1, min(WORKLOAD["B"], int(budget / probe)))
     times = []
-    for i in range(args.warmup + args.steps):
+    for i in range(warmup + steps):
         dt = cpu_recurrence_seconds(sample_B, T, C, threads)
-        if i >= args.warmup:
+        if i >= warmup:
             times.append(dt)
     sec = sum(times) / len(times)
     gbs = (BYTES_FWD + BYTES_BWD) * sample_B * T * C / sec / 1e9
     sample = f"B={sample_B} of {WORKLOAD['B']} sequences, T={T}, C={C}, fp32, fwd+bwd scans"
+    try:
+        kernels = reference_cuda_kernels()
+    except Exception as exc:                      # never lose the CPU line to the extra measurement
+        kernels = {"error": f"{type(exc).__name__}: {exc}"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": f"biwkv_fwd_bwd B={WORKLOAD['B']} T={T} C={C} fp32",
@@ -149,50 +250,239 @@ def run_reference_arm(args):
                          "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "reference_cuda_kernels_same_box": kernels,
     }))
 
 
-def _timed(fn, dev, world, dist, iters, warm=2):
-    for _ in range(warm):
-        fn()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        fn()
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b)
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
-    return ms / iters
+# --------------------------------------------------------------------------- secondary measurements
+class Ctx:
+    """What every measurement needs: the device, the ranks, and a timer whose regions last about a second."""
+
+    def __init__(self, dev, world, rank, dist, reducer, min_ms):
+        self.dev, self.world, self.rank, self.dist, self.reducer, self.min_ms = dev, world, rank, dist, reducer, min_ms
+        self.hbm, self.tflops, self.peak_kind = measured_peaks()
+
+    def max_over_ranks(self, x):
+        if self.dist is None:
+            return x
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.item()
+
+    def sync(self):
+        torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(self, fn, warm=3, min_ms=None, marks=0):
+        """ms per call of fn (max over ranks): `warm` untimed calls, one calibration call, then as many
+        back-to-back calls as fill `min_ms` of device time, between two CUDA events with a barrier and a
+        synchronize on both sides.  Every rank runs the same number of calls (fn may hold a collective).
+        marks > 0: fn(events) records that many intermediate events in its first timed call; their gaps are
+        returned as a second value."""
+        min_ms = self.min_ms if min_ms is None else min_ms
+        for _ in range(warm):
+            fn(None) if marks else fn()
+        self.sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn(None) if marks else fn()
+        b.record()
+        torch.cuda.synchronize()
+        one = self.max_over_ranks(a.elapsed_time(b))
+        iters = max(3, min(20000, int(math.ceil(min_ms / max(one, 1e-3)))))
+        sets = [[torch.cuda.Event(enable_timing=True) for _ in range(marks)] for _ in range(min(iters, 8))] if marks else []
+        self.sync()
+        a.record()
+        for i in range(iters):
+            if marks:
+                fn(sets[i] if i < len(sets) else None)
+            else:
+                fn()
+        b.record()
+        self.sync()
+        ms = self.max_over_ranks(a.elapsed_time(b)) / iters
+        if not marks:
+            return ms
+        gaps = [statistics.mean(ev[j].elapsed_time(ev[j + 1]) for ev in sets) for j in range(marks - 1)]
+        return ms, gaps
+
+    def frac(self, gbs):
+        return gbs / self.hbm
 
 
-def side_measurements(dev, world, dist):
-    """Model-level and second-operator figures, per-GPU work fixed, summed over ranks."""
+def _biwkv_inputs(cx, B, T, C, seed, dtype=torch.float32):
+    g = torch.Generator(device=cx.dev).manual_seed(seed + cx.rank)
+    k, v, gy = (torch.randn(B, T, C, device=cx.dev, generator=g).to(dtype) for _ in range(3))
+    w = (torch.rand(C, device=cx.dev, generator=g) * 2 - 1) / T
+    u = (torch.rand(C, device=cx.dev, generator=g) * 2 - 1) / T
+    return w, u, k, v, gy
+
+
+def _pair_ms(cx, fwd, bwd):
+    """(ms per pair, forward ms, backward ms) of a forward/backward pair run back to back."""
+    def both(ev):
+        if ev is not None:
+            ev[0].record()
+        kept = fwd()
+        if ev is not None:
+            ev[1].record()
+        bwd(kept)
+        if ev is not None:
+            ev[2].record()
+    ms, (f, b) = cx.timed(both, marks=3)
+    return ms, f, b
+
+
+def sec_other_pair(cx, hl, saved_is_headline):
+    """The Bi-WKV pair that is not the headline's, same shape: with --saved the recomputing pair, otherwise the
+    pair whose forward also writes log Den (4 more bytes per element) and whose backward reads y and log Den
+    (8 more) instead of rebuilding them."""
     from vision_rwkv_b200 import ops
+    w, u, k, v, gy = hl
+    E = k.numel()
+    if saved_is_headline:
+        ms, f, b = _pair_ms(cx, lambda: ops.biwkv_forward(w, u, k, v), lambda _: ops.biwkv_backward(w, u, k, v, gy))
+        name = "nothing kept between forward and backward"
+    else:
+        ms, f, b = _pair_ms(cx, lambda: ops.biwkv_forward_save(w, u, k, v),
+                            lambda kept: ops.biwkv_backward_saved(w, u, k, v, gy, kept[0], kept[1]))
+        name = "forward keeps y and log Den for the backward"
+    gbs = (BYTES_FWD + BYTES_BWD) * E * cx.world / (ms * 1e-3) / 1e9
+    return {"pair": name, "ms": ms, "fwd_ms": f, "bwd_ms": b, "shape_per_gpu": list(k.shape),
+            "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs / cx.world)}
+
+
+def sec_autograd_surface(cx, hl):
+    """RUN_CUDA(w, u, k, v).backward(gy) through torch.autograd at the headline shape: what a backbone pays."""
+    from vision_rwkv_b200.vrwkv import RUN_CUDA
+    w, u, k, v, gy = hl
+    leaves = [x.detach().requires_grad_(True) for x in (w, u, k, v)]
+
+    def call():
+        for x in leaves:
+            x.grad = None
+        RUN_CUDA(*leaves).backward(gy)
+
+    ms = cx.timed(call)
+    for x in leaves:
+        x.grad = None
+    gbs = (BYTES_FWD + BYTES_BWD) * k.numel() * cx.world / (ms * 1e-3) / 1e9
+    return {"call": "RUN_CUDA(w, u, k, v).backward(gy), float32 leaves, gradients freed between calls",
+            "ms": ms, "shape_per_gpu": list(k.shape), "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs / cx.world)}
+
+
+def sec_strong_scaling(cx, hl):
+    """A fixed global batch of 64 sequences split over the ranks, gw|gu all-reduced once per step on a side
+    stream while the next forward runs."""
+    from vision_rwkv_b200 import ops
+    from vision_rwkv_b200.parallel import shard_bounds
+    w, u, k, v, gy = hl
+    lo, hi = shard_bounds(WORKLOAD["B"], cx.rank, cx.world)
+    nb = hi - lo
+    ks, vs, gs = k[:nb], v[:nb], gy[:nb]
+    bufs = [torch.empty(2, k.shape[2], device=cx.dev) for _ in range(2)]
+    state = {"i": 0}
+
+    def step():
+        i = state["i"] = state["i"] + 1
+        ops.biwkv_forward(w, u, ks, vs)
+        if cx.world > 1:
+            cx.reducer.wait()                    # the all-reduce of the step before ran beside this forward
+        ops.biwkv_backward(w, u, ks, vs, gs, gwgu_out=bufs[i & 1])
+        if cx.world > 1:
+            cx.reducer.launch(bufs[i & 1])
+
+    ms = cx.timed(step)
+    if cx.world > 1:
+        cx.reducer.wait()
+    E = WORKLOAD["B"] * k.shape[1] * k.shape[2]
+    gbs = (BYTES_FWD + BYTES_BWD) * E / (ms * 1e-3) / 1e9
+    return {"global_batch": WORKLOAD["B"], "batch_per_gpu": nb, "n_gpus": cx.world, "ms_per_step": ms,
+            "algorithmic_GBps_all_gpus": gbs, "frac_of_hbm_peak_per_gpu": cx.frac(gbs / cx.world),
+            "collective": "one all-reduce of (2, C) per step, overlapped with the next forward" if cx.world > 1 else "none"}
+
+
+def sec_biwkv_bf16(cx, hl):
+    """Bi-WKV with bfloat16 activations at the headline shape: 6 + 10 = 16 bytes per element."""
+    from vision_rwkv_b200 import ops
+    w, u, k, v, gy = hl
+    kh, vh, gh = k.bfloat16(), v.bfloat16(), gy.bfloat16()
+    ms, f, b = _pair_ms(cx, lambda: ops.biwkv_forward(w, u, kh, vh), lambda _: ops.biwkv_backward(w, u, kh, vh, gh))
+    gbs = 16 * k.numel() * cx.world / (ms * 1e-3) / 1e9
+    return {"ms": ms, "fwd_ms": f, "bwd_ms": b, "shape_per_gpu": list(k.shape), "algorithmic_GBps": gbs,
+            "frac_of_hbm_peak": cx.frac(gbs / cx.world), "elements_per_s": k.numel() * cx.world / (ms * 1e-3)}
+
+
+def sec_sequence_sweep(cx):
+    """Bi-WKV forward+backward against sequence length at B=8, C=768, fp32: cost per token stays flat."""
+    from vision_rwkv_b200 import ops
+    rows = []
+    for T in (1024, 4096, 16384):
+        B, C = 8, 768
+        w, u, k, v, gy = _biwkv_inputs(cx, B, T, C, seed=T)
+        ms, f, b = _pair_ms(cx, lambda: ops.biwkv_forward(w, u, k, v), lambda _: ops.biwkv_backward(w, u, k, v, gy))
+        gbs = (BYTES_FWD + BYTES_BWD) * B * T * C / (ms * 1e-3) / 1e9
+        rows.append({"T": T, "fwd_ms": f, "bwd_ms": b, "ms": ms, "us_per_token": ms * 1e3 / (B * T),
+                     "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs),
+                     "kernels": "cluster-resident" if T <= 4096 else "chunked tiles with cross-tile exchange"})
+        del k, v, gy
+    return {"B": 8, "C": 768, "dtype": "f32", "per_gpu": True, "rows": rows}
+
+
+def _images(cx, n, size):
+    g = torch.Generator(device=cx.dev).manual_seed(99 + cx.rank)
+    h, w_ = (size, size) if isinstance(size, int) else size
+    return torch.randn(n, 3, h, w_, device=cx.dev, generator=g)
+
+
+def _share(total, cx):
+    from vision_rwkv_b200.parallel import shard_bounds
+    lo, hi = shard_bounds(total, cx.rank, cx.world)
+    return hi - lo
+
+
+def sec_vrwkv_s_inference(cx):
+    """VRWKV-S (embed 384, 12 blocks) inference on 256 synthetic 224x224 images split over the ranks (T=196):
+    fp32 throughout, and bf16 autocast for the linear layers with Bi-WKV reading bfloat16."""
     from vision_rwkv_b200.backbone import build
-    out = {}
-    # VRWKV-B (embed 768, 12 blocks, patch 16) inference on 224x224 synthetic images, batch-sharded,
-    # bf16 autocast for the linear layers, fp32 Bi-WKV: no collective
+    total = 256
+    n = _share(total, cx)
+    model = build("vrwkv_s").to(cx.dev).eval()
+    img = _images(cx, n, 224)
+    out = {"global_batch": total, "batch_per_gpu": n, "n_gpus": cx.world, "resolution": 224, "tokens": 196}
+
+    def run32():
+        with torch.no_grad():
+            model(img)
+
+    def run16():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            model(img)
+
+    for name, fn in (("fp32", run32), ("bf16_autocast", run16)):
+        ms = cx.timed(fn)
+        out[name] = {"ms_per_batch": ms, "img_per_s": total / (ms * 1e-3)}
+    return out
+
+
+def sec_vrwkv_b_inference(cx):
+    """VRWKV-B (embed 768, 12 blocks, patch 16) inference on 224x224 synthetic images, 64 per GPU, bf16
+    autocast for the linear layers: no collective."""
+    from vision_rwkv_b200.backbone import build
     B = 64
-    model = build("vrwkv_b").to(dev).eval()
-    img = torch.randn(B, 3, 224, 224, device=dev)
+    model = build("vrwkv_b").to(cx.dev).eval()
+    img = _images(cx, B, 224)
 
     def infer():
         with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             model(img)
 
-    ms = _timed(infer, dev, world, dist, iters=5)
-    out["vrwkv_b_inference"] = {"img_per_s": B * world / (ms * 1e-3), "ms_per_batch": ms,
-                                "batch_per_gpu": B, "resolution": 224, "n_gpus": world,
-                                "gemm_dtype": "bf16 autocast", "wkv_dtype": "f32"}
-    # the same network, forward + backward of a sum-of-squares loss (no optimizer step), batch 32 per GPU:
-    # bfloat16 activations reach Bi-WKV under autocast, so its bf16-tile kernels run in both directions
+    ms = cx.timed(infer)
+    out = {"inference": {"img_per_s": B * cx.world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": B,
+                         "resolution": 224, "n_gpus": cx.world, "gemm_dtype": "bf16 autocast"}}
+    # the same network, forward + backward of a sum-of-squares loss (no optimizer step), batch 32 per GPU
     model.train()
     img_t = img[:32]
 
@@ -203,76 +493,194 @@ def side_measurements(dev, world, dist):
             loss = model(img_t)[0].float().square().mean()
         loss.backward()
 
-    ms = _timed(train_step, dev, world, dist, iters=5)
-    out["vrwkv_b_forward_backward"] = {"img_per_s": 32 * world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": 32,
-                                       "resolution": 224, "n_gpus": world, "gemm_dtype": "bf16 autocast",
-                                       "wkv_dtype": "bf16 tiles, f32 arithmetic", "optimizer": "none",
-                                       "gradient_all_reduce": "none (per-rank replicas)"}
-    del model, img_t
-    # VRWKV6-B (embed 768, 12 heads, 12 blocks): same images; under autocast r, k, v reach the WKV6 operator in
-    # bfloat16 and the tcgen05 forward runs
+    ms = cx.timed(train_step)
+    out["forward_backward"] = {"img_per_s": 32 * cx.world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": 32,
+                               "resolution": 224, "n_gpus": cx.world, "gemm_dtype": "bf16 autocast",
+                               "optimizer": "none", "gradient_all_reduce": "none (per-rank replicas)"}
+    return out
+
+
+def sec_vrwkv_l_train(cx):
+    """VRWKV-L (embed 1024, 24 blocks) training step at 384x384 (T=576), 64 images split over the ranks:
+    activation checkpointing per block, bf16 autocast for the linear layers, cross-entropy on random labels over
+    1000 classes through a linear head on the pooled features, fused AdamW.  Across ranks the decay and bonus
+    gradients of all 24 layers travel in ONE all-reduce of a persistent (24, 2, 1024) buffer; the other
+    parameters' gradients are the training framework's business and are not reduced here."""
+    import torch.nn.functional as F
+    from vision_rwkv_b200.backbone import build
+    total = 64
+    n = _share(total, cx)
+    model = build("vrwkv_l", img_size=384, with_cp=True).to(cx.dev).train()
+    head = torch.nn.Linear(1024, 1000).to(cx.dev)
+    params = list(model.parameters()) + list(head.parameters())
+    opt = torch.optim.AdamW(params, lr=1e-5, fused=True)
+    img = _images(cx, n, 384)
+    labels = torch.randint(0, 1000, (n,), device=cx.dev)
+    decays = [blk.att.spatial_decay for blk in model.layers]
+    firsts = [blk.att.spatial_first for blk in model.layers]
+    buf = torch.zeros(len(decays), 2, 1024, device=cx.dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            feat = model(img)[0]
+            logits = head(feat.float().mean(dim=(2, 3)))
+        F.cross_entropy(logits.float(), labels).backward()
+        if cx.world > 1:
+            buf[:, 0].copy_(torch.stack([p.grad for p in decays]))
+            buf[:, 1].copy_(torch.stack([p.grad for p in firsts]))
+            cx.reducer.launch(buf)
+            cx.reducer.wait()
+            for i, (d, f_) in enumerate(zip(decays, firsts)):
+                d.grad.copy_(buf[i, 0])
+                f_.grad.copy_(buf[i, 1])
+        opt.step()
+
+    ms = cx.timed(step, warm=2)
+    return {"global_batch": total, "batch_per_gpu": n, "n_gpus": cx.world, "resolution": 384, "tokens": 576,
+            "ms_per_step": ms, "img_per_s": total / (ms * 1e-3), "with_cp": True, "gemm_dtype": "bf16 autocast",
+            "optimizer": "AdamW (fused)", "collective": "one all-reduce of (24, 2, 1024) gw|gu per step" if cx.world > 1 else "none"}
+
+
+def sec_vrwkv_b_dense(cx):
+    """VRWKV-B as a dense-prediction backbone: 16 synthetic 800x1344 images split over the ranks (50x84 = 4200
+    tokens), inference, bf16 autocast for the linear layers."""
+    from vision_rwkv_b200.backbone import build
+    total = 16
+    n = _share(total, cx)
+    model = build("vrwkv_b", img_size=(800, 1344)).to(cx.dev).eval()
+    img = _images(cx, n, (800, 1344))
+
+    def infer():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            model(img)
+
+    ms = cx.timed(infer)
+    return {"global_batch": total, "batch_per_gpu": n, "n_gpus": cx.world, "resolution": [800, 1344], "tokens": 4200,
+            "ms_per_batch": ms, "img_per_s": total / (ms * 1e-3), "gemm_dtype": "bf16 autocast"}
+
+
+def sec_vrwkv6_b_inference(cx):
+    """VRWKV6-B (embed 768, 12 heads, 12 blocks) inference, 64 images of 224x224 per GPU: under autocast r, k, v
+    reach the WKV6 operator in bfloat16 and the tcgen05 forward runs."""
     from vision_rwkv_b200.backbone6 import build_v6
-    model6 = build_v6("vrwkv6_b").to(dev).eval()
+    B = 64
+    model6 = build_v6("vrwkv6_b").to(cx.dev).eval()
+    img = _images(cx, B, 224)
 
     def infer6():
         with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             model6(img)
 
-    ms = _timed(infer6, dev, world, dist, iters=5)
-    out["vrwkv6_b_inference"] = {"img_per_s": B * world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": B,
-                                 "resolution": 224, "n_gpus": world, "gemm_dtype": "bf16 autocast",
-                                 "wkv_dtype": "bf16 operands on tensor cores, f32 state"}
-    del model6, img
-    # Bi-WKV with bfloat16 activations at the headline shape: 6 + 10 = 16 bytes per element fwd+bwd
-    Bh, Th, Ch = WORKLOAD["B"], WORKLOAD["T"], WORKLOAD["C"]
-    gh = torch.Generator(device=dev).manual_seed(11)
-    kh, vh, gyh = (torch.randn(Bh, Th, Ch, device=dev, generator=gh).bfloat16() for _ in range(3))
-    wh = (torch.rand(Ch, device=dev, generator=gh) * 2 - 1) / Th
-    uh = (torch.rand(Ch, device=dev, generator=gh) * 2 - 1) / Th
+    ms = cx.timed(infer6)
+    return {"img_per_s": B * cx.world / (ms * 1e-3), "ms_per_batch": ms, "batch_per_gpu": B, "resolution": 224,
+            "n_gpus": cx.world, "gemm_dtype": "bf16 autocast", "wkv_dtype": "bf16 operands on tensor cores, f32 state"}
 
-    def biwkv_bf16_step():
-        ops.biwkv_forward(wh, uh, kh, vh)
-        ops.biwkv_backward(wh, uh, kh, vh, gyh)
 
-    ms = _timed(biwkv_bf16_step, dev, world, dist, iters=5)
-    out["biwkv_bf16_fwd_bwd"] = {"ms": ms, "B_per_gpu": Bh, "T": Th, "C": Ch,
-                                 "algorithmic_GBps": 16 * Bh * Th * Ch * world / (ms * 1e-3) / 1e9,
-                                 "elements_per_s": Bh * Th * Ch * world / (ms * 1e-3)}
-    del kh, vh, gyh
-    # WKV6 operator as in VRWKV6-B: C=768, 12 heads, B=32 per GPU, T=196, fwd+bwd (exact fp32 sweeps)
-    Bw, T, H = 32, 196, 12
+def _wkv6_inputs(cx, B, T, H, dtype):
+    g = torch.Generator(device=cx.dev).manual_seed(7 + cx.rank)
     C = 64 * H
-    g = torch.Generator(device=dev).manual_seed(7)
-    r, k6, v6, gy6 = (torch.randn(Bw, T, C, device=dev, generator=g) for _ in range(4))
-    w6 = torch.randn(Bw, T, C, device=dev, generator=g) * 0.5 - 0.6
-    u6 = torch.randn(H, 64, device=dev, generator=g) * 0.1
+    r, k, v, gy = (torch.randn(B, T, C, device=cx.dev, generator=g).to(dtype) for _ in range(4))
+    w = torch.randn(B, T, C, device=cx.dev, generator=g) * 0.5 - 0.6
+    u = torch.randn(H, 64, device=cx.dev, generator=g) * 0.1
+    return r, k, v, w, u, gy
 
-    def wkv6_step():
-        ops.wkv6_forward(r, k6, v6, w6, u6, H)
-        ops.wkv6_backward(r, k6, v6, w6, u6, gy6, H)
 
-    ms = _timed(wkv6_step, dev, world, dist, iters=5)
-    out["wkv6_fwd_bwd"] = {"ms": ms, "B_per_gpu": Bw, "T": T, "C": C, "H": H, "dtype": "f32",
-                           "elements_per_s": Bw * T * C * world / (ms * 1e-3)}
-    del r, k6, v6, gy6, w6
-    # WKV6 forward at a dense-prediction length (T=4096): exact fp32 sweeps against the tcgen05 kernel
+def sec_wkv6(cx):
+    """WKV6 as in VRWKV6-B: C=768, 12 heads of 64, 32 sequences split over the ranks, forward + backward.
+    T=196 in fp32 (exact sweeps) and bf16 (tcgen05 kernels); T=4096 in bf16 with its roofline: algorithmic
+    bytes 28 per element if every tensor moved as bfloat16 (forward reads r, k, v, w and writes y; backward
+    reads r, k, v, w, gy and writes gr, gk, gv, gw), 3584 flops per element in the chunked formulation
+    (14 head-size products of 2 x 64 flops each: 4 forward, 10 backward)."""
+    from vision_rwkv_b200 import ops
+    total, H = 32, 12
+    C = 64 * H
+    n = _share(total, cx)
+    out = {"global_batch": total, "batch_per_gpu": n, "n_gpus": cx.world, "C": C, "heads": H}
+    r, k, v, w, u, gy = _wkv6_inputs(cx, n, 196, H, torch.float32)
+    ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(r, k, v, w, u, H), lambda _: ops.wkv6_backward(r, k, v, w, u, gy, H))
+    out["wkv6_fwd_bwd_t196_f32"] = {"ms": ms, "fwd_ms": f, "bwd_ms": b, "kernels": "exact fp32 state sweeps",
+                                    "elements_per_s": total * 196 * C / (ms * 1e-3)}
+    rh, kh, vh, gh = (x.bfloat16() for x in (r, k, v, gy))
+    ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(rh, kh, vh, w, u, H, tensor_cores=True),
+                        lambda _: ops.wkv6_backward(rh, kh, vh, w, u, gh, H, tensor_cores=True))
+    out["wkv6_fwd_bwd_t196_bf16"] = {"ms": ms, "fwd_ms": f, "bwd_ms": b, "kernels": "tcgen05 forward and backward",
+                                     "elements_per_s": total * 196 * C / (ms * 1e-3)}
+    del r, k, v, w, gy, rh, kh, vh, gh
     T = 4096
-    r, k6, v6 = (torch.randn(Bw, T, C, device=dev, generator=g) for _ in range(3))
-    w6 = torch.randn(Bw, T, C, device=dev, generator=g) * 0.5 - 0.6
-    ms_exact = _timed(lambda: ops.wkv6_forward(r, k6, v6, w6, u6, H), dev, world, dist, iters=5)
-    ms_tc = _timed(lambda: ops.wkv6_forward(r, k6, v6, w6, u6, H, tensor_cores=True), dev, world, dist, iters=5)
-    out["wkv6_forward_t4096"] = {"ms_exact_f32": ms_exact, "ms_tensor_cores": ms_tc, "B_per_gpu": Bw, "T": T,
-                                 "C": C, "H": H, "algorithmic_GBps_tensor_cores": 20 * Bw * T * C / (ms_tc * 1e-3) / 1e9}
-    del r, k6, v6, w6
-    # fused Q-Shift + 3 interpolations, forward: 16 bytes per element
+    r, k, v, w, u, gy = _wkv6_inputs(cx, n, T, H, torch.bfloat16)
+    ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(r, k, v, w, u, H, tensor_cores=True),
+                        lambda _: ops.wkv6_backward(r, k, v, w, u, gy, H, tensor_cores=True))
+    E = total * T * C
+    gbs = 28 * E / (ms * 1e-3) / 1e9
+    tf = 3584 * E / (ms * 1e-3) / 1e12
+    moved = 42 * E / (ms * 1e-3) / 1e9
+    out["wkv6_fwd_bwd_t4096_bf16"] = {
+        "ms": ms, "fwd_ms": f, "bwd_ms": b, "kernels": "tcgen05 forward and backward", "T": T,
+        "elements_per_s": E / (ms * 1e-3),
+        "roofline": {"hbm": {"achieved": gbs, "peak": cx.hbm * cx.world, "unit": "GB/s", "frac": gbs / (cx.hbm * cx.world),
+                             "algorithmic_bytes_per_element": 28,
+                             "moved_bytes_per_element": 42, "moved_GBps": moved,
+                             "note": "w is read and y, gr, gk, gv, gw are written as float32 by these entry points"},
+                     "tensor": {"achieved": tf, "peak": cx.tflops * cx.world, "unit": "TFLOP/s",
+                                "frac": tf / (cx.tflops * cx.world), "flops_per_element": 3584},
+                     "peak_source": cx.peak_kind}}
+    # the exact float32 sweeps on the same values, for comparison
+    r32, k32, v32, g32 = (x.float() for x in (r, k, v, gy))
+    ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(r32, k32, v32, w, u, H),
+                        lambda _: ops.wkv6_backward(r32, k32, v32, w, u, g32, H))
+    out["wkv6_fwd_bwd_t4096_f32_exact"] = {"ms": ms, "fwd_ms": f, "bwd_ms": b, "kernels": "exact fp32 state sweeps",
+                                           "elements_per_s": E / (ms * 1e-3)}
+    return out
+
+
+def sec_qshift(cx):
+    """Fused Q-Shift + 3 interpolations, forward: one read of x, three writes: 16 bytes per element."""
+    from vision_rwkv_b200 import ops
+    g = torch.Generator(device=cx.dev).manual_seed(3)
     Bq, Hh, Ww, Cq = 64, 64, 64, 768
-    x = torch.randn(Bq, Hh * Ww, Cq, device=dev, generator=g)
-    mixes = [torch.rand(Cq, device=dev, generator=g) for _ in range(3)]
-    ms = _timed(lambda: ops.qshift_mix_forward(x, mixes, (Hh, Ww)), dev, world, dist, iters=10)
+    x = torch.randn(Bq, Hh * Ww, Cq, device=cx.dev, generator=g)
+    mixes = [torch.rand(Cq, device=cx.dev, generator=g) for _ in range(3)]
+    ms = cx.timed(lambda: ops.qshift_mix_forward(x, mixes, (Hh, Ww)))
     gbs = 16 * x.numel() / (ms * 1e-3) / 1e9
-    peak, _ = measured_peak()
-    out["qshift_mix_forward"] = {"ms": ms, "algorithmic_GBps": gbs, "frac_of_hbm_peak": gbs / peak,
-                                 "shape": [Bq, Hh * Ww, Cq], "outputs": 3}
+    return {"ms": ms, "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs), "shape": [Bq, Hh * Ww, Cq],
+            "outputs": 3, "per_gpu": True}
+
+
+def side_measurements(cx, hl, args):
+    """Every secondary measurement by name; one that raises leaves its message in place of its numbers."""
+    table = [
+        ("other_pair", lambda: sec_other_pair(cx, hl, args.saved)),
+        ("autograd_surface", lambda: sec_autograd_surface(cx, hl)),
+        ("strong_scaling_b64", lambda: sec_strong_scaling(cx, hl)),
+        ("biwkv_bf16_fwd_bwd", lambda: sec_biwkv_bf16(cx, hl)),
+        ("biwkv_sequence_sweep_b8", lambda: sec_sequence_sweep(cx)),
+        ("vrwkv_s_inference_b256", lambda: sec_vrwkv_s_inference(cx)),
+        ("vrwkv_b", lambda: sec_vrwkv_b_inference(cx)),
+        ("vrwkv_l_train_step_b64_t576", lambda: sec_vrwkv_l_train(cx)),
+        ("vrwkv_b_dense_800x1344_b16", lambda: sec_vrwkv_b_dense(cx)),
+        ("vrwkv6_b_inference", lambda: sec_vrwkv6_b_inference(cx)),
+        ("wkv6", lambda: sec_wkv6(cx)),
+        ("qshift_mix_forward", lambda: sec_qshift(cx)),
+    ]
+    needs_headline = {"other_pair", "autograd_surface", "strong_scaling_b64", "biwkv_bf16_fwd_bwd"}
+    out = {"timing": f"each figure: CUDA events around >= {cx.min_ms:.0f} ms of back-to-back calls after warm-up, max over ranks"}
+    freed = False
+    for name, fn in table:
+        if args.only and name not in args.only:
+            continue
+        if name not in needs_headline and not freed:
+            hl.clear()                            # the headline tensors (2.4 GB) are not needed from here on
+            torch.cuda.empty_cache()
+            freed = True
+        try:
+            out[name] = fn()
+        except Exception as exc:
+            # every rank sees the same exception class for a shape or memory problem; a rank-local failure
+            # inside a collective would stall the others, which the launcher's timeout then reports
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:400]}
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
     return out
 
 
@@ -280,24 +688,30 @@ def side_measurements(dev, world, dist):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 600: about a second; reference arm 5)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed steps before them (default 20; reference arm 1)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--recompute", action="store_true",
-                    help="time the forward/backward pair that keeps nothing between the two calls")
+    ap.add_argument("--saved", action="store_true",
+                    help="time the pair whose forward keeps y and log Den for the backward instead of the default pair")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunk", type=int, default=4, help="sequences per pipelined chunk of the host-buffer call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"], help="sequences per GPU")
     ap.add_argument("--tokens", type=int, default=WORKLOAD["T"])
     ap.add_argument("--channels", type=int, default=WORKLOAD["C"])
-    ap.add_argument("--no-secondary", action="store_true",
-                    help="skip the model-level and WKV6 side measurements")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements")
+    ap.add_argument("--only", action="append", default=[], help="run only this secondary measurement (repeatable)")
+    ap.add_argument("--min-ms", type=float, default=1000.0, help="length of each secondary timed region")
+    ap.add_argument("--sustain-ms", type=float, default=1500.0,
+                    help="after the K timed steps, keep stepping for this long so that the clock samples cover a loaded GPU")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
+        args.steps = 5 if args.steps is None else args.steps
+        args.warmup = 1 if args.warmup is None else args.warmup
         run_reference_arm(args)
         return
+    args.steps = 600 if args.steps is None else args.steps
+    args.warmup = max(20 if args.warmup is None else args.warmup, 3)
 
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -322,7 +736,6 @@ def main():
         dist.barrier()
     from vision_rwkv_b200 import launch_count, ops
     from vision_rwkv_b200.parallel import GradAllReducer
-    from vision_rwkv_b200.vrwkv import RUN_CUDA
 
     B, T, C = args.batch, args.tokens, args.channels
     E = B * T * C
@@ -332,77 +745,80 @@ def main():
     gy = torch.randn(B, T, C, device=dev, generator=gen)
     w = (torch.rand(C, device=dev, generator=gen) * 2 - 1) / T
     u = (torch.rand(C, device=dev, generator=gen) * 2 - 1) / T
-    gwgu = torch.empty(2, C, device=dev)
+    gwgu = [torch.empty(2, C, device=dev) for _ in range(2)]
     reducer = GradAllReducer()
+    cx = Ctx(dev, world, rank, dist if world > 1 else None, reducer, args.min_ms)
 
-    # The training step as the autograd surface runs it by default: the forward keeps log Den next to y,
-    # the backward starts from both (--recompute: the pair that keeps nothing and rebuilds them).
+    # The training step as the autograd surface runs it by default: nothing is kept, the backward rebuilds
+    # y and Den from k, v (--saved: the forward keeps log Den next to y, the backward starts from both).
     def forward_step():
-        if args.recompute:
-            return ops.biwkv_forward(w, u, k, v), None
-        return ops.biwkv_forward_save(w, u, k, v)
+        if args.saved:
+            return ops.biwkv_forward_save(w, u, k, v)
+        return ops.biwkv_forward(w, u, k, v), None
 
-    def backward_step(y, logden):
+    def backward_step(y, logden, out):
         if logden is None:
-            ops.biwkv_backward(w, u, k, v, gy, gwgu_out=gwgu)
+            ops.biwkv_backward(w, u, k, v, gy, gwgu_out=out)
         else:
-            ops.biwkv_backward_saved(w, u, k, v, gy, y, logden, gwgu_out=gwgu)
+            ops.biwkv_backward_saved(w, u, k, v, gy, y, logden, gwgu_out=out)
 
-    def step():
+    def step(i, ev=None):
+        if ev is not None:
+            ev[0].record()
         y, logden = forward_step()
-        backward_step(y, logden)
+        if ev is not None:
+            ev[1].record()
         if world > 1:
-            reducer.launch(gwgu)
-            reducer.wait()
-        return y
-
-    def sync_all():
-        torch.cuda.synchronize()
+            reducer.wait()            # the all-reduce of step i-1 ran on its own stream beside this forward
+        backward_step(y, logden, gwgu[i & 1])
+        if ev is not None:
+            ev[2].record()
         if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+            reducer.launch(gwgu[i & 1])
 
-    for _ in range(args.warmup):
-        step()
-    sync_all()
+    for i in range(args.warmup):
+        step(i)
+    reducer.wait()
+    cx.sync()
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
     launches0 = launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
-               torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    sync_all()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(min(args.steps, 64))]
+    cx.sync()
     t_host0 = time.perf_counter()
     ev[0].record()
     for i in range(args.steps):
-        a, b, c = fwd_ev[i]
-        a.record()
-        y_i, logden_i = forward_step()
-        b.record()
-        backward_step(y_i, logden_i)
-        c.record()
-        if world > 1:
-            reducer.launch(gwgu)
-            reducer.wait()
+        step(i, marks[i] if i < len(marks) else None)
+    reducer.wait()
     ev[1].record()
-    sync_all()
-    t_host1 = time.perf_counter()
+    cx.sync()
     launches = launch_count() - launches0
-    elapsed_ms = ev[0].elapsed_time(ev[1])
-    fwd_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in fwd_ev)
-    bwd_ms = statistics.mean(b.elapsed_time(c) for _, b, c in fwd_ev)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = t.item()
-    clocks = sampler.stop(t_host0, t_host1) if rank == 0 else None
+    elapsed_ms = cx.max_over_ranks(ev[0].elapsed_time(ev[1]))
     ms_per_step = elapsed_ms / args.steps
+    # keep the GPU under the same load until the clock samples cover at least --sustain-ms: the figures of this
+    # region are reported beside the headline (sustained), they do not replace it
+    more = max(0, int(math.ceil((args.sustain_ms - elapsed_ms) / max(ms_per_step, 1e-3))))
+    sustained = None
+    if more > 0:
+        ev[2].record()
+        for i in range(more):
+            step(i)
+        reducer.wait()
+        ev[3].record()
+        cx.sync()
+        sustained = {"steps": more, "ms_per_step": cx.max_over_ranks(ev[2].elapsed_time(ev[3])) / more}
+    t_host1 = time.perf_counter()
+    fwd_ms = statistics.mean(m[0].elapsed_time(m[1]) for m in marks)
+    bwd_ms = statistics.mean(m[1].elapsed_time(m[2]) for m in marks)
+    clocks = sampler.stop(t_host0, t_host1) if rank == 0 else None
     value = (BYTES_FWD + BYTES_BWD) * E * world / (ms_per_step * 1e-3) / 1e9
+    ops.raise_if_failed()             # a bounded device-side wait that ran out in any launch so far ends the run here
 
-    # ---- end to end through the public autograd surface, host buffers ------------------
+    # ---- end to end through the public host-buffer call ------------------
     e2e = None
     if args.e2e_steps > 0:
         hk, hv, hgy = (torch.empty(B, T, C, pin_memory=True).copy_(x) for x in (k, v, gy))
@@ -418,32 +834,29 @@ def main():
                                         chunk=args.e2e_chunk, reducer=reducer if world > 1 else None)
 
         e2e_step()
-        sync_all()
+        cx.sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.e2e_steps):
             e2e_step()
         e1.record()
-        sync_all()
-        e_ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([e_ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = t.item()
-        e_ms /= args.e2e_steps
+        cx.sync()
+        e_ms = cx.max_over_ranks(e0.elapsed_time(e1)) / args.e2e_steps
         e2e = {"value": (BYTES_FWD + BYTES_BWD) * E * world / (e_ms * 1e-3) / 1e9, "unit": UNIT,
                "ms_per_step": e_ms, "steps": args.e2e_steps,
-               "api": "vision_rwkv_b200.host.biwkv_forward_backward_host (pinned host buffers in and out)",
+               "api": "vision_rwkv_b200.host.biwkv_forward_backward_host: pinned host buffers in and out, batch chunks "
+                      "pipelined over three streams, ops.biwkv_forward + ops.biwkv_backward (the C ABI) per chunk",
                "h2d_bytes_per_step": (3 * E + 2 * C) * 4 * world,
                "d2h_bytes_per_step": (3 * E + 2 * C) * 4 * world}
         del hk, hv, hgy, out_y, out_gk, out_gv
 
-    # ---- side measurements (not the headline): VRWKV-B inference img/s, WKV6 op, Q-Shift ----
+    # ---- secondary measurements (not the headline) ----
     secondary = None
     if not args.no_secondary:
+        hl = [w, u, k, v, gy]
         del k, v, gy
-        torch.cuda.empty_cache()
-        secondary = side_measurements(dev, world, dist if world > 1 else None)
+        secondary = side_measurements(cx, hl, args)
+        ops.raise_if_failed()
 
     if rank != 0:
         if world > 1:
@@ -454,15 +867,15 @@ def main():
     peak, peak_kind = measured_peak()
     bwd_gbs = BYTES_BWD * E / (bwd_ms * 1e-3) / 1e9
     fwd_gbs = BYTES_FWD * E / (fwd_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "biwkv backward (all launches of one backward call)",
+    pair = "saved" if args.saved else "recompute"
+    roofline = {"bound": "hbm",
+                "kernel": "Bi-WKV backward: " + ("biwkv_backward_saved tile kernel + partial reduction" if args.saved else
+                                                 "biwkv_resident_kernel<backward> (+ idle exact-arithmetic kernel and partial reduction)"),
                 "achieved": bwd_gbs, "peak": peak, "peak_source": f"{peak_kind} copy bandwidth",
                 "unit": "GB/s", "frac": bwd_gbs / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel from the ncu capture at B=8
-                # (profiles/), scaled to this launch by its element count: the traffic is proportional to it
-                "traffic": (480.0e6 if args.recompute else 694.5e6) * E / (8 * 4096 * 768),
-                "traffic_source": "ncu at B=8,T=4096,C=768 scaled by elements: "
-                                  + ("profiles/biwkv_fused_b8_t4096_c768.md" if args.recompute
-                                     else "profiles/biwkv_saved_b8_t4096_c768.md"),
+                "traffic": NCU_BACKWARD_DRAM_BYTES[pair] * E / NCU_CAPTURE_ELEMENTS,
+                "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch under ncu at B=8, T=4096, C=768, "
+                                  "scaled by the element count",
                 "algorithmic_bytes_per_launch": BYTES_BWD * E, "ms_per_launch": bwd_ms,
                 "forward": {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "ms": fwd_ms,
                             "algorithmic_bytes": BYTES_FWD * E},
@@ -485,11 +898,14 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"biwkv_fwd_bwd B={B}/gpu T={T} C={C} fp32",
-                   "backward": "recomputes y and Den" if args.recompute else
-                               "starts from the y and log Den the forward kept (4 more bytes per element written, 8 read)",
+                   "backward": "starts from the y and log Den the forward kept (4 more bytes per element written, 8 read)"
+                               if args.saved else "rebuilds y and Den from k, v: nothing is kept between the two calls",
                    "global_batch": B * world, "parallelism": f"batch-sharded x{world}",
-                   "collective": "one all-reduce of gw|gu (2,C) per step" if world > 1 else "none",
-                   "l2": "inputs (2.4 GB per pass) exceed the 126 MB L2; no explicit flush"},
+                   "collective": "one all-reduce of gw|gu (2,C) per step on a side stream, waited for before the next "
+                                 "backward" if world > 1 else "none",
+                   "l2": f"inputs ({12 * E / 1e9:.1f} GB per step) exceed the 126 MB L2; no explicit flush"
+                         if 12 * E > 2 * 126e6 else "inputs fit the L2 at this reduced shape: not a bench figure"},
+        "sustained": sustained,
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
         "clocks": clocks, "secondary": secondary,
     })

@@ -77,7 +77,9 @@ def test_output_is_the_f32_result_rounded_once(cuda_device):
     want = y32.bfloat16()
     differ = (y16 != want)
     assert differ.float().mean().item() < 1e-3
-    step = y32.abs() * 2.0 ** -7           # one unit in the last place of bf16 is at most this
+    # one unit in the last place of bf16 is at most |y| * 2^-7; where y is a small difference of larger terms the two
+    # float32 evaluations themselves differ by a few 1e-6 of max|y|, which is the floor
+    step = torch.maximum(y32.abs() * 2.0 ** -7, y32.abs().max() * 4e-6)
     assert ((y16.float() - want.float()).abs() <= step).all()
 
 

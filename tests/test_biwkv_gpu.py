@@ -270,8 +270,23 @@ def test_bounded_wait_runs_out_and_reports(cuda_device, kernel_path):
         with pytest.raises(_lib.VrwkvError, match="status word"):
             ops.biwkv_backward(w, u, k, v, gy)
         torch.cuda.synchronize()
+        # the default mode does not synchronise: the call returns, and the failure surfaces at a later call
+        # into the module or, at the latest, when the caller asks
+        ops.CHECK_STATUS = False
+        ops.biwkv_forward(w, u, k, v)
+        with pytest.raises(_lib.VrwkvError, match="earlier launch"):
+            ops.raise_if_failed()
+        ops.biwkv_forward(w, u, k, v)
+        torch.cuda.synchronize()
+        with pytest.raises(_lib.VrwkvError, match="earlier launch"):
+            ops.biwkv_forward(w, u, k, v)
+        torch.cuda.synchronize()
+        with pytest.raises(_lib.VrwkvError, match="earlier launch"):
+            ops.raise_if_failed()
+        ops.CHECK_STATUS = True
     finally:
         lib.vrwkv_set_path(0)
+    ops.raise_if_failed()
     # the context is intact and the next call is right again
     y = ops.biwkv_forward(w, u, k, v)
     assert rel_err(y, O.biwkv_scan_forward(*[x.double().cpu() for x in (w, u, k, v)])) <= TOL

@@ -3,6 +3,7 @@ GPU through the C ABI: the oracle on a slice that finishes in seconds (channels 
 (batch, head) pairs are independent, so a slice of the full-size result must equal the
 oracle on the sliced inputs), plus shape/finite checks on the whole output.
 
+  headline    Bi-WKV fwd+bwd,  B=64, T=4096, C=768 (the shape the benchmark times)
   configs[1]  VRWKV-S inference   Bi-WKV forward,  B=256, T=196,  C=384
   configs[2]  VRWKV-L training    Bi-WKV fwd+bwd,  B=64 per box (8 here), T=576, C=1024
   configs[3]  dense prediction    Bi-WKV fwd+bwd,  B=16 (2 here), T=4200, C=768; sweep T in
@@ -36,6 +37,29 @@ def _check_slice(w, u, k, v, gy, y, grads, b, cs, tol=1e-5):
         _, _, gk_ref, gv_ref = BO.biwkv_scan_backward(*sl, gy[b:b + 1, :, cs].double().cpu())
         assert rel_err(grads[2][b:b + 1, :, cs], gk_ref) <= tol
         assert rel_err(grads[3][b:b + 1, :, cs], gv_ref) <= tol
+
+
+def test_headline_shape_full_size(cuda_device):
+    """The benchmark's own launch geometry: B=64, T=4096, C=768 through the default kernels (clusters of 16 CTAs,
+    24 channel strips, 1536 work units), checked against the float64 recurrence on random (sequence, 4-channel)
+    slices that include the last sequence and the last strip, and gw, gu on a 2-channel slice over the whole batch."""
+    from vision_rwkv_b200 import ops
+    B, T, C = 64, 4096, 768
+    w, u, k, v, gy = _biwkv_inputs(B, T, C, cuda_device, 64)
+    y = ops.biwkv_forward(w, u, k, v)
+    grads = ops.biwkv_backward(w, u, k, v, gy)
+    ops.raise_if_failed()
+    assert y.shape == k.shape and torch.isfinite(y).all() and all(torch.isfinite(g).all() for g in grads)
+    rng = torch.Generator().manual_seed(5)
+    picks = [(B - 1, C - 4), (0, 0), (B - 1, 0), (0, C - 4)]
+    while len(picks) < 10:
+        picks.append((int(torch.randint(0, B, (1,), generator=rng)), 4 * int(torch.randint(0, C // 4, (1,), generator=rng))))
+    for b, c0 in picks:
+        _check_slice(w, u, k, v, gy, y, grads, b=b, cs=slice(c0, c0 + 4))
+    cs = slice(382, 384)                      # the last pair of a strip, every sequence
+    sl = [x.double().cpu() for x in (w[cs], u[cs], k[:, :, cs], v[:, :, cs], gy[:, :, cs])]
+    gw_ref, gu_ref, _, _ = BO.biwkv_scan_backward(*sl)
+    assert rel_err(grads[0][cs], gw_ref) <= 1e-4 and rel_err(grads[1][cs], gu_ref) <= 1e-4
 
 
 def test_config1_vrwkv_s_inference_shape(cuda_device):

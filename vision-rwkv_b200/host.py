@@ -80,11 +80,8 @@ def biwkv_forward_backward_host(w, u, k, v, gy, out_y, out_gk, out_gv, out_gwgu,
                 dg.copy_(gy[b0:b0 + nb], non_blocking=True)
                 pool.loaded[s].record(pool.s_in)
             main.wait_event(pool.loaded[s])
-            y, logden = ops.biwkv_forward_save(wd, ud, dk, dv)
-            if logden is None:
-                _, _, gk, gv = ops.biwkv_backward(wd, ud, dk, dv, dg, gwgu_out=pool.part[s])
-            else:
-                _, _, gk, gv = ops.biwkv_backward_saved(wd, ud, dk, dv, dg, y, logden, gwgu_out=pool.part[s])
+            y = ops.biwkv_forward(wd, ud, dk, dv)
+            _, _, gk, gv = ops.biwkv_backward(wd, ud, dk, dv, dg, gwgu_out=pool.part[s])
             pool.gwgu.add_(pool.part[s])
             pool.consumed[s].record(main)
             pool.computed[s].record(main)
@@ -98,7 +95,9 @@ def biwkv_forward_backward_host(w, u, k, v, gy, out_y, out_gk, out_gv, out_gwgu,
                     t.record_stream(pool.s_out)
                 pool.drained[s].record(pool.s_out)
         if reducer is not None:
+            # the collective runs on the reducer's side stream while the last chunks are still leaving
             reducer.launch(pool.gwgu)
-            reducer.wait()
         main.wait_stream(pool.s_out)
+        if reducer is not None:
+            reducer.wait()
         out_gwgu.copy_(pool.gwgu, non_blocking=True)

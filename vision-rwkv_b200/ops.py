@@ -17,17 +17,86 @@ from . import _lib
 # When true, every call synchronises and raises if a bounded device-side wait ran out
 # (the kernels then return garbage instead of hanging).  Off by default: it costs a sync.
 CHECK_STATUS = False
+# Without CHECK_STATUS a failed launch is still reported, one or more calls late and with no
+# synchronisation: after every launch the 4-byte status word is copied to pinned host memory on
+# the same stream, and the next call into this module (or `raise_if_failed()`) raises for every
+# earlier launch whose copy has landed with a non-zero word.
+STATUS_MIRROR = True
+
+
+class _StatusMirror:
+    """Ring of pinned status words for one device, each with the event that marks its copy."""
+    SLOTS = 32
+
+    def __init__(self):
+        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self.events = [torch.cuda.Event() for _ in range(self.SLOTS)]
+        self.names = [None] * self.SLOTS
+        self.head = 0                    # next slot to fill
+        self.tail = 0                    # oldest slot not yet looked at
+        self.failed = []                 # reports not yet raised
+
+    def post(self, ws, what):
+        if self.head - self.tail == self.SLOTS:          # ring full: the oldest copy has long been queued
+            self.collect(wait=True, limit=1)
+        slot = self.head % self.SLOTS
+        self.host[slot:slot + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
+        self.events[slot].record()
+        self.names[slot] = what
+        self.head += 1
+
+    def collect(self, wait=False, limit=None):
+        while self.tail < self.head and (limit is None or limit > 0):
+            slot = self.tail % self.SLOTS
+            if wait:
+                self.events[slot].synchronize()
+            elif not self.events[slot].query():
+                break
+            word = int(self.host[slot])
+            if word:
+                self.failed.append(f"{self.names[slot]}: device status word {word & 0xffffffff:#x}")
+            self.tail += 1
+            if limit is not None:
+                limit -= 1
+
+    def raise_pending(self):
+        if self.failed:
+            failed, self.failed = self.failed, []
+            raise _lib.VrwkvError("; ".join(failed) + " (a bounded device-side wait ran out in an earlier launch: "
+                                  "its outputs, and everything computed from them, are invalid)")
+
+
+_mirrors = {}
+
+
+def raise_if_failed(device=None, wait=True):
+    """Raise VrwkvError if any launch issued through this module on `device` (default: all) reported a
+    timed-out wait.  wait=True synchronises with the status copies still in flight: call it where a
+    step's results are consumed (after the optimizer step, before a checkpoint)."""
+    for index, mirror in list(_mirrors.items()):
+        if device is None or torch.device(device).index in (None, index):
+            mirror.collect(wait=wait)
+            mirror.raise_pending()
 
 
 def _check_status(lib, ws, what):
-    if not CHECK_STATUS:
+    if CHECK_STATUS:
+        word = ctypes.c_uint(0)
+        st = lib.vrwkv_workspace_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream,
+                                        ctypes.byref(word))
+        _lib.check(st, "vrwkv_workspace_status")
+        if word.value:
+            raise _lib.VrwkvError(f"{what}: device status word {word.value:#x} (a bounded wait ran out)")
         return
-    word = ctypes.c_uint(0)
-    st = lib.vrwkv_workspace_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream,
-                                    ctypes.byref(word))
-    _lib.check(st, "vrwkv_workspace_status")
-    if word.value:
-        raise _lib.VrwkvError(f"{what}: device status word {word.value:#x} (a bounded wait ran out)")
+    if not STATUS_MIRROR or torch.cuda.is_current_stream_capturing():
+        return
+    index = ws.device.index
+    mirror = _mirrors.get(index)
+    if mirror is None:
+        mirror = _mirrors[index] = _StatusMirror()
+    mirror.post(ws, what)
+    mirror.collect()                     # earlier launches whose word has landed
+    mirror.raise_pending()
 
 
 UNSUPPORTED = 8      # VRWKV_ERR_UNSUPPORTED: the bf16 kernels do not cover this shape / alignment

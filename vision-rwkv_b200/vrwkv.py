@@ -32,10 +32,12 @@ import torch
 from . import ops
 
 BF16_IO = os.environ.get("VRWKV_BF16_IO", "1") != "0"
-# Keep log Den_t (one float per element) from the forward so that the backward starts from the
-# saved y and log Den instead of recomputing them: one cross-tile exchange instead of two, about
-# 20 % less backward time for B*T*C floats of extra activation memory per call.  Float32 path only.
-SAVE_DENOMINATOR = os.environ.get("VRWKV_SAVE_DENOMINATOR", "1") != "0"
+# Off by default: the forward keeps nothing and the backward rebuilds y and Den inside the
+# cluster-resident kernel, which reads k, v, gy once and is the fastest pair (T <= 4096).  When on,
+# the float32 forward also writes log Den_t (one float per element) and the backward starts from the
+# saved y and log Den: B*T*C floats of extra activation memory per call, served by the older tile
+# kernels; useful only for sequences longer than the resident kernels hold.
+SAVE_DENOMINATOR = os.environ.get("VRWKV_SAVE_DENOMINATOR", "0") != "0"
 
 
 def _result_dtype(w):
