@@ -19,12 +19,17 @@ TOL_BF16 = 1e-2
 TOL_F32 = 1e-5
 
 
-@pytest.fixture(autouse=True)
-def checked_status():
-    from vision_rwkv_b200 import ops
+@pytest.fixture(autouse=True, params=["auto", "tiles"])
+def checked_status(request):
+    """Every test runs twice: through the default kernels (cluster-resident where the shape allows) and with
+    them switched off, which leaves the chunked bfloat16-tile kernels."""
+    from vision_rwkv_b200 import _lib, ops
+    lib = _lib.load()
+    assert lib.vrwkv_set_path({"auto": 0, "tiles": 2}[request.param]) == 0
     ops.CHECK_STATUS = True
     yield
     ops.CHECK_STATUS = False
+    lib.vrwkv_set_path(0)
 
 
 def rounded_inputs(B, T, C, seed, k_scale=1.0):
@@ -33,7 +38,7 @@ def rounded_inputs(B, T, C, seed, k_scale=1.0):
     return w, u, k, v, gy
 
 
-def run_and_check(dev, w, u, k, v, gy):
+def run_and_check(dev, w, u, k, v, gy, sums_tol=None):
     from vision_rwkv_b200 import ops
     y = ops.biwkv_forward(w.to(dev), u.to(dev), k.to(dev), v.to(dev))
     gw, gu, gk, gv = ops.biwkv_backward(w.to(dev), u.to(dev), k.to(dev), v.to(dev), gy.to(dev))
@@ -43,7 +48,8 @@ def run_and_check(dev, w, u, k, v, gy):
     ref_y = O.biwkv_scan_forward(*d[:4])
     ref_gw, ref_gu, ref_gk, ref_gv = O.biwkv_scan_backward(*d)
     C = k.shape[2]
-    sums_tol = 1e-4 if C < 16 else TOL_F32
+    if sums_tol is None:
+        sums_tol = 1e-4 if C < 16 else TOL_F32
     errs = {"y": (rel_err(y.float(), ref_y), TOL_BF16), "gk": (rel_err(gk.float(), ref_gk), TOL_BF16),
             "gv": (rel_err(gv.float(), ref_gv), TOL_BF16)}
     if ref_gw.abs().max() > 0:
@@ -54,7 +60,7 @@ def run_and_check(dev, w, u, k, v, gy):
 
 
 @pytest.mark.parametrize("B,T,C", [(2, 196, 192), (1, 1, 8), (1, 2, 32), (3, 17, 40), (1, 129, 64), (2, 300, 72),
-                                   (1, 1024, 96), (1, 4096, 64)])
+                                   (1, 1024, 96), (1, 4096, 64), (2, 1000, 40), (1, 33, 8), (3, 515, 104), (1, 4095, 32)])
 def test_parity_with_oracle(cuda_device, B, T, C):
     run_and_check(cuda_device, *rounded_inputs(B, T, C, seed=T + C))
 
@@ -62,7 +68,9 @@ def test_parity_with_oracle(cuda_device, B, T, C):
 def test_wide_exponent_range_takes_the_per_token_path(cuda_device):
     """k spread over +-100: the sub-chunk range test fails and the max-shifted per-token code runs,
     reading and writing the bfloat16 tiles through the same accessors."""
-    run_and_check(cuda_device, *rounded_inputs(2, 200, 64, seed=3, k_scale=30.0))
+    # |k| up to 100: the rounding of k log2(e) alone is 6e-6 of a term, so gw, gu get the float32 tests' figure for
+    # wide exponent ranges
+    run_and_check(cuda_device, *rounded_inputs(2, 200, 64, seed=3, k_scale=30.0), sums_tol=5e-5)
 
 
 def test_output_is_the_f32_result_rounded_once(cuda_device):

@@ -78,7 +78,8 @@ def test_agrees_with_the_recomputing_backward_at_scale(cuda_device):
     y, logden = ops.biwkv_forward_save(w, u, k, v)
     a = ops.biwkv_backward_saved(w, u, k, v, gy, y, logden)
     b = ops.biwkv_backward(w, u, k, v, gy)
-    assert torch.equal(y, ops.biwkv_forward(w, u, k, v))
+    # the plain forward runs other kernels (cluster-resident, plain-float arithmetic): same values to float32 accuracy
+    assert rel_err(y, ops.biwkv_forward(w, u, k, v).double().cpu()) <= 2e-6
     for x, r in zip(a, b):
         assert rel_err(x, r.double().cpu()) <= 1e-5
     again = ops.biwkv_backward_saved(w, u, k, v, gy, y, logden)

@@ -40,6 +40,7 @@
 // Recurrence restated: classification/mmcls_custom/models/backbones/cuda_new/
 // bi_wkv_kernel.cu:21-116 (forward), :119-367 (gradients).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <atomic>
@@ -210,6 +211,33 @@ struct Enter {
 
 // x * (hi + lo) + y, both channels
 __device__ __forceinline__ float2 mulc_add(float2 x, float2 hi, float2 lo, float2 y) { return fma2(x, hi, fma2(x, lo, y)); }
+
+// Element access of a thread's sub-chunk in one data slot.  `area` = the sub-chunk's 16 rows of kCs
+// floats (2 KB).  float32 tensors: row i is where it arrived.  bfloat16 tensors: the 16 rows arrive
+// dense (64 bytes each) in the upper half of the area and are widened in place as the first pass over
+// them walks up the rows: writing float row i (bytes 128 i and up) covers bfloat16 rows <= 2 i - 15
+// only, which have been read by then, also when the reads of 4 rows are issued ahead of the writes.
+// Results leave as dense bfloat16 rows at the start of the area: row i lands on float rows <= i / 2,
+// consumed before it.  Both half-warps of a warp run in lockstep over areas of their own.
+constexpr int kHalfRowBytes = kCs * 2;
+constexpr int kHalfAreaBytes = kL * kHalfRowBytes;     // 1 KB: the upper half of the 2 KB area
+template <bool kHalf>
+__device__ __forceinline__ float2 ld_in(const float* area, int i, int pr) {
+    if (kHalf) {
+        const unsigned char* row = reinterpret_cast<const unsigned char*>(area) + kHalfAreaBytes + i * kHalfRowBytes;
+        return __bfloat1622float2(*(reinterpret_cast<const __nv_bfloat162*>(row) + pr));
+    }
+    return *(reinterpret_cast<const float2*>(area + i * kCs) + pr);
+}
+template <bool kHalf>
+__device__ __forceinline__ void st_out(float* area, int i, int pr, float2 v) {
+    if (kHalf) {
+        unsigned char* row = reinterpret_cast<unsigned char*>(area) + i * kHalfRowBytes;
+        *(reinterpret_cast<__nv_bfloat162*>(row) + pr) = __float22bfloat162_rn(v);
+    } else {
+        *(reinterpret_cast<float2*>(area + i * kCs) + pr) = v;
+    }
+}
 
 // One exchange level on plain floats (steps 1-4 of the file header).  F / MF: this thread's sub-chunk
 // aggregate relative to the first token after its 16 tokens (and its first moment in distance), R:
@@ -612,7 +640,8 @@ __device__ __noinline__ void exact_subchunk(const Ctx& c, int sub, int ch, float
 // ---- the kernel -----------------------------------------------------------------------------------
 // kStash: tokens whose leftward state a thread keeps in registers at a time (16: one reverse sweep
 // per sub-chunk; 8: the second half is swept twice, for half the registers).
-template <bool kBwd, int kStash>
+// kHalf: k, v, gy and the outputs are bfloat16 tensors (float32 arithmetic and shared-memory state all the same).
+template <bool kBwd, int kStash, bool kHalf>
 __global__ void __launch_bounds__(kMaxThreads, kBwd ? 2 : 3)
 biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __grid_constant__ CUtensorMap map_g,     // backward: gy
@@ -673,12 +702,25 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         sm100::mbar_init(full + warp, 1);
         if (kBwd) sm100::mbar_init(gfull + warp, 1);
         sm100::mbar_init_fence();
-        sm100::mbar_expect_tx(full + warp, 2 * kSpanBytes);
-        sm100::tma_load_3d(slot_k + warp * kSpan * kCs, &map_k, full + warp, strip * kCs, tok0 + warp * kSpan, b);
-        sm100::tma_load_3d(slot_v + warp * kSpan * kCs, &map_v, full + warp, strip * kCs, tok0 + warp * kSpan, b);
-        if (kBwd) {
-            sm100::mbar_expect_tx(gfull + warp, kSpanBytes);
-            sm100::tma_load_3d(slot_g + warp * kSpan * kCs, &map_g, gfull + warp, strip * kCs, tok0 + warp * kSpan, b);
+        if (kHalf) {
+            // bfloat16: one box per 16-token sub-chunk, into the upper half of the sub-chunk's own area
+            sm100::mbar_expect_tx(full + warp, 4 * kHalfAreaBytes);
+            if (kBwd) sm100::mbar_expect_tx(gfull + warp, 2 * kHalfAreaBytes);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = warp * kSpan + h * kL;
+                sm100::tma_load_3d(reinterpret_cast<unsigned char*>(slot_k + r * kCs) + kHalfAreaBytes, &map_k, full + warp, strip * kCs, tok0 + r, b);
+                sm100::tma_load_3d(reinterpret_cast<unsigned char*>(slot_v + r * kCs) + kHalfAreaBytes, &map_v, full + warp, strip * kCs, tok0 + r, b);
+                if (kBwd) sm100::tma_load_3d(reinterpret_cast<unsigned char*>(slot_g + r * kCs) + kHalfAreaBytes, &map_g, gfull + warp, strip * kCs, tok0 + r, b);
+            }
+        } else {
+            sm100::mbar_expect_tx(full + warp, 2 * kSpanBytes);
+            sm100::tma_load_3d(slot_k + warp * kSpan * kCs, &map_k, full + warp, strip * kCs, tok0 + warp * kSpan, b);
+            sm100::tma_load_3d(slot_v + warp * kSpan * kCs, &map_v, full + warp, strip * kCs, tok0 + warp * kSpan, b);
+            if (kBwd) {
+                sm100::mbar_expect_tx(gfull + warp, kSpanBytes);
+                sm100::tma_load_3d(slot_g + warp * kSpan * kCs, &map_g, gfull + warp, strip * kCs, tok0 + warp * kSpan, b);
+            }
         }
     }
     if (threadIdx.x == 0) {
@@ -732,9 +774,15 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     float2* k2 = reinterpret_cast<float2*>(slot_k + row0 * kCs) + pr;
     float2* v2 = reinterpret_cast<float2*>(slot_v + row0 * kCs) + pr;
     float2* g2 = reinterpret_cast<float2*>(slot_g + row0 * kCs) + pr;
+    float* const area_k = slot_k + row0 * kCs;
+    float* const area_v = slot_v + row0 * kCs;
+    float* const area_g = slot_g + row0 * kCs;
     // rows past T arrive as zeros; a k of -1e30 makes their terms vanish without any masking below
     if (n < kL)
-        for (int i = n; i < kL; ++i) k2[i * kRow] = f2(-1e30f, -1e30f);
+        for (int i = n; i < kL; ++i) {
+            if (kHalf) *(reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<unsigned char*>(area_k) + kHalfAreaBytes + i * kHalfRowBytes) + pr) = __float2bfloat162_rn(-1e30f);
+            else k2[i * kRow] = f2(-1e30f, -1e30f);
+        }
     __syncwarp();
 
     // ---- level 1, pass 1: terms z = lambda e^{k} [v, 1] in place of k, v; sub-chunk aggregates ----
@@ -749,7 +797,8 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int g = 0; g < kL; g += kGroup) {
             float2 kk[kGroup], vv[kGroup];
 #pragma unroll
-            for (int j = 0; j < kGroup; ++j) { kk[j] = k2[(g + j) * kRow]; vv[j] = v2[(g + j) * kRow]; }
+            for (int j = 0; j < kGroup; ++j) { kk[j] = ld_in<kHalf>(area_k, g + j, pr); vv[j] = ld_in<kHalf>(area_v, g + j, pr); }
+            if (kHalf) __syncwarp();      // in-place widening: every lane has read these rows before any lane writes over them
 #pragma unroll
             for (int j = 0; j < kGroup; ++j) {
                 const int i = g + j;
@@ -806,13 +855,14 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 float2 zxs[kGroup], zys[kGroup];
 #pragma unroll
                 for (int j = 0; j < kGroup; ++j) { zxs[j] = k2[(blk * kStash + g + j) * kRow]; zys[j] = v2[(blk * kStash + g + j) * kRow]; }
+                if (kHalf) __syncwarp();
 #pragma unroll
                 for (int j = 0; j < kGroup; ++j) {
                     const int i = blk * kStash + g + j;
                     const float2 zx = zxs[j], zy = zys[j];
                     const float2 nn = fma2(c2, zx, add2(P.n, sn[g + j]));
                     const float2 dd = fma2(c2, zy, add2(P.d, sd[g + j]));
-                    k2[i * kRow] = mul2(nn, f2(rcp(dd.x), rcp(dd.y)));
+                    st_out<kHalf>(area_k, i, pr, mul2(nn, f2(rcp(dd.x), rcp(dd.y))));
                     P.n = fma2(lam2, P.n, zx);
                     P.d = fma2(lam2, P.d, zy);
                 }
@@ -847,8 +897,9 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
                     for (int j = 0; j < kGroupB; ++j) {
                         const int i = blk * kStash + g + j;
-                        zxs[j] = k2[i * kRow]; zys[j] = v2[i * kRow]; gys[j] = g2[i * kRow];
+                        zxs[j] = k2[i * kRow]; zys[j] = v2[i * kRow]; gys[j] = ld_in<kHalf>(area_g, i, pr);
                     }
+                    if (kHalf) __syncwarp();
 #pragma unroll
                     for (int j = 0; j < kGroupB; ++j) {
                         const int i = blk * kStash + g + j;
@@ -913,6 +964,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         const int i = blk * kStash + g + j;
                         zxs[j] = k2[i * kRow]; zys[j] = v2[i * kRow]; gs_[j] = g2[i * kRow];
                     }
+                    if (kHalf) __syncwarp();
 #pragma unroll
                     for (int j = 0; j < kGroupB; ++j) {
                         const int i = blk * kStash + g + j;
@@ -920,8 +972,8 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         const float2 zx = zxs[j], zy = zys[j];
                         const float2 AG = fma2(c2, g_, add2(sn[g + j], Rp.n));
                         const float2 AH = fma2(c2, h, add2(sd[g + j], Rp.d));      // -A^H
-                        v2[i * kRow] = mul2(zy, AG);
-                        k2[i * kRow] = fma2(zx, AG, mul2(zy, AH));
+                        st_out<kHalf>(area_v, i, pr, mul2(zy, AG));
+                        st_out<kHalf>(area_k, i, pr, fma2(zx, AG, mul2(zy, AH)));
                         gwa = fma2(zx, MRp.n, gwa);
                         gwa = fma2(zy, MRp.d, gwa);
                         Rp.n = fma2(lam2, Rp.n, g_);
@@ -943,7 +995,20 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
     sm100::fence_proxy_async_smem();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (kHalf) {
+        // one box per sub-chunk (its 16 dense bfloat16 rows), issued by the warp that wrote them
+        if (lane == 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = warp * kSpan + h * kL;
+                if (tok0 + r < p.T) {
+                    sm100::tma_store_3d(&map_o0, slot_k + r * kCs, strip * kCs, tok0 + r, b);
+                    if (kBwd) sm100::tma_store_3d(&map_o1, slot_v + r * kCs, strip * kCs, tok0 + r, b);
+                }
+            }
+            sm100::tma_store_commit();
+        }
+    } else if (threadIdx.x == 0) {
         sm100::tma_store_3d(&map_o0, slot_k, strip * kCs, tok0, b);
         if (kBwd) sm100::tma_store_3d(&map_o1, slot_v, strip * kCs, tok0, b);
         sm100::tma_store_commit();
@@ -956,7 +1021,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         }
     }
     TL_MARK(8);
-    if (threadIdx.x == 0) sm100::tma_store_wait_read();   // shared memory may go once the stores have read it
+    if (kHalf ? lane == 0 : threadIdx.x == 0) sm100::tma_store_wait_read();   // shared memory may go once the stores have read it
     TL_MARK(9);
 }
 
@@ -964,7 +1029,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 // Runs after the fast kernel with a small persistent grid of clusters and serves the units it left
 // behind (normally none: one load and out).  Same shared-memory layout, same tiles, same work split
 // between the CTAs of a cluster, per-token max-shifted arithmetic.
-template <bool kBwd>
+template <bool kBwd, bool kHalf>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_o0,
@@ -1013,11 +1078,19 @@ biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const int unit = p.redo_list[j];
         const int b = unit / p.n_strips, strip = unit - b * p.n_strips;
         if (threadIdx.x == 0) {
-            sm100::mbar_expect_tx(full, RW::kSlots * slot_bytes);
-            for (int sp = 0; sp < nw; ++sp) {            // the load maps describe one span per box
-                sm100::tma_load_3d(slot_k + sp * kSpan * kCs, &map_k, full, strip * kCs, tok0 + sp * kSpan, b);
-                sm100::tma_load_3d(slot_v + sp * kSpan * kCs, &map_v, full, strip * kCs, tok0 + sp * kSpan, b);
-                if (kBwd) sm100::tma_load_3d(slot_g + sp * kSpan * kCs, &map_g, full, strip * kCs, tok0 + sp * kSpan, b);
+            sm100::mbar_expect_tx(full, RW::kSlots * (kHalf ? slot_bytes / 2 : slot_bytes));
+            if (kHalf) {
+                for (int r = 0; r < nw * kSpan; r += kL) {   // one box per 16-token sub-chunk, into the upper half of its area
+                    sm100::tma_load_3d(reinterpret_cast<unsigned char*>(slot_k + r * kCs) + kHalfAreaBytes, &map_k, full, strip * kCs, tok0 + r, b);
+                    sm100::tma_load_3d(reinterpret_cast<unsigned char*>(slot_v + r * kCs) + kHalfAreaBytes, &map_v, full, strip * kCs, tok0 + r, b);
+                    if (kBwd) sm100::tma_load_3d(reinterpret_cast<unsigned char*>(slot_g + r * kCs) + kHalfAreaBytes, &map_g, full, strip * kCs, tok0 + r, b);
+                }
+            } else {
+                for (int sp = 0; sp < nw; ++sp) {            // the load maps describe one span per box
+                    sm100::tma_load_3d(slot_k + sp * kSpan * kCs, &map_k, full, strip * kCs, tok0 + sp * kSpan, b);
+                    sm100::tma_load_3d(slot_v + sp * kSpan * kCs, &map_v, full, strip * kCs, tok0 + sp * kSpan, b);
+                    if (kBwd) sm100::tma_load_3d(slot_g + sp * kSpan * kCs, &map_g, full, strip * kCs, tok0 + sp * kSpan, b);
+                }
             }
         }
         const int ch0 = strip * kCs + 2 * pr;
@@ -1025,6 +1098,18 @@ biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const float2 u2 = (ch0 < p.C) ? *reinterpret_cast<const float2*>(p.u + ch0) : f2(0.f, 0.f);
         if (!sm100::mbar_wait(full, phase, kSpinLimit)) atomicOr(p.status, 2u);
         phase ^= 1u;
+        if (kHalf) {
+            // widen this thread's 16 rows in place, walking up (see ld_in)
+            for (int i = 0; i < kL; ++i) {
+                const float2 a = ld_in<true>(slot_k + row0 * kCs, i, pr), bb = ld_in<true>(slot_v + row0 * kCs, i, pr);
+                const float2 g_ = kBwd ? ld_in<true>(slot_g + row0 * kCs, i, pr) : f2(0.f, 0.f);
+                __syncwarp();
+                *reinterpret_cast<float2*>(ks + i * kCs) = a;
+                *reinterpret_cast<float2*>(vs + i * kCs) = bb;
+                if (kBwd) *reinterpret_cast<float2*>(gs + i * kCs) = g_;
+                __syncwarp();
+            }
+        }
         float2 gw = f2(0.f, 0.f), gu = f2(0.f, 0.f);
         const int sub = 2 * warp + upper;
         exact_subchunk<kBwd>(c, sub, 2 * pr, ks, vs, gs, n, w2.x, u2.x, gw.x, gu.x);
@@ -1033,9 +1118,32 @@ biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             *reinterpret_cast<float2*>(gs) = gw;
             *reinterpret_cast<float2*>(gs + kCs) = gu;
         }
+        if (kHalf) {
+            // narrow the results in place, walking up: dense bfloat16 rows at the start of the area
+            __syncwarp();
+            for (int i = 0; i < kL; ++i) {
+                const float2 a = *reinterpret_cast<const float2*>(ks + i * kCs);
+                const float2 bb = kBwd ? *reinterpret_cast<const float2*>(vs + i * kCs) : f2(0.f, 0.f);
+                __syncwarp();
+                st_out<true>(slot_k + row0 * kCs, i, pr, a);
+                if (kBwd) st_out<true>(slot_v + row0 * kCs, i, pr, bb);
+                __syncwarp();
+            }
+        }
         sm100::fence_proxy_async_smem();
         __syncthreads();
-        if (threadIdx.x == 0) {
+        if (kHalf) {
+            if (lane == 0) {
+                for (int h = 0; h < 2; ++h) {
+                    const int r = warp * kSpan + h * kL;
+                    if (tok0 + r < p.T) {
+                        sm100::tma_store_3d(&map_o0, slot_k + r * kCs, strip * kCs, tok0 + r, b);
+                        if (kBwd) sm100::tma_store_3d(&map_o1, slot_v + r * kCs, strip * kCs, tok0 + r, b);
+                    }
+                }
+                sm100::tma_store_commit();
+            }
+        } else if (threadIdx.x == 0) {
             sm100::tma_store_3d(&map_o0, slot_k, strip * kCs, tok0, b);
             if (kBwd) sm100::tma_store_3d(&map_o1, slot_v, strip * kCs, tok0, b);
             sm100::tma_store_commit();
@@ -1047,7 +1155,7 @@ biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 p.partial[((static_cast<size_t>(unit) * p.cluster + c.rank) * 2 + jj) * kCs + lane] = acc;
             }
         }
-        if (threadIdx.x == 0) sm100::tma_store_wait_read();
+        if (kHalf ? lane == 0 : threadIdx.x == 0) sm100::tma_store_wait_read();
         __syncthreads();      // the slots are free for the next unit
     }
 }
@@ -1102,18 +1210,22 @@ static bool make_plan(int T, Plan& pl) {
 
 struct DeviceState {
     bool probed = false, ok = false;
-    // [bwd][log2 cluster][n_warps]: 0 unknown, 1 launchable, -1 not
-    signed char fits[2][5][kMaxWarps + 1] = {};
+    // [bfloat16][bwd][log2 cluster][n_warps]: 0 unknown, 1 launchable, -1 not
+    signed char fits[2][2][5][kMaxWarps + 1] = {};
 };
 static std::mutex g_mutex;
 static DeviceState g_dev[64];
 
-template <bool kBwd>
+template <bool kBwd, bool kHalf>
 static const void* kernel_ptr() {
-    return reinterpret_cast<const void*>(biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash>);
+    return reinterpret_cast<const void*>(biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf>);
+}
+template <bool kBwd, bool kHalf>
+static const void* exact_ptr() {
+    return reinterpret_cast<const void*>(biwkv_exact_kernel<kBwd, kHalf>);
 }
 
-template <bool kBwd>
+template <bool kBwd, bool kHalf>
 static bool fits(const Plan& pl) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
@@ -1124,17 +1236,12 @@ static bool fits(const Plan& pl) {
         int cl = 0;
         cudaDeviceGetAttribute(&cl, cudaDevAttrClusterLaunch, dev);
         bool good = cl != 0 && tensor_map::encode_fn() != nullptr;
-        good = good && cudaFuncSetAttribute(kernel_ptr<false>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(smem_bytes<false>(kMaxWarps))) == cudaSuccess;
-        good = good && cudaFuncSetAttribute(kernel_ptr<true>(), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(smem_bytes<true>(kMaxWarps))) == cudaSuccess;
-        good = good && cudaFuncSetAttribute(kernel_ptr<false>(), cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
-        good = good && cudaFuncSetAttribute(kernel_ptr<true>(), cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
-        const void* ex[2] = {reinterpret_cast<const void*>(biwkv_exact_kernel<false>), reinterpret_cast<const void*>(biwkv_exact_kernel<true>)};
-        for (int i = 0; i < 2; ++i) {
-            good = good && cudaFuncSetAttribute(ex[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                static_cast<int>(i ? smem_bytes<true>(kMaxWarps) : smem_bytes<false>(kMaxWarps))) == cudaSuccess;
-            good = good && cudaFuncSetAttribute(ex[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        const void* fn[8] = {kernel_ptr<false, false>(), kernel_ptr<false, true>(), exact_ptr<false, false>(), exact_ptr<false, true>(),
+                             kernel_ptr<true, false>(),  kernel_ptr<true, true>(),  exact_ptr<true, false>(),  exact_ptr<true, true>()};
+        for (int i = 0; i < 8; ++i) {
+            good = good && cudaFuncSetAttribute(fn[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(i >= 4 ? smem_bytes<true>(kMaxWarps) : smem_bytes<false>(kMaxWarps))) == cudaSuccess;
+            good = good && cudaFuncSetAttribute(fn[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         }
         if (!good) cudaGetLastError();
         d.ok = good;
@@ -1142,7 +1249,7 @@ static bool fits(const Plan& pl) {
     if (!d.ok) return false;
     int lg = 0;
     while ((1 << lg) < pl.cluster) ++lg;
-    signed char& slot = d.fits[kBwd ? 1 : 0][lg][pl.n_warps];
+    signed char& slot = d.fits[kHalf ? 1 : 0][kBwd ? 1 : 0][lg][pl.n_warps];
     if (slot == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(pl.cluster);
@@ -1153,22 +1260,23 @@ static bool fits(const Plan& pl) {
         at[0].val.clusterDim.x = pl.cluster; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         int n = 0;
-        const cudaError_t err = cudaOccupancyMaxActiveClusters(&n, kernel_ptr<kBwd>(), &cfg);
+        const cudaError_t err = cudaOccupancyMaxActiveClusters(&n, kernel_ptr<kBwd, kHalf>(), &cfg);
         if (err != cudaSuccess) cudaGetLastError();
         slot = (err == cudaSuccess && n > 0) ? 1 : -1;
     }
     return slot > 0;
 }
 
-bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd) {
-    if (C % 4 != 0) return false;                                  // TMA row pitch must be 16-byte
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd, bool bf16) {
+    if (C % (bf16 ? 8 : 4) != 0) return false;                     // TMA row pitch must be 16-byte
     for (const void* q : ptrs)
         if (reinterpret_cast<uintptr_t>(q) & 15u) return false;    // TMA base alignment
     Plan pl;
     if (!make_plan(T, pl)) return false;
     const long long ctas = static_cast<long long>(B) * ((C + kCs - 1) / kCs) * pl.cluster;
     if (ctas > (1LL << 30)) return false;
-    return bwd ? fits<true>(pl) : fits<false>(pl);
+    if (bf16) return bwd ? fits<true, true>(pl) : fits<false, true>(pl);
+    return bwd ? fits<true, false>(pl) : fits<false, false>(pl);
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -1180,9 +1288,9 @@ size_t workspace_bytes(int B, int T, int C, bool bwd) {
     return 256 + align_up(units * sizeof(int), 256) + (bwd ? align_up(units * pl.cluster * 2 * kCs * sizeof(float), 256) : 0);
 }
 
-template <bool kBwd>
-static int launch(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, const float* gy,
-                  float* o0, float* o1, float* gwgu, void* workspace, cudaStream_t stream) {
+template <bool kBwd, bool kHalf>
+static int launch(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, const void* gy,
+                  void* o0, void* o1, float* gwgu, void* workspace, cudaStream_t stream) {
     Plan pl;
     if (!make_plan(T, pl)) return -1;
     Params p{};
@@ -1200,11 +1308,12 @@ static int launch(int B, int T, int C, const float* w, const float* u, const flo
     p.withhold_rank = g_withhold.load() ? 1 : -1;
     cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
     CUtensorMap mk, mv, mg, m0, m1;
-    // loads: one box per 32-token span; stores: one box per CTA
-    bool ok = tensor_map::make_btc_f32(&mk, k, B, T, C, kCs, kSpan) && tensor_map::make_btc_f32(&mv, v, B, T, C, kCs, kSpan) &&
-              tensor_map::make_btc_f32(&m0, o0, B, T, C, kCs, pl.n_tok);
-    ok = ok && tensor_map::make_btc_f32(&mg, kBwd ? gy : k, B, T, C, kCs, kSpan) &&
-         tensor_map::make_btc_f32(&m1, kBwd ? o1 : o0, B, T, C, kCs, pl.n_tok);
+    // float32: loads one box per 32-token span, stores one box per CTA; bfloat16: one box per 16-token sub-chunk both ways
+    const int box_in = kHalf ? kL : kSpan, box_out = kHalf ? kL : pl.n_tok;
+    bool ok = tensor_map::make_btc(&mk, k, B, T, C, kCs, box_in, kHalf) && tensor_map::make_btc(&mv, v, B, T, C, kCs, box_in, kHalf) &&
+              tensor_map::make_btc(&m0, o0, B, T, C, kCs, box_out, kHalf);
+    ok = ok && tensor_map::make_btc(&mg, kBwd ? gy : k, B, T, C, kCs, box_in, kHalf) &&
+         tensor_map::make_btc(&m1, kBwd ? o1 : o0, B, T, C, kCs, box_out, kHalf);
     if (!ok) {
         set_error_detail("cuTensorMapEncodeTiled rejected a (C, T, B) tensor map");
         return -1;
@@ -1219,14 +1328,14 @@ static int launch(int B, int T, int C, const float* w, const float* u, const flo
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = pl.cluster; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash>, mk, mv, mg, m0, m1, p);
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf>, mk, mv, mg, m0, m1, p);
     if (err != cudaSuccess) {
         set_error_detail(cudaGetErrorName(err));
         return -1;
     }
     // the exact kernel: a few clusters that serve whatever the fast kernel left behind
     cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>(units, 16)) * pl.cluster);
-    const cudaError_t err2 = cudaLaunchKernelEx(&cfg, biwkv_exact_kernel<kBwd>, mk, mv, mg, m0, m1, p);
+    const cudaError_t err2 = cudaLaunchKernelEx(&cfg, biwkv_exact_kernel<kBwd, kHalf>, mk, mv, mg, m0, m1, p);
     if (err2 != cudaSuccess) {
         set_error_detail(cudaGetErrorName(err2));
         return -1;
@@ -1241,12 +1350,22 @@ static int launch(int B, int T, int C, const float* w, const float* u, const flo
 
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
             void* workspace, cudaStream_t stream) {
-    return launch<false>(B, T, C, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
+    return launch<false, false>(B, T, C, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
 }
 
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, const float* gy,
              float* gwgu, float* gk, float* gv, void* workspace, cudaStream_t stream) {
-    return launch<true>(B, T, C, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+    return launch<true, false>(B, T, C, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+}
+
+int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
+                 void* workspace, cudaStream_t stream) {
+    return launch<false, true>(B, T, C, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
+}
+
+int backward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, const void* gy,
+                  float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream) {
+    return launch<true, true>(B, T, C, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
 }
 
 }  // namespace resident

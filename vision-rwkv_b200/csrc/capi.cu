@@ -162,6 +162,8 @@ int vrwkv_biwkv_forward_bf16(int B, int T, int C, const float* w, const float* u
     if (!w || !u || !k || !v || !y || !workspace) return VRWKV_ERR_NULL;
     if (misaligned4(w) || misaligned4(u) || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_forward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, y}, false, true))
+        return finish(biwkv::resident::forward_bf16(B, T, C, w, u, k, v, y, workspace, static_cast<cudaStream_t>(stream)));
     if (!biwkv::fused::eligible(B, T, C, {k, v, y}, true)) return VRWKV_ERR_UNSUPPORTED;
     return finish(biwkv::fused::forward_bf16(B, T, C, w, u, k, v, y, workspace, static_cast<cudaStream_t>(stream)));
 }
@@ -174,6 +176,9 @@ int vrwkv_biwkv_backward_bf16(int B, int T, int C, const float* w, const float* 
     if (misaligned4(w) || misaligned4(u) || misaligned4(gwgu) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_backward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, gy, gk, gv}, true, true))
+        return finish(biwkv::resident::backward_bf16(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace,
+                                                     static_cast<cudaStream_t>(stream)));
     if (!biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}, true)) return VRWKV_ERR_UNSUPPORTED;
     return finish(biwkv::fused::backward_bf16(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace,
                                               static_cast<cudaStream_t>(stream)));

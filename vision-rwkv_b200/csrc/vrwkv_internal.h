@@ -19,9 +19,9 @@ int generic_backward(int B, int T, int C, const float* w, const float* u, const 
                      const float* v, const float* gy, float* gwgu, float* gk, float* gv,
                      void* workspace, cudaStream_t stream);
 namespace resident {
-// Cluster-resident single-pass path (biwkv_resident.cu): float32, C % 4 == 0, 16-byte aligned
-// tensors, T <= 4096.  True when it can serve this call on the current device.
-bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd);
+// Cluster-resident single-pass path (biwkv_resident.cu): float32 (C % 4 == 0) or bfloat16 (C % 8 == 0)
+// tensors, 16-byte aligned, T <= 4096.  True when it can serve this call on the current device.
+bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd, bool bf16 = false);
 void set_withhold_test(bool on);   // test only: one rank per cluster sends nothing, waits give up early
 size_t workspace_bytes(int B, int T, int C, bool bwd);
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
@@ -29,6 +29,11 @@ int forward(int B, int T, int C, const float* w, const float* u, const float* k,
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
              const float* gy, float* gwgu, float* gk, float* gv, void* workspace,
              cudaStream_t stream);
+// k, v, y, gy, gk, gv hold bfloat16; w, u, gwgu stay float; arithmetic and shared-memory state are the float kernels'.
+int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
+                 void* workspace, cudaStream_t stream);
+int backward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v,
+                  const void* gy, float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream);
 }  // namespace resident
 namespace fused {
 // True when the fused TMA path can serve this call on the current device.
