@@ -60,7 +60,7 @@ def run_and_check(dev, w, u, k, v, gy, sums_tol=None):
 
 
 @pytest.mark.parametrize("B,T,C", [(2, 196, 192), (1, 1, 8), (1, 2, 32), (3, 17, 40), (1, 129, 64), (2, 300, 72),
-                                   (1, 1024, 96), (1, 4096, 64), (2, 1000, 40), (1, 33, 8), (3, 515, 104), (1, 4095, 32)])
+                                   (1, 1024, 96), (1, 4096, 64), (2, 1000, 40), (1, 33, 8), (3, 515, 104), (1, 4095, 32), (1, 4100, 32), (2, 9000, 64)])
 def test_parity_with_oracle(cuda_device, B, T, C):
     run_and_check(cuda_device, *rounded_inputs(B, T, C, seed=T + C))
 

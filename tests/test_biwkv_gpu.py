@@ -153,6 +153,34 @@ def test_fused_path_is_taken_when_eligible(cuda_device, kernel_path):
     assert launch_count() - n0 == 3
 
 
+@pytest.mark.parametrize("B,T,C", [(1, 4097, 32), (2, 5000, 64), (1, 8192, 32), (1, 12289, 40), (1, 16384, 32), (1, 32768, 32)])
+def test_sequences_of_several_segments(cuda_device, kernel_path, B, T, C):
+    """T > 4096: several clusters per (sequence, strip) in the default kernels, handing their aggregates to one
+    another through global memory; launches: forward 1 + the stand-by chunked forward, backward 1 + reduction +
+    the stand-by chunked backward and its reduction (which return at once for inputs inside the plain-float range)."""
+    from vision_rwkv_b200 import launch_count, ops
+    if kernel_path == "generic" and T > 16384:
+        pytest.skip("the generic kernels (channel counts TMA cannot describe) multiply a rounded decay token by token: "
+                    "their gw drifts to 2e-4 at 32768 tokens")
+    w, u, k, v, gy = O.make_inputs(B, T, C, seed=T)
+    n0 = launch_count()
+    # (the older kernel families, run here for comparison, carry gw over long sequences a little less accurately)
+    check(cuda_device, w, u, k, v, gy, tol=5e-5 if kernel_path != "auto" else 2e-5 if T > 8192 else TOL)
+    if kernel_path == "auto":
+        assert launch_count() - n0 == 2 + 4
+
+
+def test_several_segments_outside_the_plain_float_range(cuda_device, kernel_path):
+    """T > 4096 with |k| up to 100 and with strongly growing weights (w < 0): the resident launch declines
+    and the stand-by chunked kernels produce the result."""
+    if kernel_path == "generic":
+        pytest.skip("covers the hand-over from the resident launch to the chunked kernels; the generic kernels' gw "
+                    "drifts to 1e-4 over 6000 tokens of growing weights")
+    w, u, k, v, gy = O.make_inputs(1, 6000, 32, seed=8)
+    check(cuda_device, w, u, k * 30.0, v, gy, tol=5e-5)
+    check(cuda_device, -w.abs() * 50.0, u, k, v, gy, tol=5e-5)
+
+
 def test_bitwise_reproducible(cuda_device):
     args = O.make_inputs(4, 300, 40, seed=3)
     a = run_gpu(cuda_device, *args)

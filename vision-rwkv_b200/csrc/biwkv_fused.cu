@@ -100,7 +100,11 @@ struct Params {
     unsigned* flags;   // [n_tiles][levels], zero before launch, 2 when both halves are written
     unsigned* status;  // device status word
     float* partial;    // backward: [n_tiles][2][kCs]
+    const unsigned* run_if;   // when set: every kernel of the launch returns at once while this word is zero
 };
+__device__ __forceinline__ bool switched_off(const Params& p) {
+    return p.run_if != nullptr && *reinterpret_cast<const volatile unsigned*>(p.run_if) == 0u;
+}
 
 struct TileCoord {
     int b, strip, chunk;
@@ -496,6 +500,7 @@ biwkv_fused_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     constexpr bool kHalf = !std::is_same<E, float>::value;
     constexpr uint32_t kStageBytes = kSlots * kSlotBytes<E>;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
+    if (switched_off(p)) return;
     unsigned char* stage_base = smem_raw;                                           // [2][kSlots][kTc][kCs] of E
     // bfloat16 tiles: the scaled output gradients of the tile in flight stay in fp32 in a region of their own
     float* gscratch = reinterpret_cast<float*>(stage_base + 2 * kStageBytes);       // [kTc][kCs], kBwd && kHalf only
@@ -743,6 +748,7 @@ biwkv_forward_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                                const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_l,
                                const Params p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
+    if (switched_off(p)) return;
     constexpr uint32_t kStageBytes = 2 * kSlotBytes<E>;
     unsigned char* stage_base = smem_raw;                                           // [3][2][kTc][kCs] of E
     float* sub = reinterpret_cast<float*>(stage_base + kFwdStages * kStageBytes);   // [kWarps][kRows][kCs]
@@ -1280,6 +1286,7 @@ reduce_tile_partials(Params p, float* __restrict__ out) {
     __shared__ float red[32][33];
     const int strip = blockIdx.x, j = blockIdx.y, lane = threadIdx.x;
     const int c = strip * kCs + lane;
+    if (switched_off(p)) return;
     const int rows = p.B * p.n_chunks;
     float acc = 0.f;
     for (int r = threadIdx.y; r < rows; r += 32) {
@@ -1405,8 +1412,9 @@ size_t workspace_bytes(int B, int T, int C, bool bwd) { return make_layout(B, T,
 
 template <bool kBwd, typename E>
 static int launch(Layout& l, const float* w, const float* u, const E* k, const E* v, const E* gy, E* o0, E* o1,
-                  float* gwgu, void* workspace, cudaStream_t stream) {
+                  float* gwgu, void* workspace, cudaStream_t stream, const unsigned* run_if = nullptr) {
     Params& p = l.p;
+    p.run_if = run_if;
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     p.w = w; p.u = u;
     p.status = reinterpret_cast<unsigned*>(ws + l.off_status);
@@ -1463,15 +1471,16 @@ static int launch(Layout& l, const float* w, const float* u, const E* k, const E
 }
 
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
-            void* workspace, cudaStream_t stream) {
+            void* workspace, cudaStream_t stream, const unsigned* run_if) {
     Layout l = make_layout(B, T, C, false);
-    return launch<false, float>(l, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream);
+    return launch<false, float>(l, w, u, k, v, nullptr, y, nullptr, nullptr, workspace, stream, run_if);
 }
 
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
-             const float* gy, float* gwgu, float* gk, float* gv, void* workspace, cudaStream_t stream) {
+             const float* gy, float* gwgu, float* gk, float* gv, void* workspace, cudaStream_t stream,
+             const unsigned* run_if) {
     Layout l = make_layout(B, T, C, true);
-    return launch<true, float>(l, w, u, k, v, gy, gk, gv, gwgu, workspace, stream);
+    return launch<true, float>(l, w, u, k, v, gy, gk, gv, gwgu, workspace, stream, run_if);
 }
 
 static constexpr size_t saved_smem_bytes() {
@@ -1549,19 +1558,19 @@ int forward_save(int B, int T, int C, const float* w, const float* u, const floa
 }
 
 int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
-                 void* workspace, cudaStream_t stream) {
+                 void* workspace, cudaStream_t stream, const unsigned* run_if) {
     using E = __nv_bfloat16;
     Layout l = make_layout(B, T, C, false);
     return launch<false, E>(l, w, u, static_cast<const E*>(k), static_cast<const E*>(v), nullptr, static_cast<E*>(y),
-                            nullptr, nullptr, workspace, stream);
+                            nullptr, nullptr, workspace, stream, run_if);
 }
 
 int backward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, const void* gy,
-                  float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream) {
+                  float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream, const unsigned* run_if) {
     using E = __nv_bfloat16;
     Layout l = make_layout(B, T, C, true);
     return launch<true, E>(l, w, u, static_cast<const E*>(k), static_cast<const E*>(v), static_cast<const E*>(gy),
-                           static_cast<E*>(gk), static_cast<E*>(gv), gwgu, workspace, stream);
+                           static_cast<E*>(gk), static_cast<E*>(gv), gwgu, workspace, stream, run_if);
 }
 
 }  // namespace fused

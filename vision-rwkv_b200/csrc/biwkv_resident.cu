@@ -100,7 +100,14 @@ struct Params {
     int* redo_list;         // ... and which
     uint32_t spin_limit;  // polls before a wait for the other CTAs gives up
     int withhold_rank;    // test only: this rank of every cluster sends nothing (-1: none)
+    // sequences longer than one cluster holds: `segs` clusters per (sequence, strip), each with
+    // cluster * n_tok tokens, which hand their aggregates to one another through global memory
+    int segs;
+    float* xseg;          // [unit][seg][level][direction][kSegRec]
+    unsigned* xflag;      // same index; zero before launch, 1 (| 2: out of range) once the record is there
 };
+constexpr int kSegRec = 4 * kCs;      // floats per record (forward: 2 rows used)
+constexpr int kMaxSegs = 8;
 
 // shared memory: data slots | span records | blocks received from the other CTAs | this CTA's two
 // outgoing blocks | state entering this CTA | constants | mbarriers and the flag word
@@ -199,6 +206,9 @@ struct Ctx {
     uint32_t spin_limit;
     bool withhold;   // test only: this CTA sends nothing to the others
     int warp, lane, n_warps, n_tok, cluster, rank;
+    int seg, segs, unit;     // this cluster's segment of the sequence
+    float* xseg;
+    unsigned* xflag;
 };
 
 // a thread's two channels: numerators (n) and denominators (d) of a state, each packed (ch 2p, ch 2p+1)
@@ -239,11 +249,131 @@ __device__ __forceinline__ void st_out(float* area, int i, int pr, float2 v) {
     }
 }
 
+// ---- sequences of several segments ---------------------------------------------------------------
+// Each cluster first completes its own exchange, then its last rank publishes the segment's aggregate
+// towards later tokens and its rank 0 the one towards earlier tokens (record, fence, release of a flag
+// word), and only then do its CTAs wait (bounded) for the records of the other segments of the same
+// (sequence, strip): whoever waits has already published, and clusters are dispatched in index
+// order with a unit's segments adjacent, so the records a resident cluster waits for belong to
+// clusters that are resident too or next in line.  Decay factors over whole segments are formed in
+// double precision from the CTA's (high, low) pair for one CTA's tokens.
+__device__ __forceinline__ size_t seg_index(const Ctx& c, int seg, int level, int dir) {
+    return ((static_cast<size_t>(c.unit) * c.segs + seg) * 2 + level) * 2 + dir;
+}
+struct HiLo {
+    float2 hi, lo;
+};
+// lambda^(n_tok * blocks) from the CTA's (high, low) pair for lambda^n_tok, by squaring in double precision
+__device__ __forceinline__ HiLo decay_over_blocks(const Ctx& c, int blocks) {
+    double base = static_cast<double>(c.consts[kLamC_hi * kCs + c.lane]) + static_cast<double>(c.consts[kLamC_lo * kCs + c.lane]);
+    double x = 1.0;
+    for (int e = blocks; e > 0; e >>= 1) {
+        if (e & 1) x *= base;
+        base *= base;
+    }
+    const float hi = static_cast<float>(x);
+    return HiLo{dup(hi), dup(static_cast<float>(x - static_cast<double>(hi)))};
+}
+// waits for `count` flags starting at segment `first` (lane j takes segment first + j); returns the OR of their values
+__device__ __forceinline__ unsigned seg_wait(const Ctx& c, int first, int count, int level, int dir) {
+    unsigned seen = 1u;
+    if (c.lane < count) {
+        const unsigned* f = c.xflag + seg_index(c, first + c.lane, level, dir);
+        seen = 0u;
+        for (uint32_t it = 0; it < c.spin_limit; ++it) {
+            seen = sm100::flag_relaxed(f);
+            if (seen) break;
+            __nanosleep(32);
+        }
+        if (seen) seen = sm100::flag_acquire(f);
+    }
+    if (!__all_sync(0xffffffffu, seen != 0u) && c.lane == 0) atomicOr(c.status, 4u);
+    unsigned bits = seen;
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) bits |= __shfl_xor_sync(0xffffffffu, bits, m);
+    return bits;
+}
+// Towards later tokens.  In: X, MX = state entering this CTA from the lower ranks of its own cluster; P, M =
+// the CTA's own aggregate.  Out: X, MX also hold everything from the earlier segments; flag |= theirs.
+template <bool kMom>
+__device__ __noinline__ void seg_exchange_forward(const Ctx& c, int level, float2& X, float2& MX, float2 P, float2 M, int& flag) {
+    const int lane = c.lane;
+    const int seg_tok = c.cluster * c.n_tok;
+    if (c.rank == c.cluster - 1 && c.seg + 1 < c.segs) {
+        const float2 hi = dup(c.consts[kLamC_hi * kCs + lane]), lo = dup(c.consts[kLamC_lo * kCs + lane]);
+        const float2 F = mulc_add(X, hi, lo, P);
+        float* rec = c.xseg + seg_index(c, c.seg, level, 0) * kSegRec;
+        rec[lane] = F.x; rec[kCs + lane] = F.y;
+        if (kMom) {
+            const float2 MF = mulc_add(fma2(dup(static_cast<float>(c.n_tok)), X, MX), hi, lo, M);
+            rec[2 * kCs + lane] = MF.x; rec[3 * kCs + lane] = MF.y;
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) sm100::flag_release(c.xflag + seg_index(c, c.seg, level, 0), 1u | (flag ? 2u : 0u));
+    }
+    if (c.seg > 0) {
+        const unsigned bits = seg_wait(c, 0, c.seg, level, 0);
+        if (bits & 2u) flag = 1;
+        const HiLo ls = decay_over_blocks(c, c.cluster);
+        const float2 len = dup(static_cast<float>(seg_tok));
+        float2 A = f2(0.f, 0.f), MA = f2(0.f, 0.f);
+        for (int q = 0; q < c.seg; ++q) {
+            const float* rec = c.xseg + seg_index(c, q, level, 0) * kSegRec;
+            const float2 f = f2(__ldcg(rec + lane), __ldcg(rec + kCs + lane));
+            if (kMom) {
+                const float2 mf = f2(__ldcg(rec + 2 * kCs + lane), __ldcg(rec + 3 * kCs + lane));
+                MA = mulc_add(fma2(len, A, MA), ls.hi, ls.lo, mf);
+            }
+            A = mulc_add(A, ls.hi, ls.lo, f);
+        }
+        // across the lower ranks of this cluster
+        const int d = c.rank * c.n_tok;
+        const HiLo ld = decay_over_blocks(c, c.rank);
+        if (kMom) MX = mulc_add(fma2(dup(static_cast<float>(d)), A, MA), ld.hi, ld.lo, MX);
+        X = mulc_add(A, ld.hi, ld.lo, X);
+    }
+}
+// Towards earlier tokens: Y = state entering this CTA from the higher ranks, S = the CTA's own aggregate.
+__device__ __noinline__ void seg_exchange_reverse(const Ctx& c, int level, float2& Y, float2 S, int& flag) {
+    const int lane = c.lane;
+    if (c.rank == 0 && c.seg > 0) {
+        const float2 hi = dup(c.consts[kLamC_hi * kCs + lane]), lo = dup(c.consts[kLamC_lo * kCs + lane]);
+        const float2 R = mulc_add(Y, hi, lo, S);
+        float* rec = c.xseg + seg_index(c, c.seg, level, 1) * kSegRec;
+        rec[lane] = R.x; rec[kCs + lane] = R.y;
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) sm100::flag_release(c.xflag + seg_index(c, c.seg, level, 1), 1u | (flag ? 2u : 0u));
+    }
+    if (c.seg + 1 < c.segs) {
+        const unsigned bits = seg_wait(c, c.seg + 1, c.segs - 1 - c.seg, level, 1);
+        if (bits & 2u) flag = 1;
+        const HiLo ls = decay_over_blocks(c, c.cluster);
+        float2 A = f2(0.f, 0.f);
+        for (int q = c.segs - 1; q > c.seg; --q) {
+            const float* rec = c.xseg + seg_index(c, q, level, 1) * kSegRec;
+            A = mulc_add(A, ls.hi, ls.lo, f2(__ldcg(rec + lane), __ldcg(rec + kCs + lane)));
+        }
+        const HiLo ld = decay_over_blocks(c, c.cluster - 1 - c.rank);
+        Y = mulc_add(A, ld.hi, ld.lo, Y);
+    }
+}
+// OR of this CTA's and the other CTAs' out-of-range flags (level 0), from the flag words of the blocks they sent
+template <bool kBwd>
+__device__ __forceinline__ int cluster_flag(const Ctx& c, int any) {
+    using RW = Rows<kBwd>;
+    const int lane = c.lane;
+    const int other = (lane < c.cluster && lane != c.rank)
+                          ? __float_as_int(c.peers[(lane - (lane > c.rank ? 1 : 0)) * RW::kBlockF + kCs * (lane < c.rank ? RW::kF : RW::kR)]) : 0;
+    return __any_sync(0xffffffffu, (other | any) != 0) ? 1 : 0;
+}
+
 // One exchange level on plain floats (steps 1-4 of the file header).  F / MF: this thread's sub-chunk
 // aggregate relative to the first token after its 16 tokens (and its first moment in distance), R:
 // relative to the last token before them.  Returns with `unsafe` = OR over the cluster of `unsafe`
 // (level 0 only).
-template <bool kBwd>
+template <bool kBwd, bool kMulti>
 __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F, Pair2 MF, Pair2 R, bool& unsafe TL_ARGS) {
     using RW = Rows<kBwd>;
     constexpr bool kMom = kBwd;
@@ -276,6 +406,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
         }
     }
     const int any = __syncthreads_or(unsafe ? 1 : 0);
+    float2 ctaP = f2(0.f, 0.f), ctaM = f2(0.f, 0.f), ctaS = f2(0.f, 0.f);     // the CTA's own aggregates (scan warps)
     TL_MARK(12 + level * 5);
     // (2) serial walk over the spans, one warp per direction, lane = channel, state = (a, b)
     const int scanF = 0, scanR = nw > 1 ? 1 : 0;
@@ -309,6 +440,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
             }
         }
         if (level == 1) TL_MARK(23);
+        if (kMulti) { ctaP = P; ctaM = M; }
         // the CTA's aggregate (and its flag) for the higher ranks: into the outgoing block
         float* st = c.stage;
         if (kMom) *reinterpret_cast<float4*>(st + lane * 4) = make_float4(P.x, P.y, M.x, M.y);
@@ -335,6 +467,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
                 S = mulc_add(S, hi2, lo2, r[s]);
             }
         }
+        if (kMulti) ctaS = S;
         float* st = c.stage + RW::kBlockF;
         *reinterpret_cast<float2*>(st + lane * 2) = S;
         if (lane == 0) st[kCs * RW::kR] = __int_as_float(any);
@@ -399,15 +532,12 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
                     }
                 }
             }
-            if (level == 0) {
-                const int other = (lane < c.cluster && lane != c.rank)
-                                      ? __float_as_int(c.peers[(lane - (lane > c.rank ? 1 : 0)) * RW::kBlockF + kCs * (lane < c.rank ? RW::kF : RW::kR)]) : 0;
-                flag = __any_sync(0xffffffffu, (other | any) != 0) ? 1 : 0;
-            }
+            if (level == 0) flag = cluster_flag<kBwd>(c, any);
         }
+        if (kMulti) seg_exchange_forward<kMom>(c, level, X, MX, ctaP, ctaM, flag);
         c.cta[lane] = X.x; c.cta[kCs + lane] = X.y;
         if (kMom) { c.cta[2 * kCs + lane] = MX.x; c.cta[3 * kCs + lane] = MX.y; }
-        if (lane == 0) *c.flag = static_cast<unsigned>(flag);
+        if (lane == 0) c.flag[0] = static_cast<unsigned>(flag);
     }
     if (warp == scanR) {
         float2 Y = f2(0.f, 0.f);
@@ -424,6 +554,12 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
                 for (int j = 0; j < kBatch; ++j)
                     if (r0 - j > c.rank) Y = mulc_add(Y, hi2, lo2, f[j]);
             }
+        }
+        if (kMulti) {
+            int flag = 0;
+            if (level == 0) flag = c.cluster > 1 ? cluster_flag<kBwd>(c, any) : any;
+            seg_exchange_reverse(c, level, Y, ctaS, flag);
+            if (lane == 0) c.flag[1] = static_cast<unsigned>(flag);
         }
         c.cta[RW::kF * kCs + lane] = Y.x; c.cta[(RW::kF + 1) * kCs + lane] = Y.y;
     }
@@ -458,7 +594,7 @@ __device__ __forceinline__ Enter fast_exchange(const Ctx& c, int level, Pair2 F,
             e.MP = MPw;
             e.S = Pair2{mulc_add(Sw.n, l16h, l16l, keepA.n), mulc_add(Sw.d, l16h, l16l, keepA.d)};
         }
-        if (level == 0) unsafe = *c.flag != 0u;
+        if (level == 0) unsafe = kMulti ? (c.flag[0] | c.flag[1]) != 0u : c.flag[0] != 0u;
     }
     return e;
 }
@@ -641,7 +777,9 @@ __device__ __noinline__ void exact_subchunk(const Ctx& c, int sub, int ch, float
 // kStash: tokens whose leftward state a thread keeps in registers at a time (16: one reverse sweep
 // per sub-chunk; 8: the second half is swept twice, for half the registers).
 // kHalf: k, v, gy and the outputs are bfloat16 tensors (float32 arithmetic and shared-memory state all the same).
-template <bool kBwd, int kStash, bool kHalf>
+// kMulti: several clusters per sequence (T above what one cluster holds); compiled apart so that the
+// single-cluster kernels carry none of it.
+template <bool kBwd, int kStash, bool kHalf, bool kMulti>
 __global__ void __launch_bounds__(kMaxThreads, kBwd ? 2 : 3)
 biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __grid_constant__ CUtensorMap map_g,     // backward: gy
@@ -690,10 +828,13 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
 #endif
     TL_MARK(0);
-    const int unit = static_cast<int>(blockIdx.x) / p.cluster;
+    const int cl = static_cast<int>(blockIdx.x) / p.cluster;      // segments of a unit are neighbours in launch order
+    const int unit = kMulti ? cl / p.segs : cl, seg = kMulti ? cl - unit * p.segs : 0;
     const int b = unit / p.n_strips, strip = unit - b * p.n_strips;
-    const int tok0 = c.rank * p.n_tok;
+    const int tok0 = (seg * p.cluster + c.rank) * p.n_tok;
     const uint32_t slot_bytes = static_cast<uint32_t>(slot_floats) * 4u;
+    c.seg = seg; c.segs = kMulti ? p.segs : 1; c.unit = unit;
+    c.xseg = p.xseg; c.xflag = p.xflag;
 
     if (lane == 0) {
         // every warp fetches its own span: one box per tensor, k and v on one barrier, gy on another;
@@ -825,7 +966,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     bool unsafe = (2.f * kmax.x + fabsf(u2.x) + fabsf(w2.x) + fmaxf(-w2.x, 0.f) * Tf > kSafeRange) ||
                   (2.f * kmax.y + fabsf(u2.y) + fabsf(w2.y) + fmaxf(-w2.y, 0.f) * Tf > kSafeRange);
     TL_MARK(3);
-    const Enter e1 = fast_exchange<kBwd>(c, 0, F, MF, R, unsafe TL_PASS);
+    const Enter e1 = fast_exchange<kBwd, kMulti>(c, 0, F, MF, R, unsafe TL_PASS);
     TL_MARK(4);
 
     float2 gw = f2(0.f, 0.f), gu = f2(0.f, 0.f);
@@ -834,7 +975,12 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         // the whole cluster takes this branch together: the unit is left to the exact kernel, which
         // runs right after this one (nothing of this CTA is in flight any more: its tiles have
         // landed and everything the other CTAs sent has been waited for)
-        if (c.rank == 0 && threadIdx.x == 0) p.redo_list[atomicAdd(p.redo_count, 1u)] = unit;
+        // (a sequence of several segments is not the exact kernel's to redo: the count alone tells the
+        // launch's last stage to run the chunked kernels over the whole call)
+        if (c.rank == 0 && seg == 0 && threadIdx.x == 0) {
+            const unsigned at = atomicAdd(p.redo_count, 1u);
+            if (!kMulti) p.redo_list[at] = unit;
+        }
         return;
     }
     if (!kBwd) {
@@ -938,7 +1084,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         bool ignored = false;
         TL_MARK(5);
         if (p.cluster > 1) cluster_wait();
-        const Enter e2 = fast_exchange<kBwd>(c, 1, rr, mr, q, ignored TL_PASS);
+        const Enter e2 = fast_exchange<kBwd, kMulti>(c, 1, rr, mr, q, ignored TL_PASS);
         TL_MARK(6);
         // ---- backward, pass 3: gk, gv in place of the terms; gw from pairs (output earlier than input).
         //      Adjoint states are kept divided by lambda, so that [G, -H] enter without a multiply. ----
@@ -1008,7 +1154,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             }
             sm100::tma_store_commit();
         }
-    } else if (threadIdx.x == 0) {
+    } else if (threadIdx.x == 0 && (!kMulti || tok0 < p.T)) {
         sm100::tma_store_3d(&map_o0, slot_k, strip * kCs, tok0, b);
         if (kBwd) sm100::tma_store_3d(&map_o1, slot_v, strip * kCs, tok0, b);
         sm100::tma_store_commit();
@@ -1055,6 +1201,7 @@ biwkv_exact_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     c.status = p.status;
     c.spin_limit = kSpinLimit;
     c.withhold = false;
+    c.seg = 0; c.segs = 1; c.unit = 0; c.xseg = nullptr; c.xflag = nullptr;
     c.warp = warp; c.lane = lane; c.n_warps = nw; c.n_tok = p.n_tok; c.cluster = p.cluster;
     c.rank = p.cluster > 1 ? static_cast<int>(cluster_rank()) : 0;
 
@@ -1166,11 +1313,13 @@ reduce_partials(Params p, float* __restrict__ out) {
     __shared__ float red[32][33];
     const int strip = blockIdx.x, j = blockIdx.y, lane = threadIdx.x;
     const int ch = strip * kCs + lane;
-    const int rows = p.B * p.cluster;
+    if (p.segs > 1 && *p.redo_count != 0u) return;       // the chunked kernels redo the whole call and write gw, gu
+    const int per_unit = p.cluster * p.segs;
+    const int rows = p.B * per_unit;
     float acc = 0.f;
     for (int r = threadIdx.y; r < rows; r += 32) {
-        const int b = r / p.cluster, rank = r - b * p.cluster;
-        const size_t cta = (static_cast<size_t>(b) * p.n_strips + strip) * p.cluster + rank;
+        const int b = r / per_unit, rank = r - b * per_unit;
+        const size_t cta = (static_cast<size_t>(b) * p.n_strips + strip) * per_unit + rank;
         acc += p.partial[(cta * 2 + j) * kCs + lane];
     }
     red[threadIdx.y][lane] = acc;
@@ -1193,10 +1342,23 @@ static std::atomic<bool> g_withhold{false};
 void set_withhold_test(bool on) { g_withhold.store(on); }
 
 struct Plan {
-    int cluster = 0, n_warps = 0, n_tok = 0;
+    int cluster = 0, n_warps = 0, n_tok = 0, segs = 1;
 };
 
 static bool make_plan(int T, Plan& pl) {
+    constexpr int kSegMax = kMaxCluster * kMaxWarps * kSpan;      // tokens one cluster holds
+    if (T > kSegMax) {
+        // several clusters per sequence, tokens spread evenly over them
+        const int segs = (T + kSegMax - 1) / kSegMax;
+        if (segs > kMaxSegs) return false;
+        const int per = (T + segs * kMaxCluster - 1) / (segs * kMaxCluster);
+        pl.segs = segs;
+        pl.cluster = kMaxCluster;
+        pl.n_warps = (per + kSpan - 1) / kSpan;
+        pl.n_tok = pl.n_warps * kSpan;
+        return true;
+    }
+    pl.segs = 1;
     int cluster = 1;
     while ((T + cluster - 1) / cluster > kMaxWarps * kSpan && cluster < kMaxCluster) cluster *= 2;
     const int per = (T + cluster - 1) / cluster;
@@ -1210,15 +1372,15 @@ static bool make_plan(int T, Plan& pl) {
 
 struct DeviceState {
     bool probed = false, ok = false;
-    // [bfloat16][bwd][log2 cluster][n_warps]: 0 unknown, 1 launchable, -1 not
-    signed char fits[2][2][5][kMaxWarps + 1] = {};
+    // [segments > 1][bfloat16][bwd][log2 cluster][n_warps]: 0 unknown, 1 launchable, -1 not
+    signed char fits[2][2][2][5][kMaxWarps + 1] = {};   // first index: several segments per sequence
 };
 static std::mutex g_mutex;
 static DeviceState g_dev[64];
 
-template <bool kBwd, bool kHalf>
+template <bool kBwd, bool kHalf, bool kMulti = false>
 static const void* kernel_ptr() {
-    return reinterpret_cast<const void*>(biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf>);
+    return reinterpret_cast<const void*>(biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf, kMulti>);
 }
 template <bool kBwd, bool kHalf>
 static const void* exact_ptr() {
@@ -1236,11 +1398,13 @@ static bool fits(const Plan& pl) {
         int cl = 0;
         cudaDeviceGetAttribute(&cl, cudaDevAttrClusterLaunch, dev);
         bool good = cl != 0 && tensor_map::encode_fn() != nullptr;
-        const void* fn[8] = {kernel_ptr<false, false>(), kernel_ptr<false, true>(), exact_ptr<false, false>(), exact_ptr<false, true>(),
-                             kernel_ptr<true, false>(),  kernel_ptr<true, true>(),  exact_ptr<true, false>(),  exact_ptr<true, true>()};
-        for (int i = 0; i < 8; ++i) {
+        const void* fn[12] = {kernel_ptr<false, false>(), kernel_ptr<false, true>(), exact_ptr<false, false>(), exact_ptr<false, true>(),
+                              kernel_ptr<false, false, true>(), kernel_ptr<false, true, true>(),
+                              kernel_ptr<true, false>(),  kernel_ptr<true, true>(),  exact_ptr<true, false>(),  exact_ptr<true, true>(),
+                              kernel_ptr<true, false, true>(), kernel_ptr<true, true, true>()};
+        for (int i = 0; i < 12; ++i) {
             good = good && cudaFuncSetAttribute(fn[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                static_cast<int>(i >= 4 ? smem_bytes<true>(kMaxWarps) : smem_bytes<false>(kMaxWarps))) == cudaSuccess;
+                                                static_cast<int>(i >= 6 ? smem_bytes<true>(kMaxWarps) : smem_bytes<false>(kMaxWarps))) == cudaSuccess;
             good = good && cudaFuncSetAttribute(fn[i], cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         }
         if (!good) cudaGetLastError();
@@ -1249,7 +1413,7 @@ static bool fits(const Plan& pl) {
     if (!d.ok) return false;
     int lg = 0;
     while ((1 << lg) < pl.cluster) ++lg;
-    signed char& slot = d.fits[kHalf ? 1 : 0][kBwd ? 1 : 0][lg][pl.n_warps];
+    signed char& slot = d.fits[pl.segs > 1 ? 1 : 0][kHalf ? 1 : 0][kBwd ? 1 : 0][lg][pl.n_warps];
     if (slot == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(pl.cluster);
@@ -1260,7 +1424,7 @@ static bool fits(const Plan& pl) {
         at[0].val.clusterDim.x = pl.cluster; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         int n = 0;
-        const cudaError_t err = cudaOccupancyMaxActiveClusters(&n, kernel_ptr<kBwd, kHalf>(), &cfg);
+        const cudaError_t err = cudaOccupancyMaxActiveClusters(&n, pl.segs > 1 ? kernel_ptr<kBwd, kHalf, true>() : kernel_ptr<kBwd, kHalf>(), &cfg);
         if (err != cudaSuccess) cudaGetLastError();
         slot = (err == cudaSuccess && n > 0) ? 1 : -1;
     }
@@ -1273,7 +1437,7 @@ bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool
         if (reinterpret_cast<uintptr_t>(q) & 15u) return false;    // TMA base alignment
     Plan pl;
     if (!make_plan(T, pl)) return false;
-    const long long ctas = static_cast<long long>(B) * ((C + kCs - 1) / kCs) * pl.cluster;
+    const long long ctas = static_cast<long long>(B) * ((C + kCs - 1) / kCs) * pl.cluster * pl.segs;
     if (ctas > (1LL << 30)) return false;
     if (bf16) return bwd ? fits<true, true>(pl) : fits<false, true>(pl);
     return bwd ? fits<true, false>(pl) : fits<false, false>(pl);
@@ -1281,11 +1445,31 @@ bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// workspace: status block (256 B) | redo list | backward partials | segment flags | segment records
+struct Carve {
+    size_t off_list, off_partial, off_flags, off_records, total;
+};
+static Carve carve(int B, int C, const Plan& pl, bool bwd) {
+    const size_t units = static_cast<size_t>(B) * ((C + kCs - 1) / kCs);
+    Carve cv;
+    cv.off_list = 256;
+    cv.off_partial = cv.off_list + align_up(units * sizeof(int), 256);
+    cv.off_flags = cv.off_partial + (bwd ? align_up(units * pl.segs * pl.cluster * 2 * kCs * sizeof(float), 256) : 0);
+    const size_t recs = pl.segs > 1 ? units * pl.segs * 4 : 0;
+    cv.off_records = cv.off_flags + align_up(recs * sizeof(unsigned), 256);
+    cv.total = cv.off_records + align_up(recs * kSegRec * sizeof(float), 256);
+    return cv;
+}
+
 size_t workspace_bytes(int B, int T, int C, bool bwd) {
     Plan pl;
     if (!make_plan(T, pl)) return 256;
-    const size_t units = static_cast<size_t>(B) * ((C + kCs - 1) / kCs);
-    return 256 + align_up(units * sizeof(int), 256) + (bwd ? align_up(units * pl.cluster * 2 * kCs * sizeof(float), 256) : 0);
+    return carve(B, C, pl, bwd).total;
+}
+
+bool multi_segment(int T) {
+    Plan pl;
+    return make_plan(T, pl) && pl.segs > 1;
 }
 
 template <bool kBwd, bool kHalf>
@@ -1301,9 +1485,13 @@ static int launch(int B, int T, int C, const float* w, const float* u, const voi
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     p.status = reinterpret_cast<unsigned*>(ws);
     const size_t units = static_cast<size_t>(B) * p.n_strips;
+    const Carve cv = carve(B, C, pl, kBwd);
     p.redo_count = reinterpret_cast<unsigned*>(ws) + 1;
-    p.redo_list = reinterpret_cast<int*>(ws + 256);
-    p.partial = reinterpret_cast<float*>(ws + 256 + align_up(units * sizeof(int), 256));
+    p.redo_list = reinterpret_cast<int*>(ws + cv.off_list);
+    p.partial = reinterpret_cast<float*>(ws + cv.off_partial);
+    p.segs = pl.segs;
+    p.xflag = reinterpret_cast<unsigned*>(ws + cv.off_flags);
+    p.xseg = reinterpret_cast<float*>(ws + cv.off_records);
     p.spin_limit = g_withhold.load() ? (1u << 10) : kSpinLimit;
     p.withhold_rank = g_withhold.load() ? 1 : -1;
     cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
@@ -1319,8 +1507,9 @@ static int launch(int B, int T, int C, const float* w, const float* u, const voi
         return -1;
     }
     cudaMemsetAsync(ws, 0, 256, stream);
+    if (pl.segs > 1) cudaMemsetAsync(p.xflag, 0, cv.off_records - cv.off_flags, stream);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(B) * p.n_strips * pl.cluster);
+    cfg.gridDim = dim3(static_cast<unsigned>(B) * p.n_strips * pl.cluster * pl.segs);
     cfg.blockDim = dim3(pl.n_warps * 32);
     cfg.dynamicSmemBytes = smem_bytes<kBwd>(pl.n_warps);
     cfg.stream = stream;
@@ -1328,19 +1517,24 @@ static int launch(int B, int T, int C, const float* w, const float* u, const voi
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = pl.cluster; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf>, mk, mv, mg, m0, m1, p);
+    const cudaError_t err = pl.segs > 1
+        ? cudaLaunchKernelEx(&cfg, biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf, true>, mk, mv, mg, m0, m1, p)
+        : cudaLaunchKernelEx(&cfg, biwkv_resident_kernel<kBwd, kBwd ? kBwdStash : kFwdStash, kHalf, false>, mk, mv, mg, m0, m1, p);
     if (err != cudaSuccess) {
         set_error_detail(cudaGetErrorName(err));
         return -1;
     }
-    // the exact kernel: a few clusters that serve whatever the fast kernel left behind
-    cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>(units, 16)) * pl.cluster);
-    const cudaError_t err2 = cudaLaunchKernelEx(&cfg, biwkv_exact_kernel<kBwd, kHalf>, mk, mv, mg, m0, m1, p);
-    if (err2 != cudaSuccess) {
-        set_error_detail(cudaGetErrorName(err2));
-        return -1;
+    int launched = 1;
+    if (pl.segs == 1) {
+        // the exact kernel: a few clusters that serve whatever the fast kernel left behind
+        cfg.gridDim = dim3(static_cast<unsigned>(std::min<size_t>(units, 16)) * pl.cluster);
+        const cudaError_t err2 = cudaLaunchKernelEx(&cfg, biwkv_exact_kernel<kBwd, kHalf>, mk, mv, mg, m0, m1, p);
+        if (err2 != cudaSuccess) {
+            set_error_detail(cudaGetErrorName(err2));
+            return -1;
+        }
+        ++launched;
     }
-    int launched = 2;
     if (kBwd) {
         reduce_partials<<<dim3(p.n_strips, 2), dim3(32, 32), 0, stream>>>(p, gwgu);
         ++launched;

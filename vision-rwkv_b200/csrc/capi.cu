@@ -80,10 +80,19 @@ int vrwkv_workspace_status(const void* workspace, void* stream, unsigned* status
     return VRWKV_OK;
 }
 
+// The resident kernels' workspace; for sequences of several segments the chunked kernels' workspace follows it
+// (they stand by for inputs outside the plain-float range and run only when the resident launch says so).
+static size_t resident_offset(int B, int T, int C, bool bwd) {
+    return (biwkv::resident::workspace_bytes(B, T, C, bwd) + 255) / 256 * 256;
+}
+static size_t resident_total(int B, int T, int C, bool bwd) {
+    return resident_offset(B, T, C, bwd) + (biwkv::resident::multi_segment(T) ? biwkv::fused::workspace_bytes(B, T, C, bwd) : 0);
+}
+
 size_t vrwkv_biwkv_forward_workspace_bytes(int B, int T, int C) {
     if (check_shape(B, T, C) != VRWKV_OK) return 0;
     return std::max({biwkv::generic_forward_workspace(B, T, C) + 256, biwkv::fused::workspace_bytes(B, T, C, false),
-                     biwkv::resident::workspace_bytes(B, T, C, false)});
+                     resident_total(B, T, C, false)});
 }
 
 int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
@@ -96,8 +105,17 @@ int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u,
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_forward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, y}, false))
-        return finish(biwkv::resident::forward(B, T, C, w, u, k, v, y, workspace, s));
+    const bool multi = biwkv::resident::multi_segment(T);
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, y}, false) &&
+        (!multi || biwkv::fused::eligible(B, T, C, {k, v, y}))) {
+        int n = biwkv::resident::forward(B, T, C, w, u, k, v, y, workspace, s);
+        if (n >= 0 && multi) {
+            const int m = biwkv::fused::forward(B, T, C, w, u, k, v, y, static_cast<char*>(workspace) + resident_offset(B, T, C, false), s,
+                                                static_cast<const unsigned*>(workspace) + 1);
+            n = m < 0 ? m : n + m;
+        }
+        return finish(n);
+    }
     if (g_path.load() != 1 && biwkv::fused::eligible(B, T, C, {k, v, y}))
         return finish(biwkv::fused::forward(B, T, C, w, u, k, v, y, workspace, s));
     // generic path: status word (first 256 bytes) is cleared, scratch follows
@@ -108,7 +126,7 @@ int vrwkv_biwkv_forward_f32(int B, int T, int C, const float* w, const float* u,
 size_t vrwkv_biwkv_backward_workspace_bytes(int B, int T, int C) {
     if (check_shape(B, T, C) != VRWKV_OK) return 0;
     return std::max({biwkv::generic_backward_workspace(B, T, C) + 256, biwkv::fused::workspace_bytes(B, T, C, true),
-                     biwkv::resident::workspace_bytes(B, T, C, true)});
+                     resident_total(B, T, C, true)});
 }
 
 int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u, const float* k,
@@ -121,8 +139,18 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_backward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, gy, gk, gv}, true))
-        return finish(biwkv::resident::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s));
+    const bool multi = biwkv::resident::multi_segment(T);
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, gy, gk, gv}, true) &&
+        (!multi || biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}))) {
+        int n = biwkv::resident::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s);
+        if (n >= 0 && multi) {
+            const int m = biwkv::fused::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv,
+                                                 static_cast<char*>(workspace) + resident_offset(B, T, C, true), s,
+                                                 static_cast<const unsigned*>(workspace) + 1);
+            n = m < 0 ? m : n + m;
+        }
+        return finish(n);
+    }
     if (g_path.load() != 1 && biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}))
         return finish(biwkv::fused::backward(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s));
     cudaMemsetAsync(workspace, 0, 256, s);
@@ -162,8 +190,18 @@ int vrwkv_biwkv_forward_bf16(int B, int T, int C, const float* w, const float* u
     if (!w || !u || !k || !v || !y || !workspace) return VRWKV_ERR_NULL;
     if (misaligned4(w) || misaligned4(u) || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_forward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
-    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, y}, false, true))
-        return finish(biwkv::resident::forward_bf16(B, T, C, w, u, k, v, y, workspace, static_cast<cudaStream_t>(stream)));
+    const bool multi = biwkv::resident::multi_segment(T);
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, y}, false, true) &&
+        (!multi || biwkv::fused::eligible(B, T, C, {k, v, y}, true))) {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        int n = biwkv::resident::forward_bf16(B, T, C, w, u, k, v, y, workspace, s);
+        if (n >= 0 && multi) {
+            const int m = biwkv::fused::forward_bf16(B, T, C, w, u, k, v, y, static_cast<char*>(workspace) + resident_offset(B, T, C, false), s,
+                                                     static_cast<const unsigned*>(workspace) + 1);
+            n = m < 0 ? m : n + m;
+        }
+        return finish(n);
+    }
     if (!biwkv::fused::eligible(B, T, C, {k, v, y}, true)) return VRWKV_ERR_UNSUPPORTED;
     return finish(biwkv::fused::forward_bf16(B, T, C, w, u, k, v, y, workspace, static_cast<cudaStream_t>(stream)));
 }
@@ -176,9 +214,19 @@ int vrwkv_biwkv_backward_bf16(int B, int T, int C, const float* w, const float* 
     if (misaligned4(w) || misaligned4(u) || misaligned4(gwgu) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_biwkv_backward_workspace_bytes(B, T, C)) return VRWKV_ERR_WORKSPACE;
-    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, gy, gk, gv}, true, true))
-        return finish(biwkv::resident::backward_bf16(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace,
-                                                     static_cast<cudaStream_t>(stream)));
+    const bool multi = biwkv::resident::multi_segment(T);
+    if (g_path.load() == 0 && biwkv::resident::eligible(B, T, C, {k, v, gy, gk, gv}, true, true) &&
+        (!multi || biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}, true))) {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        int n = biwkv::resident::backward_bf16(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace, s);
+        if (n >= 0 && multi) {
+            const int m = biwkv::fused::backward_bf16(B, T, C, w, u, k, v, gy, gwgu, gk, gv,
+                                                      static_cast<char*>(workspace) + resident_offset(B, T, C, true), s,
+                                                      static_cast<const unsigned*>(workspace) + 1);
+            n = m < 0 ? m : n + m;
+        }
+        return finish(n);
+    }
     if (!biwkv::fused::eligible(B, T, C, {k, v, gy, gk, gv}, true)) return VRWKV_ERR_UNSUPPORTED;
     return finish(biwkv::fused::backward_bf16(B, T, C, w, u, k, v, gy, gwgu, gk, gv, workspace,
                                               static_cast<cudaStream_t>(stream)));

@@ -24,6 +24,10 @@ namespace resident {
 bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bwd, bool bf16 = false);
 void set_withhold_test(bool on);   // test only: one rank per cluster sends nothing, waits give up early
 size_t workspace_bytes(int B, int T, int C, bool bwd);
+// Sequences longer than one cluster holds (T > 4096) run as several clusters per sequence.  Inputs outside the
+// plain-float range then leave workspace word 1 non-zero instead of results: the caller follows up with the
+// chunked kernels switched on by that word.
+bool multi_segment(int T);
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
             float* y, void* workspace, cudaStream_t stream);
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
@@ -39,11 +43,12 @@ namespace fused {
 // True when the fused TMA path can serve this call on the current device.
 bool eligible(int B, int T, int C, std::initializer_list<const void*> ptrs, bool bf16 = false);
 size_t workspace_bytes(int B, int T, int C, bool bwd);
+// run_if: when set, every kernel of the launch returns at once while that device word is zero.
 int forward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
-            float* y, void* workspace, cudaStream_t stream);
+            float* y, void* workspace, cudaStream_t stream, const unsigned* run_if = nullptr);
 int backward(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
              const float* gy, float* gwgu, float* gk, float* gv, void* workspace,
-             cudaStream_t stream);
+             cudaStream_t stream, const unsigned* run_if = nullptr);
 // Forward that also writes log Den (one float per element), and the backward that starts from the
 // saved y and log Den: one exchange level instead of two.
 bool eligible_saved(int B, int T, int C, std::initializer_list<const void*> ptrs);
@@ -54,9 +59,10 @@ int backward_saved(int B, int T, int C, const float* w, const float* u, const fl
                    void* workspace, cudaStream_t stream);
 // k, v, y, gy, gk, gv hold bfloat16; w, u, gwgu stay float; arithmetic is the float kernels'.
 int forward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v, void* y,
-                 void* workspace, cudaStream_t stream);
+                 void* workspace, cudaStream_t stream, const unsigned* run_if = nullptr);
 int backward_bf16(int B, int T, int C, const float* w, const float* u, const void* k, const void* v,
-                  const void* gy, float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream);
+                  const void* gy, float* gwgu, void* gk, void* gv, void* workspace, cudaStream_t stream,
+                  const unsigned* run_if = nullptr);
 }  // namespace fused
 }  // namespace biwkv
 
