@@ -47,7 +47,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the backward kernel, from an ncu capture
 # of `bench.py --batch 8 --steps 1 --warmup 3 --no-secondary --no-cpu-baseline --e2e-steps 0`
 # (B=8, T=4096, C=768: 25.2 M elements); the traffic is proportional to the element count.
-NCU_BACKWARD_DRAM_BYTES = {"recompute": 471.7e6, "saved": 694.5e6}
+NCU_BACKWARD_DRAM_BYTES = {"recompute": 463.9e6, "saved": 694.5e6}
 NCU_CAPTURE_ELEMENTS = 8 * 4096 * 768
 
 
@@ -586,17 +586,19 @@ def _wkv6_inputs(cx, B, T, H, dtype):
     return r, k, v, w, u, gy
 
 
-def sec_wkv6(cx):
+def sec_wkv6(cx, total=32, long_only=False):
     """WKV6 as in VRWKV6-B: C=768, 12 heads of 64, 32 sequences split over the ranks, forward + backward.
     T=196 in fp32 (exact sweeps) and bf16 (tcgen05 kernels); T=4096 in bf16 with its roofline: algorithmic
     bytes 28 per element if every tensor moved as bfloat16 (forward reads r, k, v, w and writes y; backward
     reads r, k, v, w, gy and writes gr, gk, gv, gw), 3584 flops per element in the chunked formulation
     (14 head-size products of 2 x 64 flops each: 4 forward, 10 backward)."""
     from vision_rwkv_b200 import ops
-    total, H = 32, 12
+    H = 12
     C = 64 * H
     n = _share(total, cx)
     out = {"global_batch": total, "batch_per_gpu": n, "n_gpus": cx.world, "C": C, "heads": H}
+    if long_only:
+        return _wkv6_long(cx, out, total, n, H, exact_too=False)
     r, k, v, w, u, gy = _wkv6_inputs(cx, n, 196, H, torch.float32)
     ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(r, k, v, w, u, H), lambda _: ops.wkv6_backward(r, k, v, w, u, gy, H))
     out["wkv6_fwd_bwd_t196_f32"] = {"ms": ms, "fwd_ms": f, "bwd_ms": b, "kernels": "exact fp32 state sweeps",
@@ -607,6 +609,12 @@ def sec_wkv6(cx):
     out["wkv6_fwd_bwd_t196_bf16"] = {"ms": ms, "fwd_ms": f, "bwd_ms": b, "kernels": "tcgen05 forward and backward",
                                      "elements_per_s": total * 196 * C / (ms * 1e-3)}
     del r, k, v, w, gy, rh, kh, vh, gh
+    return _wkv6_long(cx, out, total, n, H, exact_too=True)
+
+
+def _wkv6_long(cx, out, total, n, H, exact_too):
+    from vision_rwkv_b200 import ops
+    C = 64 * H
     T = 4096
     r, k, v, w, u, gy = _wkv6_inputs(cx, n, T, H, torch.bfloat16)
     ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(r, k, v, w, u, H, tensor_cores=True),
@@ -625,6 +633,8 @@ def sec_wkv6(cx):
                      "tensor": {"achieved": tf, "peak": cx.tflops * cx.world, "unit": "TFLOP/s",
                                 "frac": tf / (cx.tflops * cx.world), "flops_per_element": 3584},
                      "peak_source": cx.peak_kind}}
+    if not exact_too:
+        return out
     # the exact float32 sweeps on the same values, for comparison
     r32, k32, v32, g32 = (x.float() for x in (r, k, v, gy))
     ms, f, b = _pair_ms(cx, lambda: ops.wkv6_forward(r32, k32, v32, w, u, H),
@@ -660,14 +670,15 @@ def side_measurements(cx, hl, args):
         ("vrwkv_l_train_step_b64_t576", lambda: sec_vrwkv_l_train(cx)),
         ("vrwkv_b_dense_800x1344_b16", lambda: sec_vrwkv_b_dense(cx)),
         ("vrwkv6_b_inference", lambda: sec_vrwkv6_b_inference(cx)),
-        ("wkv6", lambda: sec_wkv6(cx)),
+        ("wkv6", lambda: sec_wkv6(cx, args.wkv6_batch)),
+        ("wkv6_t4096_bf16_only", lambda: sec_wkv6(cx, args.wkv6_batch, long_only=True)),
         ("qshift_mix_forward", lambda: sec_qshift(cx)),
     ]
     needs_headline = {"other_pair", "autograd_surface", "strong_scaling_b64", "biwkv_bf16_fwd_bwd"}
     out = {"timing": f"each figure: CUDA events around >= {cx.min_ms:.0f} ms of back-to-back calls after warm-up, max over ranks"}
     freed = False
     for name, fn in table:
-        if args.only and name not in args.only:
+        if (args.only and name not in args.only) or (not args.only and name.endswith("_only")):
             continue
         if name not in needs_headline and not freed:
             hl.clear()                            # the headline tensors (2.4 GB) are not needed from here on
@@ -702,6 +713,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--only", action="append", default=[], help="run only this secondary measurement (repeatable)")
     ap.add_argument("--min-ms", type=float, default=1000.0, help="length of each secondary timed region")
+    ap.add_argument("--wkv6-batch", type=int, default=32, help="sequences (over all ranks) of the WKV6 measurements")
     ap.add_argument("--sustain-ms", type=float, default=1500.0,
                     help="after the K timed steps, keep stepping for this long so that the clock samples cover a loaded GPU")
     args = ap.parse_args()
