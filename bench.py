@@ -373,13 +373,14 @@ def sec_autograd_surface(cx, hl):
             "ms": ms, "shape_per_gpu": list(k.shape), "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs / cx.world)}
 
 
-def sec_strong_scaling(cx, hl):
+def sec_strong_scaling(cx, hl, total=None):
     """A fixed global batch of 64 sequences split over the ranks, gw|gu all-reduced once per step on a side
     stream while the next forward runs."""
     from vision_rwkv_b200 import ops
     from vision_rwkv_b200.parallel import shard_bounds
     w, u, k, v, gy = hl
-    lo, hi = shard_bounds(WORKLOAD["B"], cx.rank, cx.world)
+    total = min(total or WORKLOAD["B"], k.shape[0] * cx.world)
+    lo, hi = shard_bounds(total, cx.rank, cx.world)
     nb = hi - lo
     ks, vs, gs = k[:nb], v[:nb], gy[:nb]
     bufs = [torch.empty(2, k.shape[2], device=cx.dev) for _ in range(2)]
@@ -397,11 +398,37 @@ def sec_strong_scaling(cx, hl):
     ms = cx.timed(step)
     if cx.world > 1:
         cx.reducer.wait()
-    E = WORKLOAD["B"] * k.shape[1] * k.shape[2]
+    E = total * k.shape[1] * k.shape[2]
     gbs = (BYTES_FWD + BYTES_BWD) * E / (ms * 1e-3) / 1e9
-    return {"global_batch": WORKLOAD["B"], "batch_per_gpu": nb, "n_gpus": cx.world, "ms_per_step": ms,
-            "algorithmic_GBps_all_gpus": gbs, "frac_of_hbm_peak_per_gpu": cx.frac(gbs / cx.world),
-            "collective": "one all-reduce of (2, C) per step, overlapped with the next forward" if cx.world > 1 else "none"}
+    out = {"global_batch": total, "batch_per_gpu": nb, "n_gpus": cx.world, "ms_per_step": ms,
+           "algorithmic_GBps_all_gpus": gbs, "frac_of_hbm_peak_per_gpu": cx.frac(gbs / cx.world),
+           "collective": "one all-reduce of (2, C) per step, overlapped with the next forward" if cx.world > 1 else "none"}
+    # The same step captured once in a CUDA graph and replayed: at a few sequences per GPU the kernels are short
+    # enough for launch gaps and host work to show, and a training loop would replay a captured step anyway.
+    try:
+        torch.cuda.synchronize()
+        buf = bufs[0]
+        side = torch.cuda.Stream(cx.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for _ in range(2):                          # allocations and lazy set-up outside the capture
+                ops.biwkv_forward(w, u, ks, vs)
+                ops.biwkv_backward(w, u, ks, vs, gs, gwgu_out=buf)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                ops.biwkv_forward(w, u, ks, vs)
+                ops.biwkv_backward(w, u, ks, vs, gs, gwgu_out=buf)
+                if cx.world > 1:
+                    cx.dist.all_reduce(buf)
+        torch.cuda.current_stream().wait_stream(side)
+        gms = cx.timed(graph.replay)
+        out["cuda_graph"] = {"ms_per_step": gms, "algorithmic_GBps_all_gpus": (BYTES_FWD + BYTES_BWD) * E / (gms * 1e-3) / 1e9,
+                             "captured": "forward, backward" + (", all-reduce of (2, C)" if cx.world > 1 else "")}
+        del graph
+    except Exception as exc:
+        out["cuda_graph"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    return out
 
 
 def sec_biwkv_bf16(cx, hl):
@@ -662,7 +689,7 @@ def side_measurements(cx, hl, args):
     table = [
         ("other_pair", lambda: sec_other_pair(cx, hl, args.saved)),
         ("autograd_surface", lambda: sec_autograd_surface(cx, hl)),
-        ("strong_scaling_b64", lambda: sec_strong_scaling(cx, hl)),
+        ("strong_scaling_b64", lambda: sec_strong_scaling(cx, hl, args.strong_batch)),
         ("biwkv_bf16_fwd_bwd", lambda: sec_biwkv_bf16(cx, hl)),
         ("biwkv_sequence_sweep_b8", lambda: sec_sequence_sweep(cx)),
         ("vrwkv_s_inference_b256", lambda: sec_vrwkv_s_inference(cx)),
@@ -713,6 +740,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--only", action="append", default=[], help="run only this secondary measurement (repeatable)")
     ap.add_argument("--min-ms", type=float, default=1000.0, help="length of each secondary timed region")
+    ap.add_argument("--strong-batch", type=int, default=WORKLOAD["B"],
+                    help="global batch of the strong-scaling measurement (8 on one GPU = one rank's share of 64 on eight)")
     ap.add_argument("--wkv6-batch", type=int, default=32, help="sequences (over all ranks) of the WKV6 measurements")
     ap.add_argument("--sustain-ms", type=float, default=1500.0,
                     help="after the K timed steps, keep stepping for this long so that the clock samples cover a loaded GPU")

@@ -8,7 +8,9 @@ sources in place through the two shim files next to this script.
 
 Flags follow the reference's own JIT calls (classification/mae/vrwkv/vrwkv.py:27-28,
 classification/mmcls_custom/models/backbones/vrwkv6.py:25-32), with the B200 architecture
-in place of its sm_86.
+in place of its sm_86.  The kernel file the live backbones load (cuda_new/bi_wkv_kernel.cu) includes
+torch headers for its host wrappers; it is compiled against the small stand-ins under ref_stubs/
+(torch/extension.h, THC/THCAtomics.cuh) so that no torch build is involved.
 """
 from __future__ import annotations
 
@@ -24,6 +26,8 @@ DEFAULT_REF = os.environ.get("VRWKV_REFERENCE_ROOT", os.path.join(os.sep, "root"
 TARGETS = {
     "libref_biwkv.so": ("ref_shim_biwkv.cu", "classification/mae/vrwkv/cuda/wkv_cuda.cu",
                         ["-DTmax=4096", "--maxrregcount", "60"]),
+    "libref_biwkv_live.so": ("ref_shim_biwkv_live.cu", "classification/mmcls_custom/models/backbones/cuda_new/bi_wkv_kernel.cu",
+                             ["--maxrregcount", "60"]),       # classification/mmcls_custom/models/backbones/vrwkv.py:24-25
     "libref_wkv6.so": ("ref_shim_wkv6.cu", "classification/mmcls_custom/models/backbones/cuda_v6/wkv6_cuda.cu",
                        ["-D_N_=64", "-D_T_=256", "--extra-device-vectorization"]),
 }

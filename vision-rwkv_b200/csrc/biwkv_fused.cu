@@ -1421,7 +1421,7 @@ static int launch(Layout& l, const float* w, const float* u, const E* k, const E
     p.flags = reinterpret_cast<unsigned*>(ws + l.off_flags);
     p.exch = reinterpret_cast<float*>(ws + l.off_exch);
     p.partial = reinterpret_cast<float*>(ws + l.off_partial);
-    cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
+    tensor_map::bind_primary_context();   // the tensor-map encoder is a driver call
     CUtensorMap mk, mv, mg, m0, m1;
     bool ok = make_map<E>(&mk, k, p.B, p.T, p.C) && make_map<E>(&mv, v, p.B, p.T, p.C) &&
               make_map<E>(&m0, o0, p.B, p.T, p.C);
@@ -1529,7 +1529,7 @@ int backward_saved(int B, int T, int C, const float* w, const float* u, const fl
     p.flags = reinterpret_cast<unsigned*>(ws + l.off_flags);
     p.exch = reinterpret_cast<float*>(ws + l.off_exch);
     p.partial = reinterpret_cast<float*>(ws + l.off_partial);
-    cudaFree(nullptr);
+    tensor_map::bind_primary_context();   // the tensor-map encoder is a driver call
     CUtensorMap mk, mv, mg, my, ml, m0, m1;
     const bool ok = make_map<float>(&mk, k, B, T, C) && make_map<float>(&mv, v, B, T, C) && make_map<float>(&mg, gy, B, T, C) &&
                     make_map<float>(&my, y, B, T, C) && make_map<float>(&ml, logden, B, T, C) &&

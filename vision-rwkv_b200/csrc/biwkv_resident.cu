@@ -1494,7 +1494,7 @@ static int launch(int B, int T, int C, const float* w, const float* u, const voi
     p.xseg = reinterpret_cast<float*>(ws + cv.off_records);
     p.spin_limit = g_withhold.load() ? (1u << 10) : kSpinLimit;
     p.withhold_rank = g_withhold.load() ? 1 : -1;
-    cudaFree(nullptr);   // binds the primary context in this host thread: the encoder is a driver call
+    tensor_map::bind_primary_context();   // the tensor-map encoder is a driver call
     CUtensorMap mk, mv, mg, m0, m1;
     // float32: loads one box per 32-token span, stores one box per CTA; bfloat16: one box per 16-token sub-chunk both ways
     const int box_in = kHalf ? kL : kSpan, box_out = kHalf ? kL : pl.n_tok;

@@ -24,6 +24,17 @@ inline EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// cuTensorMapEncodeTiled needs a current context; a host thread that has made no runtime call that creates one
+// (a fresh worker thread) binds the primary context here, once per thread.  Not repeated per call: an allocator
+// call is not allowed while a stream is being captured into a graph.
+inline void bind_primary_context() {
+    thread_local bool bound = false;
+    if (!bound) {
+        cudaFree(nullptr);
+        bound = true;
+    }
+}
+
 // Box of box_c channels x box_t tokens of one batch entry; out-of-range elements load as zero and
 // are clipped on store.  `base` must be 16-byte aligned and the row pitch C * elem_bytes a multiple
 // of 16 (C % 4 == 0 for float, C % 8 == 0 for bfloat16).

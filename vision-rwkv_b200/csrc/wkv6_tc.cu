@@ -1363,7 +1363,7 @@ static bool configure_once() {
 static int launch(int B, int T, int H, const void* r, const void* k, const void* v, const float* w_raw, const float* u,
                   float* y, unsigned* status, bool half_in, bool pipelined, cudaStream_t stream) {
     if (!configure_once()) return -1;
-    cudaFree(nullptr);   // descriptors are encoded against the current context; a fresh thread may not have one bound
+    tensor_map::bind_primary_context();   // the tensor-map encoder is a driver call
     const int C = H * N;
     CUtensorMap mr, mk, mv, mw, my;
     if (!(tensor_map::make_btc(&mr, r, B, T, C, N, SC, half_in) && tensor_map::make_btc(&mk, k, B, T, C, N, SC, half_in) &&
@@ -1425,7 +1425,7 @@ int backward(int B, int T, int H, const void* r, const void* k, const void* v, c
              const void* gy, float* gr, float* gk, float* gv, float* gw, float* gu, void* workspace, bool half_in,
              cudaStream_t stream) {
     if (!configure_once()) return -1;
-    cudaFree(nullptr);
+    tensor_map::bind_primary_context();   // the tensor-map encoder is a driver call
     const size_t C = static_cast<size_t>(H) * N, E = static_cast<size_t>(B) * T * C;
     unsigned* status = static_cast<unsigned*>(workspace);
     float* ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
