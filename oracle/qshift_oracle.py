@@ -2,7 +2,7 @@
 
 Restates, with index arithmetic instead of slice assignments,
 classification/mmcls_custom/models/backbones/vrwkv.py:68-79 (`q_shift`: four channel groups of
-int(C * gamma) channels moved by `shift_pixel` pixels right, left, down, up on the H x W token
+channels, bounded at int(C * gamma * k), moved by `shift_pixel` pixels right, left, down, up on the H x W token
 grid with zero fill; remaining channels copied) and :156-164 (out = x * mix + xx * (1 - mix)).
 Pinned by construction: it is a permutation with zero fill, checked in the tests against an
 independent formulation by padded 2-D shifts and by torch.autograd for the gradients.
@@ -15,17 +15,17 @@ import torch
 def q_shift(x, resolution, shift_pixel=1, gamma=0.25):
     B, T, C = x.shape
     H, W = resolution
-    g = int(C * gamma)
+    b1, b2, b3, b4 = (int(C * gamma * j) for j in (1, 2, 3, 4))      # the reference's slice bounds (:72-76)
     grid = x.reshape(B, H, W, C)
     out = torch.zeros_like(grid)
     s = shift_pixel
     if s < W:
-        out[:, :, s:, 0:g] = grid[:, :, :W - s, 0:g]
-        out[:, :, :W - s, g:2 * g] = grid[:, :, s:, g:2 * g]
+        out[:, :, s:, 0:b1] = grid[:, :, :W - s, 0:b1]
+        out[:, :, :W - s, b1:b2] = grid[:, :, s:, b1:b2]
     if s < H:
-        out[:, s:, :, 2 * g:3 * g] = grid[:, :H - s, :, 2 * g:3 * g]
-        out[:, :H - s, :, 3 * g:4 * g] = grid[:, s:, :, 3 * g:4 * g]
-    out[..., 4 * g:] = grid[..., 4 * g:]
+        out[:, s:, :, b2:b3] = grid[:, :H - s, :, b2:b3]
+        out[:, :H - s, :, b3:b4] = grid[:, s:, :, b3:b4]
+    out[..., b4:] = grid[..., b4:]
     return out.reshape(B, T, C)
 
 

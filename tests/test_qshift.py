@@ -14,15 +14,16 @@ def shift_by_padding(x, resolution, s, gamma):
     g = int(C * gamma)
     img = x.transpose(1, 2).reshape(B, C, H, W)
     out = img.clone()
-    out[:, 0:g] = F.pad(img[:, 0:g], (s, 0, 0, 0))[..., :W]
-    out[:, g:2 * g] = F.pad(img[:, g:2 * g], (0, s, 0, 0))[..., s:]
-    out[:, 2 * g:3 * g] = F.pad(img[:, 2 * g:3 * g], (0, 0, s, 0))[:, :, :H]
-    out[:, 3 * g:4 * g] = F.pad(img[:, 3 * g:4 * g], (0, 0, 0, s))[:, :, s:]
+    b1, b2, b3, b4 = (int(C * gamma * j) for j in (1, 2, 3, 4))          # the reference's own bounds (vrwkv.py:72-76)
+    out[:, 0:b1] = F.pad(img[:, 0:b1], (s, 0, 0, 0))[..., :W]
+    out[:, b1:b2] = F.pad(img[:, b1:b2], (0, s, 0, 0))[..., s:]
+    out[:, b2:b3] = F.pad(img[:, b2:b3], (0, 0, s, 0))[:, :, :H]
+    out[:, b3:b4] = F.pad(img[:, b3:b4], (0, 0, 0, s))[:, :, s:]
     return out.flatten(2).transpose(1, 2)
 
 
 @pytest.mark.parametrize("B,H,W,C,s,gamma", [(2, 5, 7, 16, 1, 0.25), (1, 14, 14, 36, 1, 0.25),
-                                             (1, 4, 3, 10, 2, 0.2), (1, 1, 6, 8, 1, 0.25)])
+                                             (1, 4, 3, 10, 2, 0.2), (1, 1, 6, 8, 1, 0.25), (1, 3, 3, 192, 1, 0.2)])
 def test_oracle_matches_padded_shift(B, H, W, C, s, gamma):
     x = torch.randn(B, H * W, C, dtype=torch.float64)
     assert torch.equal(O.q_shift(x, (H, W), s, gamma), shift_by_padding(x, (H, W), s, gamma))
@@ -82,6 +83,18 @@ def test_fused_per_head_shift_matches_oracle(cuda_device, B, H, W, C, head_dim, 
     assert rel_err(xd.grad, xr.grad) < 1e-6
     for a, b in zip(md, mr):
         assert a.grad.shape == b.grad.shape and rel_err(a.grad, b.grad) < 1e-5
+
+
+@pytest.mark.gpu
+def test_group_bounds_that_are_not_multiples_are_refused(cuda_device):
+    """C = 192, gamma = 0.2: the reference slices at 38, 76, 115, 153, which no single group size reproduces; the
+    wrapper says so instead of shifting at 38, 76, 114, 152."""
+    from vision_rwkv_b200 import ops
+    x = torch.randn(1, 9, 192, device=cuda_device)
+    mix = [torch.rand(192, device=cuda_device)]
+    with pytest.raises(RuntimeError, match="not an integer"):
+        ops.qshift_mix_forward(x, mix, (3, 3), gamma=0.2)
+    assert [int(192 * 0.2 * j) for j in (1, 2, 3, 4)] == [38, 76, 115, 153]
 
 
 @pytest.mark.gpu

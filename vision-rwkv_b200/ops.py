@@ -394,6 +394,12 @@ def _qshift_args(x, mixes, resolution, shift_pixel, gamma, head_dim=None):
         group = int(C * gamma)
         if group <= 0:
             raise RuntimeError(f"int(C * gamma) = 0 for C={C}")
+        # the reference slices at int(C * gamma * k), k = 1..4 (vrwkv.py:72-76); the kernel's groups are k * int(C * gamma).
+        # The two agree whenever C * gamma is an integer (every shipped configuration: gamma = 1/4, C % 4 == 0);
+        # anything else is refused rather than shifted at slightly different channels.
+        if any(int(C * gamma * j) != j * group for j in (2, 3, 4)):
+            raise RuntimeError(f"C * gamma = {C * gamma} is not an integer: the group boundaries int(C * gamma * k) of the "
+                               f"reference are not multiples of one group size, which this kernel requires")
     for m in mixes:
         if m.numel() != C:
             raise RuntimeError(f"mix vectors must hold C={C} values")
