@@ -51,8 +51,9 @@ const char* vrwkv_last_error_detail(void);
 unsigned long long vrwkv_launch_count(void);
 
 /* Kernel path selection, for tests and measurements: 0 = automatic (default: Bi-WKV takes the
- * cluster-resident single-pass kernels when T <= 4096, C % 4 == 0 and the tensors are 16-byte
- * aligned, else the persistent tile kernels, else the generic multi-launch path), 1 = the
+ * cluster-resident single-pass kernels when T <= 32768, C % 4 == 0 (bfloat16: C % 8 == 0) and the
+ * tensors are 16-byte aligned - one cluster per sequence strip up to T = 4096, several above -,
+ * else the persistent tile kernels, else the generic multi-launch path), 1 = the
  * first-generation kernels (Bi-WKV: the generic multi-launch path; WKV6 tensor-core forward:
  * the serial-phase kernel instead of the warp-specialised one), 2 = Bi-WKV skips the
  * cluster-resident kernels (persistent tile kernels where eligible), 3 = test of the bounded
@@ -63,7 +64,8 @@ unsigned long long vrwkv_launch_count(void);
 int vrwkv_set_path(int path);
 /* Copies the device status word kept in the first 4 bytes of a workspace to *status_out
  * after synchronising `stream`.  0 means no bounded device-side wait ran out; bit 0 = a
- * tile-exchange flag never arrived, bit 1 = a TMA load never completed.  Diagnostic only;
+ * hand-over between CTAs (tile-exchange flag, cluster mbarrier) never arrived, bit 1 = a TMA load never
+ * completed, bit 2 = a record of another segment of a long sequence never arrived.  Diagnostic only;
  * no reference counterpart (the reference never checks its launches). */
 int vrwkv_workspace_status(const void* workspace, void* stream, unsigned* status_out);
 
@@ -102,9 +104,10 @@ int vrwkv_biwkv_backward_f32(int B, int T, int C, const float* w, const float* u
  * backward rebuilds y, 1/Den and the shift per token inside its kernel and holds them in three
  * scratch tensors (bi_wkv_kernel.cu:259-302, 415-417).  Here the forward can write log Den_t next
  * to y (one extra float per element), and vrwkv_biwkv_backward_saved_f32 takes k, v, gy and the
- * saved y, log Den: it needs one cross-tile exchange instead of two and is about 40 % faster than
- * vrwkv_biwkv_backward_f32, at the price of keeping logden (B*T*C floats) from forward to backward.
- * Results agree with the recomputing pair to float32 rounding.  Same workspace sizes.  Both are
+ * saved y, log Den: it needs one cross-tile exchange instead of two, at the price of keeping logden
+ * (B*T*C floats) from forward to backward.  The pair runs on the tile kernels; for T <= 4096 the
+ * cluster-resident vrwkv_biwkv_forward_f32 + vrwkv_biwkv_backward_f32, which keep nothing, are
+ * about twice as fast.  Results agree with the recomputing pair to float32 rounding.  Same workspace sizes.  Both are
  * served by the single-pass TMA kernels only (C % 4 == 0, 16-byte aligned tensors, T below about
  * 37 000); otherwise they return VRWKV_ERR_UNSUPPORTED and nothing ran. */
 int vrwkv_biwkv_forward_save_f32(int B, int T, int C, const float* w, const float* u, const float* k,
