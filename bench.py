@@ -453,7 +453,7 @@ def sec_sequence_sweep(cx):
         gbs = (BYTES_FWD + BYTES_BWD) * B * T * C / (ms * 1e-3) / 1e9
         rows.append({"T": T, "fwd_ms": f, "bwd_ms": b, "ms": ms, "us_per_token": ms * 1e3 / (B * T),
                      "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs),
-                     "kernels": "cluster-resident" if T <= 4096 else "chunked tiles with cross-tile exchange"})
+                     "kernels": "one cluster per sequence strip" if T <= 4096 else "several clusters per sequence strip, aggregates exchanged through global memory"})
         del k, v, gy
     return {"B": 8, "C": 768, "dtype": "f32", "per_gpu": True, "rows": rows}
 
@@ -684,6 +684,29 @@ def sec_qshift(cx):
             "outputs": 3, "per_gpu": True}
 
 
+def sec_normgate(cx):
+    """Fused normalise-and-gate epilogue: LayerNorm + gate over C = 1024 (behind Bi-WKV in VRWKV-L) and per-head
+    GroupNorm + gate at C = 768 (behind WKV6), bfloat16 gate.  Forward moves 4 + 2 + 4 = 10 bytes per element,
+    backward 4 + 4 + 2 in and 4 + 2 out = 16."""
+    from vision_rwkv_b200 import ops
+    g = torch.Generator(device=cx.dev).manual_seed(5)
+    out = {}
+    for name, rows, C, group in (("layernorm_c1024", 64 * 576, 1024, 1024), ("groupnorm64_c768", 64 * 1024, 768, 64)):
+        x = torch.randn(rows, C, device=cx.dev, generator=g)
+        gate = torch.rand(rows, C, device=cx.dev, generator=g).bfloat16()
+        gout = torch.randn(rows, C, device=cx.dev, generator=g)
+        wt, bs = torch.ones(C, device=cx.dev), torch.zeros(C, device=cx.dev)
+        _, mean, rstd = ops.normgate_forward(x, gate, wt, bs, group)
+        f = cx.timed(lambda: ops.normgate_forward(x, gate, wt, bs, group))
+        b = cx.timed(lambda: ops.normgate_backward(gout, x, gate, wt, bs, mean, rstd, group))
+        E = rows * C
+        out[name] = {"rows": rows, "C": C, "fwd_ms": f, "bwd_ms": b, "fwd_GBps": 10 * E / (f * 1e-3) / 1e9,
+                     "bwd_GBps": 16 * E / (b * 1e-3) / 1e9, "fwd_frac_of_hbm_peak": cx.frac(10 * E / (f * 1e-3) / 1e9),
+                     "bwd_frac_of_hbm_peak": cx.frac(16 * E / (b * 1e-3) / 1e9), "per_gpu": True}
+        del x, gate, gout
+    return out
+
+
 def side_measurements(cx, hl, args):
     """Every secondary measurement by name; one that raises leaves its message in place of its numbers."""
     table = [
@@ -700,6 +723,7 @@ def side_measurements(cx, hl, args):
         ("wkv6", lambda: sec_wkv6(cx, args.wkv6_batch)),
         ("wkv6_t4096_bf16_only", lambda: sec_wkv6(cx, args.wkv6_batch, long_only=True)),
         ("qshift_mix_forward", lambda: sec_qshift(cx)),
+        ("normgate", lambda: sec_normgate(cx)),
     ]
     needs_headline = {"other_pair", "autograd_surface", "strong_scaling_b64", "biwkv_bf16_fwd_bwd"}
     out = {"timing": f"each figure: CUDA events around >= {cx.min_ms:.0f} ms of back-to-back calls after warm-up, max over ranks"}

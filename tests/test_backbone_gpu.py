@@ -51,13 +51,14 @@ def oracle_forward(model, img):
     return x.reshape(x.shape[0], *res, x.shape[2]).permute(0, 3, 1, 2)
 
 
-@pytest.mark.parametrize("post_norm,key_norm,init_values,size", [(True, False, 1.0, 32), (False, True, None, 40)])
-def test_small_backbone_forward_and_backward(cuda_device, post_norm, key_norm, init_values, size):
+@pytest.mark.parametrize("post_norm,key_norm,init_values,size,embed", [(True, False, 1.0, 32, 32), (False, True, None, 40, 32),
+                                                                      (False, True, None, 32, 64)])   # 64: fused key_norm + gate
+def test_small_backbone_forward_and_backward(cuda_device, post_norm, key_norm, init_values, size, embed):
     from vision_rwkv_b200.backbone import VRWKV
     torch.manual_seed(0)
     torch.backends.cudnn.allow_tf32 = False          # the patch-embedding convolution would use TF32
     torch.backends.cuda.matmul.allow_tf32 = False
-    model = VRWKV(img_size=32, patch_size=8, embed_dims=32, depth=2, post_norm=post_norm, key_norm=key_norm,
+    model = VRWKV(img_size=32, patch_size=8, embed_dims=embed, depth=2, post_norm=post_norm, key_norm=key_norm,
                   init_values=init_values)
     torch.nn.init.normal_(model.pos_embed, std=0.02)
     img = torch.randn(2, 3, size, size)

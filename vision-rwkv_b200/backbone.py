@@ -20,6 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 import torch.utils.checkpoint as cp
 
+from . import normgate
 from .qshift import qshift_mix
 from .vrwkv import RUN_CUDA
 
@@ -58,6 +59,9 @@ class SpatialMix(nn.Module):
         sr = torch.sigmoid(self.receptance(xr))
         y = RUN_CUDA(self.spatial_decay / T, self.spatial_first / T, k, v)
         if self.key_norm is not None:
+            if y.is_cuda and normgate.supported(y.shape[-1], y.shape[-1]):
+                # LayerNorm and gate in one pass over y (normgate.py)
+                return self.output(normgate.norm_gate(y, sr, self.key_norm.weight, self.key_norm.bias, y.shape[-1], self.key_norm.eps))
             y = self.key_norm(y)
         return self.output(sr * y.to(sr.dtype))
 

@@ -21,6 +21,7 @@ import torch.nn.functional as F
 import torch.utils.checkpoint as cp
 
 from .backbone import _PatchEmbed, _ramp
+from . import normgate
 from .qshift import qshift_mix
 from .vrwkv6 import HEAD_SIZE, RUN_CUDA_RWKV6
 
@@ -89,6 +90,9 @@ class SpatialMixV6(nn.Module):
                            w.float().contiguous(), self.time_faaaa)
         if self.key_norm is not None:
             y = self.key_norm(y)
+        if y.is_cuda and normgate.supported(C, HEAD_SIZE):
+            # per-head GroupNorm and gate in one pass over y (normgate.py)
+            return self.output(normgate.norm_gate(y, g, self.ln_x.weight, self.ln_x.bias, HEAD_SIZE, self.ln_x.eps))
         y = self.ln_x(y.reshape(B * T, C)).view(B, T, C)
         return self.output(y.to(g.dtype) * g)
 

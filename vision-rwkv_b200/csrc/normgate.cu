@@ -1,0 +1,252 @@
+// Normalise-and-gate epilogue of the token-mixing operators, forward and backward, one pass each.
+//
+// Behind Bi-WKV the large backbone applies a LayerNorm over the channels to the operator's output
+// and multiplies by the sigmoid gate before the output projection
+// (classification/mmcls_custom/models/backbones/vrwkv.py:184-186: key_norm, then sr * x); behind
+// WKV6 a GroupNorm with one group per 64-channel head is followed by the SiLU gate
+// (classification/mmcls_custom/models/backbones/vrwkv6.py:133, 205-212: ln_x, then x * g).  With
+// tensor ops that is a normalisation pass (read, write) and a multiply pass (two reads, a write);
+// here out = (normalise(x) * gamma + beta) * gate is one pass that reads x and gate once and writes
+// out, and the backward reads gout, x, gate once and writes gx and ggate; the affine parameters'
+// gradients are accumulated per warp in registers and summed in a fixed order (no atomics).
+//
+// group = C is LayerNorm, group = 64 is the per-head GroupNorm.  One warp per (row, group); a lane
+// holds the channel pairs (64 i + 2 lane, +1) of the group, so a warp reads 256 contiguous bytes per
+// step.  Biased variance in two passes over registers, eps inside the square root, as
+// torch.nn.LayerNorm / GroupNorm compute it.  The gate may be float32 or bfloat16 (the sigmoid or
+// SiLU of a half-precision projection); x, out and the statistics are float32.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "vrwkv_b200.h"
+#include "vrwkv_internal.h"
+
+namespace normgate {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxPairs = 16;          // channel pairs per lane: groups of up to 1024 channels
+constexpr int kMaxGroup = kMaxPairs * 64;
+
+struct Args {
+    int rows, C, G, n_groups, pairs;   // pairs = G / 64
+    float eps;
+    const float* x;
+    const void* gate;
+    const float* gamma;
+    const float* beta;
+    float* out;
+    float* mean;      // (rows, n_groups)
+    float* rstd;
+    // backward
+    const float* gout;
+    float* gx;
+    void* ggate;
+    float* partial;   // [gridDim.x][2][C]
+};
+
+template <bool kHalfGate>
+__device__ __forceinline__ float2 load_gate(const void* gate, size_t at) {
+    if (kHalfGate) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(gate) + at));
+    return *reinterpret_cast<const float2*>(static_cast<const float*>(gate) + at);
+}
+template <bool kHalfGate>
+__device__ __forceinline__ void store_gate(void* gate, size_t at, float2 v) {
+    if (kHalfGate) *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(gate) + at) = __float22bfloat162_rn(v);
+    else *reinterpret_cast<float2*>(static_cast<float*>(gate) + at) = v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+    return v;
+}
+
+template <bool kHalfGate>
+__global__ void __launch_bounds__(kThreads) normgate_forward_kernel(const Args a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long items = static_cast<long long>(a.rows) * a.n_groups;
+    const float inv = 1.f / static_cast<float>(a.G);
+    for (long long item = static_cast<long long>(blockIdx.x) * kWarps + warp; item < items; item += static_cast<long long>(gridDim.x) * kWarps) {
+        const long long row = item / a.n_groups;
+        const int g = static_cast<int>(item - row * a.n_groups);
+        const int c0 = g * a.G + 2 * lane;
+        const size_t base = static_cast<size_t>(row) * a.C + c0;
+        float2 v[kMaxPairs];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i)
+            if (i < a.pairs) {
+                v[i] = *reinterpret_cast<const float2*>(a.x + base + 64 * i);
+                s += v[i].x + v[i].y;
+            }
+        const float mu = warp_sum(s) * inv;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i)
+            if (i < a.pairs) {
+                const float dx = v[i].x - mu, dy = v[i].y - mu;
+                q += dx * dx + dy * dy;
+            }
+        const float rs = rsqrtf(warp_sum(q) * inv + a.eps);
+        if (lane == 0) {
+            a.mean[item] = mu;
+            a.rstd[item] = rs;
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i)
+            if (i < a.pairs) {
+                const int c = c0 + 64 * i;
+                const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c), be = *reinterpret_cast<const float2*>(a.beta + c);
+                const float2 gt = load_gate<kHalfGate>(a.gate, base + 64 * i);
+                float2 o;
+                o.x = ((v[i].x - mu) * rs * ga.x + be.x) * gt.x;
+                o.y = ((v[i].y - mu) * rs * ga.y + be.y) * gt.y;
+                *reinterpret_cast<float2*>(a.out + base + 64 * i) = o;
+            }
+    }
+}
+
+// grid (blocks, n_groups): a warp stays with one group, so that its lanes own the same channels in every
+// row it visits and can keep the parameter gradients in registers
+template <bool kHalfGate>
+__global__ void __launch_bounds__(kThreads) normgate_backward_kernel(const Args a) {
+    __shared__ float red[kWarps][kMaxGroup + 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = blockIdx.y;
+    const int c0 = g * a.G + 2 * lane;
+    const float inv = 1.f / static_cast<float>(a.G);
+    float2 ag[kMaxPairs], ab[kMaxPairs], ga[kMaxPairs], be[kMaxPairs];
+#pragma unroll
+    for (int i = 0; i < kMaxPairs; ++i) {
+        ag[i] = make_float2(0.f, 0.f);
+        ab[i] = make_float2(0.f, 0.f);
+        ga[i] = make_float2(0.f, 0.f);
+        be[i] = make_float2(0.f, 0.f);
+        if (i < a.pairs) {
+            ga[i] = *reinterpret_cast<const float2*>(a.gamma + c0 + 64 * i);
+            be[i] = *reinterpret_cast<const float2*>(a.beta + c0 + 64 * i);
+        }
+    }
+    for (long long row = static_cast<long long>(blockIdx.x) * kWarps + warp; row < a.rows; row += static_cast<long long>(gridDim.x) * kWarps) {
+        const size_t base = static_cast<size_t>(row) * a.C + c0;
+        const float mu = a.mean[row * a.n_groups + g], rs = a.rstd[row * a.n_groups + g];
+        float2 n[kMaxPairs], gn[kMaxPairs];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i)
+            if (i < a.pairs) {
+                const float2 xv = *reinterpret_cast<const float2*>(a.x + base + 64 * i);
+                const float2 go = *reinterpret_cast<const float2*>(a.gout + base + 64 * i);
+                const float2 gt = load_gate<kHalfGate>(a.gate, base + 64 * i);
+                n[i].x = (xv.x - mu) * rs; n[i].y = (xv.y - mu) * rs;
+                const float zx = n[i].x * ga[i].x + be[i].x, zy = n[i].y * ga[i].y + be[i].y;
+                store_gate<kHalfGate>(a.ggate, base + 64 * i, make_float2(go.x * zx, go.y * zy));
+                const float gzx = go.x * gt.x, gzy = go.y * gt.y;
+                ag[i].x += gzx * n[i].x; ag[i].y += gzy * n[i].y;
+                ab[i].x += gzx; ab[i].y += gzy;
+                gn[i].x = gzx * ga[i].x; gn[i].y = gzy * ga[i].y;
+                s1 += gn[i].x + gn[i].y;
+                s2 += gn[i].x * n[i].x + gn[i].y * n[i].y;
+            }
+        s1 = warp_sum(s1) * inv;
+        s2 = warp_sum(s2) * inv;
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i)
+            if (i < a.pairs) {
+                float2 o;
+                o.x = rs * (gn[i].x - s1 - n[i].x * s2);
+                o.y = rs * (gn[i].y - s1 - n[i].y * s2);
+                *reinterpret_cast<float2*>(a.gx + base + 64 * i) = o;
+            }
+    }
+    // the CTA's sums of the two parameter gradients, warps added in index order
+    for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int i = 0; i < kMaxPairs; ++i)
+            if (i < a.pairs) *reinterpret_cast<float2*>(&red[warp][64 * i + 2 * lane]) = which ? ab[i] : ag[i];
+        __syncthreads();
+        for (int c = threadIdx.x; c < a.G; c += kThreads) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) t += red[w][c];
+            a.partial[(static_cast<size_t>(blockIdx.x) * 2 + which) * a.C + g * a.G + c] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// out[which][c] = sum over the CTAs of partial[cta][which][c], in index order
+__global__ void __launch_bounds__(256) normgate_reduce_kernel(const float* __restrict__ partial, int blocks, int C, float* __restrict__ out) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int which = blockIdx.y;
+    if (c >= C) return;
+    float t = 0.f;
+    for (int b = 0; b < blocks; ++b) t += partial[(static_cast<size_t>(b) * 2 + which) * C + c];
+    out[static_cast<size_t>(which) * C + c] = t;
+}
+
+static int check(int rows, int C, int group) {
+    if (rows <= 0 || C <= 0 || group <= 0) return VRWKV_ERR_SHAPE;
+    if (group % 64 != 0 || group > kMaxGroup || C % group != 0) return VRWKV_ERR_UNSUPPORTED;
+    return VRWKV_OK;
+}
+static int backward_blocks(int rows) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long want = (static_cast<long long>(rows) + kWarps - 1) / kWarps;
+    return static_cast<int>(want < 4LL * sms ? (want < 1 ? 1 : want) : 4LL * sms);
+}
+
+}  // namespace normgate
+
+static inline bool ng_misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
+
+extern "C" int vrwkv_normgate_forward_f32(int rows, int C, int group, float eps, const float* x, const void* gate,
+                                          int gate_is_bf16, const float* gamma, const float* beta, float* out,
+                                          float* mean, float* rstd, void* stream) {
+    using namespace normgate;
+    if (int st = check(rows, C, group)) return st;
+    if (!x || !gate || !gamma || !beta || !out || !mean || !rstd) return VRWKV_ERR_NULL;
+    if (ng_misaligned(x, 8) || ng_misaligned(gate, gate_is_bf16 ? 4 : 8) || ng_misaligned(gamma, 8) || ng_misaligned(beta, 8) ||
+        ng_misaligned(out, 8) || ng_misaligned(mean, 4) || ng_misaligned(rstd, 4))
+        return VRWKV_ERR_ALIGNMENT;
+    Args a{};
+    a.rows = rows; a.C = C; a.G = group; a.n_groups = C / group; a.pairs = group / 64; a.eps = eps;
+    a.x = x; a.gate = gate; a.gamma = gamma; a.beta = beta; a.out = out; a.mean = mean; a.rstd = rstd;
+    const long long items = static_cast<long long>(rows) * a.n_groups;
+    const long long want = (items + kWarps - 1) / kWarps;
+    const unsigned grid = static_cast<unsigned>(want < (1LL << 20) ? want : (1LL << 20));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gate_is_bf16) normgate_forward_kernel<true><<<grid, kThreads, 0, s>>>(a);
+    else normgate_forward_kernel<false><<<grid, kThreads, 0, s>>>(a);
+    return record_launches(1);
+}
+
+extern "C" size_t vrwkv_normgate_backward_workspace_bytes(int rows, int C, int group) {
+    if (normgate::check(rows, C, group) != VRWKV_OK) return 0;
+    return static_cast<size_t>(normgate::backward_blocks(rows)) * 2 * C * sizeof(float) + 256;
+}
+
+extern "C" int vrwkv_normgate_backward_f32(int rows, int C, int group, const float* gout, const float* x, const void* gate,
+                                           int gate_is_bf16, const float* gamma, const float* beta, const float* mean,
+                                           const float* rstd, float* gx, void* ggate, float* ggamma_gbeta, void* workspace,
+                                           size_t workspace_bytes, void* stream) {
+    using namespace normgate;
+    if (int st = check(rows, C, group)) return st;
+    if (!gout || !x || !gate || !gamma || !beta || !mean || !rstd || !gx || !ggate || !ggamma_gbeta || !workspace) return VRWKV_ERR_NULL;
+    if (ng_misaligned(gout, 8) || ng_misaligned(x, 8) || ng_misaligned(gate, gate_is_bf16 ? 4 : 8) || ng_misaligned(gamma, 8) ||
+        ng_misaligned(beta, 8) || ng_misaligned(gx, 8) || ng_misaligned(ggate, gate_is_bf16 ? 4 : 8) || ng_misaligned(workspace, 256))
+        return VRWKV_ERR_ALIGNMENT;
+    if (workspace_bytes < vrwkv_normgate_backward_workspace_bytes(rows, C, group)) return VRWKV_ERR_WORKSPACE;
+    Args a{};
+    a.rows = rows; a.C = C; a.G = group; a.n_groups = C / group; a.pairs = group / 64;
+    a.x = x; a.gate = gate; a.gamma = gamma; a.beta = beta; a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd);
+    a.gout = gout; a.gx = gx; a.ggate = ggate; a.partial = static_cast<float*>(workspace);
+    const int blocks = backward_blocks(rows);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid(blocks, a.n_groups);
+    if (gate_is_bf16) normgate_backward_kernel<true><<<grid, kThreads, 0, s>>>(a);
+    else normgate_backward_kernel<false><<<grid, kThreads, 0, s>>>(a);
+    normgate_reduce_kernel<<<dim3((C + 255) / 256, 2), 256, 0, s>>>(a.partial, blocks, C, ggamma_gbeta);
+    return record_launches(2);
+}

@@ -444,3 +444,49 @@ def qshift_mix_backward(x, mixes, gouts, resolution, shift_pixel=1, gamma=0.25, 
                                                torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_qshift_mix_backward_f32")
     return gx, gmix
+
+
+def normgate_forward(x, gate, gamma, beta, group, eps=1e-5):
+    """(out, mean, rstd) with out = (normalise(x) * gamma + beta) * gate over groups of `group` channels of
+    every row of x (..., C): group = C is LayerNorm, group = 64 a GroupNorm with one group per 64-channel head.
+    x, gamma, beta float32; gate float32 or bfloat16, already activated."""
+    dev = _check_inputs((("x", x), ("gamma", gamma), ("beta", beta)))
+    _check_inputs((("gate", gate),), gate.dtype if gate.dtype in (torch.float32, torch.bfloat16) else torch.float32, dev)
+    C = x.shape[-1]
+    if gate.shape != x.shape or gamma.numel() != C or beta.numel() != C:
+        raise RuntimeError("gate must have the shape of x; gamma and beta must hold C values")
+    rows = x.numel() // C if C else 0
+    out = torch.empty_like(x)
+    n_groups = C // group if group and C % group == 0 else 0
+    mean = torch.empty((rows, max(n_groups, 1)), device=dev, dtype=torch.float32)
+    rstd = torch.empty_like(mean)
+    if x.numel() == 0:
+        return out, mean, rstd
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        st = lib.vrwkv_normgate_forward_f32(rows, C, group, float(eps), x.data_ptr(), gate.data_ptr(), int(_is_bf16(gate)),
+                                            gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                            torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_normgate_forward_f32")
+    return out, mean, rstd
+
+
+def normgate_backward(gout, x, gate, gamma, beta, mean, rstd, group):
+    """(gx, ggate, ggamma, gbeta) of `normgate_forward`; ggate has the dtype of gate."""
+    dev = _check_inputs((("gout", gout), ("x", x), ("gamma", gamma), ("beta", beta), ("mean", mean), ("rstd", rstd)))
+    _check_inputs((("gate", gate),), gate.dtype if gate.dtype in (torch.float32, torch.bfloat16) else torch.float32, dev)
+    C = x.shape[-1]
+    rows = x.numel() // C if C else 0
+    gx, ggate = torch.empty_like(x), torch.empty_like(gate)
+    gpar = torch.zeros((2, C), device=dev, dtype=torch.float32)
+    if x.numel() == 0:
+        return gx, ggate, gpar[0], gpar[1]
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_normgate_backward_workspace_bytes(rows, C, group), dev)
+        st = lib.vrwkv_normgate_backward_f32(rows, C, group, gout.data_ptr(), x.data_ptr(), gate.data_ptr(), int(_is_bf16(gate)),
+                                             gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), rstd.data_ptr(), gx.data_ptr(),
+                                             ggate.data_ptr(), gpar.data_ptr(), ws.data_ptr(), ws.numel(),
+                                             torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_normgate_backward_f32")
+    return gx, ggate, gpar[0], gpar[1]
