@@ -61,108 +61,151 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-template <bool kHalfGate>
+// kPairs: channel pairs a lane can hold (>= a.pairs); the kernels are instantiated for 1, 2, 4, 8 and 16 so that a
+// small group does not pay the registers of a large one
+template <bool kHalfGate, int kPairs>
 __global__ void __launch_bounds__(kThreads) normgate_forward_kernel(const Args a) {
+    // items a warp takes per step (more than one was measured slower for 64-channel groups: 0.45 against 0.54 of the
+    // HBM peak; the code keeps the general form)
+    constexpr int kB = 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long items = static_cast<long long>(a.rows) * a.n_groups;
     const float inv = 1.f / static_cast<float>(a.G);
-    for (long long item = static_cast<long long>(blockIdx.x) * kWarps + warp; item < items; item += static_cast<long long>(gridDim.x) * kWarps) {
-        const long long row = item / a.n_groups;
-        const int g = static_cast<int>(item - row * a.n_groups);
-        const int c0 = g * a.G + 2 * lane;
-        const size_t base = static_cast<size_t>(row) * a.C + c0;
-        float2 v[kMaxPairs];
-        float s = 0.f;
+    for (long long first = (static_cast<long long>(blockIdx.x) * kWarps + warp) * kB; first < items;
+         first += static_cast<long long>(gridDim.x) * kWarps * kB) {
+        float2 v[kB][kPairs];
+        size_t base[kB];
+        int c0[kB];
+        float mu[kB], rs[kB];
 #pragma unroll
-        for (int i = 0; i < kMaxPairs; ++i)
-            if (i < a.pairs) {
-                v[i] = *reinterpret_cast<const float2*>(a.x + base + 64 * i);
-                s += v[i].x + v[i].y;
-            }
-        const float mu = warp_sum(s) * inv;
-        float q = 0.f;
+        for (int j = 0; j < kB; ++j) {
+            const long long item = first + j < items ? first + j : items - 1;      // a repeated last item is harmless
+            const long long row = item / a.n_groups;
+            c0[j] = static_cast<int>(item - row * a.n_groups) * a.G + 2 * lane;
+            base[j] = static_cast<size_t>(row) * a.C + c0[j];
+            float s = 0.f;
 #pragma unroll
-        for (int i = 0; i < kMaxPairs; ++i)
-            if (i < a.pairs) {
-                const float dx = v[i].x - mu, dy = v[i].y - mu;
-                q += dx * dx + dy * dy;
+            for (int i = 0; i < kPairs; ++i) {
+                v[j][i] = make_float2(0.f, 0.f);
+                if (i < a.pairs) {
+                    v[j][i] = *reinterpret_cast<const float2*>(a.x + base[j] + 64 * i);
+                    s += v[j][i].x + v[j][i].y;
+                }
             }
-        const float rs = rsqrtf(warp_sum(q) * inv + a.eps);
-        if (lane == 0) {
-            a.mean[item] = mu;
-            a.rstd[item] = rs;
+            mu[j] = s;
         }
 #pragma unroll
-        for (int i = 0; i < kMaxPairs; ++i)
-            if (i < a.pairs) {
-                const int c = c0 + 64 * i;
-                const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c), be = *reinterpret_cast<const float2*>(a.beta + c);
-                const float2 gt = load_gate<kHalfGate>(a.gate, base + 64 * i);
-                float2 o;
-                o.x = ((v[i].x - mu) * rs * ga.x + be.x) * gt.x;
-                o.y = ((v[i].y - mu) * rs * ga.y + be.y) * gt.y;
-                *reinterpret_cast<float2*>(a.out + base + 64 * i) = o;
+        for (int j = 0; j < kB; ++j) mu[j] = warp_sum(mu[j]) * inv;
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            float q = 0.f;
+#pragma unroll
+            for (int i = 0; i < kPairs; ++i)
+                if (i < a.pairs) {
+                    const float dx = v[j][i].x - mu[j], dy = v[j][i].y - mu[j];
+                    q += dx * dx + dy * dy;
+                }
+            rs[j] = q;
+        }
+#pragma unroll
+        for (int j = 0; j < kB; ++j) rs[j] = rsqrtf(warp_sum(rs[j]) * inv + a.eps);
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            if (first + j >= items) break;
+            if (lane == 0) {
+                a.mean[first + j] = mu[j];
+                a.rstd[first + j] = rs[j];
             }
+#pragma unroll
+            for (int i = 0; i < kPairs; ++i)
+                if (i < a.pairs) {
+                    const int c = c0[j] + 64 * i;
+                    const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c), be = *reinterpret_cast<const float2*>(a.beta + c);
+                    const float2 gt = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    float2 o;
+                    o.x = ((v[j][i].x - mu[j]) * rs[j] * ga.x + be.x) * gt.x;
+                    o.y = ((v[j][i].y - mu[j]) * rs[j] * ga.y + be.y) * gt.y;
+                    *reinterpret_cast<float2*>(a.out + base[j] + 64 * i) = o;
+                }
+        }
     }
 }
 
 // grid (blocks, n_groups): a warp stays with one group, so that its lanes own the same channels in every
 // row it visits and can keep the parameter gradients in registers
-template <bool kHalfGate>
+template <bool kHalfGate, int kPairs>
 __global__ void __launch_bounds__(kThreads) normgate_backward_kernel(const Args a) {
-    __shared__ float red[kWarps][kMaxGroup + 32];
+    __shared__ float red[kWarps][kPairs * 64 + 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = blockIdx.y;
     const int c0 = g * a.G + 2 * lane;
     const float inv = 1.f / static_cast<float>(a.G);
-    float2 ag[kMaxPairs], ab[kMaxPairs], ga[kMaxPairs], be[kMaxPairs];
+    // per lane only the two running parameter gradients live in registers across rows; gamma and beta are re-read
+    // (cache hits), and the second sweep over a row reloads what the first one read instead of holding it
+    float2 ag[kPairs], ab[kPairs];
 #pragma unroll
-    for (int i = 0; i < kMaxPairs; ++i) {
+    for (int i = 0; i < kPairs; ++i) {
         ag[i] = make_float2(0.f, 0.f);
         ab[i] = make_float2(0.f, 0.f);
-        ga[i] = make_float2(0.f, 0.f);
-        be[i] = make_float2(0.f, 0.f);
-        if (i < a.pairs) {
-            ga[i] = *reinterpret_cast<const float2*>(a.gamma + c0 + 64 * i);
-            be[i] = *reinterpret_cast<const float2*>(a.beta + c0 + 64 * i);
-        }
     }
-    for (long long row = static_cast<long long>(blockIdx.x) * kWarps + warp; row < a.rows; row += static_cast<long long>(gridDim.x) * kWarps) {
-        const size_t base = static_cast<size_t>(row) * a.C + c0;
-        const float mu = a.mean[row * a.n_groups + g], rs = a.rstd[row * a.n_groups + g];
-        float2 n[kMaxPairs], gn[kMaxPairs];
-        float s1 = 0.f, s2 = 0.f;
+    constexpr int kB = 1;     // rows per step, as in the forward
+    for (long long first = (static_cast<long long>(blockIdx.x) * kWarps + warp) * kB; first < a.rows;
+         first += static_cast<long long>(gridDim.x) * kWarps * kB) {
+        float mu[kB], rs[kB], s1[kB], s2[kB];
+        size_t base[kB];
 #pragma unroll
-        for (int i = 0; i < kMaxPairs; ++i)
-            if (i < a.pairs) {
-                const float2 xv = *reinterpret_cast<const float2*>(a.x + base + 64 * i);
-                const float2 go = *reinterpret_cast<const float2*>(a.gout + base + 64 * i);
-                const float2 gt = load_gate<kHalfGate>(a.gate, base + 64 * i);
-                n[i].x = (xv.x - mu) * rs; n[i].y = (xv.y - mu) * rs;
-                const float zx = n[i].x * ga[i].x + be[i].x, zy = n[i].y * ga[i].y + be[i].y;
-                store_gate<kHalfGate>(a.ggate, base + 64 * i, make_float2(go.x * zx, go.y * zy));
-                const float gzx = go.x * gt.x, gzy = go.y * gt.y;
-                ag[i].x += gzx * n[i].x; ag[i].y += gzy * n[i].y;
-                ab[i].x += gzx; ab[i].y += gzy;
-                gn[i].x = gzx * ga[i].x; gn[i].y = gzy * ga[i].y;
-                s1 += gn[i].x + gn[i].y;
-                s2 += gn[i].x * n[i].x + gn[i].y * n[i].y;
-            }
-        s1 = warp_sum(s1) * inv;
-        s2 = warp_sum(s2) * inv;
+        for (int j = 0; j < kB; ++j) {
+            const bool live = first + j < a.rows;
+            const long long row = live ? first + j : first;
+            base[j] = static_cast<size_t>(row) * a.C + c0;
+            mu[j] = a.mean[row * a.n_groups + g];
+            rs[j] = a.rstd[row * a.n_groups + g];
+            s1[j] = 0.f; s2[j] = 0.f;
+            if (!live) continue;
 #pragma unroll
-        for (int i = 0; i < kMaxPairs; ++i)
-            if (i < a.pairs) {
-                float2 o;
-                o.x = rs * (gn[i].x - s1 - n[i].x * s2);
-                o.y = rs * (gn[i].y - s1 - n[i].y * s2);
-                *reinterpret_cast<float2*>(a.gx + base + 64 * i) = o;
-            }
+            for (int i = 0; i < kPairs; ++i)
+                if (i < a.pairs) {
+                    const float2 xv = *reinterpret_cast<const float2*>(a.x + base[j] + 64 * i);
+                    const float2 go = *reinterpret_cast<const float2*>(a.gout + base[j] + 64 * i);
+                    const float2 gt = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c0 + 64 * i), be = *reinterpret_cast<const float2*>(a.beta + c0 + 64 * i);
+                    const float nx = (xv.x - mu[j]) * rs[j], ny = (xv.y - mu[j]) * rs[j];
+                    store_gate<kHalfGate>(a.ggate, base[j] + 64 * i, make_float2(go.x * (nx * ga.x + be.x), go.y * (ny * ga.y + be.y)));
+                    const float gzx = go.x * gt.x, gzy = go.y * gt.y;
+                    ag[i].x += gzx * nx; ag[i].y += gzy * ny;
+                    ab[i].x += gzx; ab[i].y += gzy;
+                    const float gnx = gzx * ga.x, gny = gzy * ga.y;
+                    s1[j] += gnx + gny;
+                    s2[j] += gnx * nx + gny * ny;
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            s1[j] = warp_sum(s1[j]) * inv;
+            s2[j] = warp_sum(s2[j]) * inv;
+        }
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            if (first + j >= a.rows) break;
+#pragma unroll
+            for (int i = 0; i < kPairs; ++i)
+                if (i < a.pairs) {
+                    const float2 xv = *reinterpret_cast<const float2*>(a.x + base[j] + 64 * i);
+                    const float2 go = *reinterpret_cast<const float2*>(a.gout + base[j] + 64 * i);
+                    const float2 gt = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c0 + 64 * i);
+                    const float nx = (xv.x - mu[j]) * rs[j], ny = (xv.y - mu[j]) * rs[j];
+                    float2 o;
+                    o.x = rs[j] * (go.x * gt.x * ga.x - s1[j] - nx * s2[j]);
+                    o.y = rs[j] * (go.y * gt.y * ga.y - s1[j] - ny * s2[j]);
+                    *reinterpret_cast<float2*>(a.gx + base[j] + 64 * i) = o;
+                }
+        }
     }
     // the CTA's sums of the two parameter gradients, warps added in index order
     for (int which = 0; which < 2; ++which) {
 #pragma unroll
-        for (int i = 0; i < kMaxPairs; ++i)
+        for (int i = 0; i < kPairs; ++i)
             if (i < a.pairs) *reinterpret_cast<float2*>(&red[warp][64 * i + 2 * lane]) = which ? ab[i] : ag[i];
         __syncthreads();
         for (int c = threadIdx.x; c < a.G; c += kThreads) {
@@ -190,9 +233,13 @@ static int check(int rows, int C, int group) {
     if (group % 64 != 0 || group > kMaxGroup || C % group != 0) return VRWKV_ERR_UNSUPPORTED;
     return VRWKV_OK;
 }
-static int backward_blocks(int rows) {
+static int sm_count() {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}
+static int backward_blocks(int rows) {
+    const int sms = sm_count();
     const long long want = (static_cast<long long>(rows) + kWarps - 1) / kWarps;
     return static_cast<int>(want < 4LL * sms ? (want < 1 ? 1 : want) : 4LL * sms);
 }
@@ -215,10 +262,20 @@ extern "C" int vrwkv_normgate_forward_f32(int rows, int C, int group, float eps,
     a.x = x; a.gate = gate; a.gamma = gamma; a.beta = beta; a.out = out; a.mean = mean; a.rstd = rstd;
     const long long items = static_cast<long long>(rows) * a.n_groups;
     const long long want = (items + kWarps - 1) / kWarps;
-    const unsigned grid = static_cast<unsigned>(want < (1LL << 20) ? want : (1LL << 20));
+    const long long cap = 8LL * sm_count();                    // grid-stride loop: a few CTAs per SM, not one per eight items
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (gate_is_bf16) normgate_forward_kernel<true><<<grid, kThreads, 0, s>>>(a);
-    else normgate_forward_kernel<false><<<grid, kThreads, 0, s>>>(a);
+#define NG_FWD(P)                                                                     \
+    do {                                                                              \
+        if (gate_is_bf16) normgate_forward_kernel<true, P><<<grid, kThreads, 0, s>>>(a);  \
+        else normgate_forward_kernel<false, P><<<grid, kThreads, 0, s>>>(a);              \
+    } while (0)
+    if (a.pairs <= 1) NG_FWD(1);
+    else if (a.pairs <= 2) NG_FWD(2);
+    else if (a.pairs <= 4) NG_FWD(4);
+    else if (a.pairs <= 8) NG_FWD(8);
+    else NG_FWD(16);
+#undef NG_FWD
     return record_launches(1);
 }
 
@@ -245,8 +302,17 @@ extern "C" int vrwkv_normgate_backward_f32(int rows, int C, int group, const flo
     const int blocks = backward_blocks(rows);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const dim3 grid(blocks, a.n_groups);
-    if (gate_is_bf16) normgate_backward_kernel<true><<<grid, kThreads, 0, s>>>(a);
-    else normgate_backward_kernel<false><<<grid, kThreads, 0, s>>>(a);
+#define NG_BWD(P)                                                                      \
+    do {                                                                               \
+        if (gate_is_bf16) normgate_backward_kernel<true, P><<<grid, kThreads, 0, s>>>(a);  \
+        else normgate_backward_kernel<false, P><<<grid, kThreads, 0, s>>>(a);              \
+    } while (0)
+    if (a.pairs <= 1) NG_BWD(1);
+    else if (a.pairs <= 2) NG_BWD(2);
+    else if (a.pairs <= 4) NG_BWD(4);
+    else if (a.pairs <= 8) NG_BWD(8);
+    else NG_BWD(16);
+#undef NG_BWD
     normgate_reduce_kernel<<<dim3((C + 255) / 256, 2), 256, 0, s>>>(a.partial, blocks, C, ggamma_gbeta);
     return record_launches(2);
 }

@@ -1316,21 +1316,51 @@ __global__ void __launch_bounds__(N) wkv6_bwd_decay_kernel(const FinArgs a) {
     const int t0 = seg * kSeg, t1 = min(a.T, t0 + kSeg);
     const size_t plane = static_cast<size_t>(a.B) * a.n_seg * C;
     const size_t j = (static_cast<size_t>(b) * a.n_seg + seg) * C + c;
+    // eight tokens' loads are issued before the running sums consume them: the sums are a serial chain, the loads are not
+    constexpr int kU = 8;
+    const size_t i0 = (static_cast<size_t>(b) * a.T + t0) * C + c;
+    const int n = t1 - t0;
     float run = a.tot[j];
-    for (int t = t0; t < t1; ++t) {
-        const size_t i = (static_cast<size_t>(b) * a.T + t) * C + c;
-        const float r = in_ld<kHalfIn>(a.r, i), k = in_ld<kHalfIn>(a.k, i);
-        const float p = r * a.gr_right[i];
-        part[t - t0][lane] = run - p;
-        run += k * a.gk_left[i] - p;
+    for (int s0 = 0; s0 < n; s0 += kU) {
+        float p[kU], q[kU];
+#pragma unroll
+        for (int e = 0; e < kU; ++e) {
+            p[e] = 0.f; q[e] = 0.f;
+            if (s0 + e < n) {
+                const size_t i = i0 + static_cast<size_t>(s0 + e) * C;
+                p[e] = in_ld<kHalfIn>(a.r, i) * a.gr_right[i];
+                q[e] = in_ld<kHalfIn>(a.k, i) * a.gk_left[i];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kU; ++e)
+            if (s0 + e < n) {
+                part[s0 + e][lane] = run - p[e];
+                run += q[e] - p[e];
+            }
     }
     run = a.tot[plane + j];
-    for (int t = t1 - 1; t >= t0; --t) {
-        const size_t i = (static_cast<size_t>(b) * a.T + t) * C + c;
-        const float r = in_ld<kHalfIn>(a.r, i), k = in_ld<kHalfIn>(a.k, i);
-        const float p = r * a.gr_left[i];
-        a.gw[i] = (part[t - t0][lane] + run - p) * -__expf(a.w[i]);
-        run += k * a.gk_right[i] - p;
+    for (int s1 = n; s1 > 0; s1 -= kU) {
+        float p[kU], q[kU], ew[kU];
+#pragma unroll
+        for (int e = 0; e < kU; ++e) {
+            p[e] = 0.f; q[e] = 0.f; ew[e] = 0.f;
+            const int s = s1 - 1 - e;
+            if (s >= 0) {
+                const size_t i = i0 + static_cast<size_t>(s) * C;
+                p[e] = in_ld<kHalfIn>(a.r, i) * a.gr_left[i];
+                q[e] = in_ld<kHalfIn>(a.k, i) * a.gk_right[i];
+                ew[e] = -__expf(a.w[i]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kU; ++e) {
+            const int s = s1 - 1 - e;
+            if (s >= 0) {
+                a.gw[i0 + static_cast<size_t>(s) * C] = (part[s][lane] + run - p[e]) * ew[e];
+                run += q[e] - p[e];
+            }
+        }
     }
 }
 
