@@ -680,8 +680,19 @@ def sec_qshift(cx):
     mixes = [torch.rand(Cq, device=cx.dev, generator=g) for _ in range(3)]
     ms = cx.timed(lambda: ops.qshift_mix_forward(x, mixes, (Hh, Ww)))
     gbs = 16 * x.numel() / (ms * 1e-3) / 1e9
-    return {"ms": ms, "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs), "shape": [Bq, Hh * Ww, Cq],
-            "outputs": 3, "per_gpu": True}
+    out = {"ms": ms, "algorithmic_GBps": gbs, "frac_of_hbm_peak": cx.frac(gbs), "shape": [Bq, Hh * Ww, Cq],
+           "outputs": 3, "per_gpu": True}
+    # the VRWKV6 spatial mix's step: per-head shift + five data-dependent interpolations, bfloat16 offsets:
+    # 4 (x) + 5 * 2 (offsets) + 5 * 4 (outputs) = 34 bytes per element
+    Bd, Hd = 16, 64
+    xd = x[:Bd]
+    maas = [torch.rand(Cq, device=cx.dev, generator=g) for _ in range(5)]
+    ms5 = [torch.randn(Bd, Hd * Hd, Cq, device=cx.dev, generator=g).bfloat16() for _ in range(5)]
+    msd = cx.timed(lambda: ops.qshift_ddlerp_forward(xd, maas, ms5, (Hd, Hd), 1, 64))
+    gbd = 34 * xd.numel() / (msd * 1e-3) / 1e9
+    out["ddlerp_forward"] = {"ms": msd, "algorithmic_GBps": gbd, "frac_of_hbm_peak": cx.frac(gbd), "shape": [Bd, Hd * Hd, Cq],
+                             "outputs": 5, "offsets": "bfloat16"}
+    return out
 
 
 def sec_normgate(cx):

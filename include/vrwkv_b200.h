@@ -250,6 +250,23 @@ int vrwkv_qshift_multihead_mix_backward_f32(int B, int H, int W, int C, int head
                                             const float* const* gout, float* gx, float* const* gmix,
                                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* The per-head shift fused with the data-dependent interpolations of the VRWKV6 spatial mix
+ * (CLS/vrwkv6.py:75-100, 180-193):  out_j = x + (q_shift_multihead(x) - x) * (maa_j[c] + m_j[b,t,c]),
+ * j < n_out <= 5.  maa: n_out device pointers to (C,) float vectors; m: n_out device pointers to
+ * (B, H*W, C) per-token offsets, float32 or (m_is_bf16 != 0) bfloat16 bit patterns, any of them NULL
+ * for "no offset" (n_out = 1 with m[0] = NULL is xxx = x + xx * time_maa_x; n_out = 5 gives the inputs
+ * of the w, k, v, r, g branches).  head_dim: a multiple of 16 that divides C.  The backward returns gx,
+ * the offset gradients gm_j (dtype of m; NULL exactly where m_j is NULL) and the (C,) gradients gmaa_j,
+ * summed in a fixed order.  All tensors 16-byte aligned (bfloat16 ones 8). */
+int vrwkv_qshift_ddlerp_forward_f32(int B, int H, int W, int C, int head_dim, int shift, int n_out, const float* x,
+                                    const float* const* maa, const void* const* m, int m_is_bf16, float* const* out,
+                                    void* stream);
+size_t vrwkv_qshift_ddlerp_backward_workspace_bytes(int B, int H, int W, int C, int n_out);
+int vrwkv_qshift_ddlerp_backward_f32(int B, int H, int W, int C, int head_dim, int shift, int n_out, const float* x,
+                                     const float* const* maa, const void* const* m, int m_is_bf16,
+                                     const float* const* gout, float* gx, void* const* gm, float* const* gmaa,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* Normalise-and-gate epilogue behind the two operators, one pass forward and one backward:
  *   out = (normalise(x) * gamma + beta) * gate
  * over rows of C channels; group == C is the LayerNorm + sigmoid gate behind Bi-WKV in the large

@@ -53,3 +53,11 @@ def q_shift_multihead(x, resolution, shift_pixel=1, head_dim=64):
                         c0 = head * head_dim + part * quarter
                         out[:, h * W + w, c0:c0 + quarter] = x[:, hs * W + ws, c0:c0 + quarter]
     return out
+
+
+def ddlerp(x, maas, offsets, resolution, shift_pixel=1, head_dim=64):
+    """The mixing steps of VRWKV6's spatial mix (classification/mmcls_custom/models/backbones/vrwkv6.py:180-193):
+    xx = q_shift_multihead(x) - x, then x + xx * (maa + m) per output; an offset of None stands for the
+    first step, xxx = x + xx * time_maa_x."""
+    xx = q_shift_multihead(x, resolution, shift_pixel, head_dim) - x
+    return [x + xx * (a if m is None else a + m) for a, m in zip(maas, offsets)]

@@ -103,3 +103,48 @@ def test_per_head_shift_rejects_bad_head_size(cuda_device):
     lib = _lib.load()
     assert lib.vrwkv_qshift_multihead_mix_forward_f32(1, 2, 2, 96, 64, 1, 1, 0, 0, 0, 0) == 1      # 64 does not divide 96
     assert lib.vrwkv_qshift_multihead_mix_forward_f32(1, 2, 2, 60, 6, 1, 1, 0, 0, 0, 0) == 1       # not a multiple of 4
+
+
+DDLERP_CASES = [(2, 14, 14, 128, 64, 1, 5), (1, 5, 7, 64, 64, 1, 1), (2, 3, 4, 96, 32, 2, 3), (1, 8, 8, 768, 64, 1, 5)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,H,W,C,head_dim,s,n", DDLERP_CASES)
+@pytest.mark.parametrize("m_dtype", [torch.float32, torch.bfloat16])
+def test_fused_data_dependent_mix_matches_oracle(cuda_device, B, H, W, C, head_dim, s, n, m_dtype):
+    """Shift + n data-dependent interpolations of the VRWKV6 spatial mix, forward and all gradients; the first
+    output has no per-token offset when n is odd (the xxx = x + xx * maa_x step)."""
+    from vision_rwkv_b200.qshift import qshift_ddlerp
+    g = torch.Generator().manual_seed(B * 100 + C + n)
+    x = torch.randn(B, H * W, C, generator=g, dtype=torch.float64)
+    maas = [torch.rand(1, 1, C, generator=g, dtype=torch.float64) for _ in range(n)]
+    ms = [None if (j == 0 and n % 2) else (0.3 * torch.randn(B, H * W, C, generator=g, dtype=torch.float64)).to(m_dtype).double()
+          for j in range(n)]
+    gouts = [torch.randn(B, H * W, C, generator=g, dtype=torch.float64) for _ in range(n)]
+    rx = x.clone().requires_grad_(True)
+    rmaas = [a.clone().requires_grad_(True) for a in maas]
+    rms = [None if m is None else m.clone().requires_grad_(True) for m in ms]
+    ref = O.ddlerp(rx, [a.reshape(-1) for a in rmaas], rms, (H, W), s, head_dim)
+    torch.autograd.backward(ref, gouts)
+    dx = x.float().to(cuda_device).requires_grad_(True)
+    dmaas = [a.float().to(cuda_device).requires_grad_(True) for a in maas]
+    dms = [None if m is None else m.to(m_dtype).to(cuda_device).requires_grad_(True) for m in ms]
+    outs = qshift_ddlerp(dx, dmaas, dms, (H, W), s, head_dim)
+    torch.autograd.backward(outs, [go.float().to(cuda_device) for go in gouts])
+    tol_m = 1e-2 if m_dtype == torch.bfloat16 else 1e-5
+    for o, r in zip(outs, ref):
+        assert o.dtype == torch.float32 and rel_err(o, r.detach()) <= 1e-5
+    assert rel_err(dx.grad, rx.grad) <= 1e-5
+    for a, r in zip(dmaas, rmaas):
+        assert a.grad.shape == a.shape and rel_err(a.grad, r.grad) <= 2e-5
+    for m, r in zip(dms, rms):
+        if m is not None:
+            assert m.grad.dtype == m_dtype and rel_err(m.grad.float(), r.grad) <= tol_m
+
+
+@pytest.mark.gpu
+def test_data_dependent_mix_rejects_bad_head_size(cuda_device):
+    from vision_rwkv_b200 import ops
+    x = torch.randn(1, 4, 72, device=cuda_device)
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ops.qshift_ddlerp_forward(x, [torch.rand(72, device=cuda_device)], [None], (2, 2), 1, 24)

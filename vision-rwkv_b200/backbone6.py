@@ -22,7 +22,7 @@ import torch.utils.checkpoint as cp
 
 from .backbone import _PatchEmbed, _ramp
 from . import normgate
-from .qshift import qshift_mix
+from .qshift import qshift_ddlerp, qshift_mix
 from .vrwkv6 import HEAD_SIZE, RUN_CUDA_RWKV6
 
 MIX_RANK = 32       # width of the low-rank branch that produces the five mixing offsets
@@ -76,15 +76,27 @@ class SpatialMixV6(nn.Module):
 
     def forward(self, x, resolution):
         B, T, C = x.shape
-        xx = q_shift_multihead(x, self.shift_pixel, resolution) - x
+        fused = x.is_cuda and C % HEAD_SIZE == 0 and self.shift_pixel > 0
+        if fused:
+            # the shift and every interpolation in two passes over x (qshift.qshift_ddlerp)
+            (xxx,) = qshift_ddlerp(x, [self.time_maa_x], [None], resolution, self.shift_pixel, HEAD_SIZE)
+        else:
+            xx = q_shift_multihead(x, self.shift_pixel, resolution) - x
+            xxx = x + xx * self.time_maa_x
         # five data-dependent mixing offsets from one low-rank branch
-        low = torch.tanh((x + xx * self.time_maa_x) @ self.time_maa_w1).view(B * T, 5, MIX_RANK).transpose(0, 1)
+        low = torch.tanh(xxx @ self.time_maa_w1).view(B * T, 5, MIX_RANK).transpose(0, 1)
         mw, mk, mv, mr, mg = torch.bmm(low, self.time_maa_w2).view(5, B, T, C).unbind(0)
-        r = self.receptance(x + xx * (self.time_maa_r + mr))
-        k = self.key(x + xx * (self.time_maa_k + mk))
-        v = self.value(x + xx * (self.time_maa_v + mv))
-        g = F.silu(self.gate(x + xx * (self.time_maa_g + mg)))
-        xw = x + xx * (self.time_maa_w + mw)
+        if fused:
+            xw, xk, xv, xr, xg = qshift_ddlerp(
+                x, [self.time_maa_w, self.time_maa_k, self.time_maa_v, self.time_maa_r, self.time_maa_g],
+                [mw, mk, mv, mr, mg], resolution, self.shift_pixel, HEAD_SIZE)
+        else:
+            xw, xk, xv, xr, xg = (x + xx * (maa + m) for maa, m in (
+                (self.time_maa_w, mw), (self.time_maa_k, mk), (self.time_maa_v, mv), (self.time_maa_r, mr), (self.time_maa_g, mg)))
+        r = self.receptance(xr)
+        k = self.key(xk)
+        v = self.value(xv)
+        g = F.silu(self.gate(xg))
         w = self.time_decay + torch.tanh(xw @ self.time_decay_w1) @ self.time_decay_w2
         y = RUN_CUDA_RWKV6(B, T, C, self.n_head, r.contiguous(), k.contiguous(), v.contiguous(),
                            w.float().contiguous(), self.time_faaaa)

@@ -490,3 +490,71 @@ def normgate_backward(gout, x, gate, gamma, beta, mean, rstd, group):
                                              torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_normgate_backward_f32")
     return gx, ggate, gpar[0], gpar[1]
+
+
+def _ptr_array_or_null(tensors):
+    return (ctypes.c_void_p * len(tensors))(*[None if t is None else t.data_ptr() for t in tensors])
+
+
+def _ddlerp_args(x, maas, ms, resolution, head_dim):
+    if x.dim() != 3:
+        raise RuntimeError(f"x must be (B, T, C), got {tuple(x.shape)}")
+    B, T, C = x.shape
+    H, W = resolution
+    if H * W != T:
+        raise RuntimeError(f"patch resolution {H}x{W} does not match T={T}")
+    if not 1 <= len(maas) <= 5 or len(ms) != len(maas):
+        raise RuntimeError("between one and five mix vectors, and as many offsets (None for no offset)")
+    if head_dim % 16 or C % head_dim:
+        raise RuntimeError(f"head_dim={head_dim} must be a multiple of 16 that divides C={C}")
+    given = [m for m in ms if m is not None]
+    half = bool(given) and given[0].dtype == torch.bfloat16
+    for m in given:
+        if m.shape != x.shape or m.dtype != (torch.bfloat16 if half else torch.float32):
+            raise RuntimeError("offsets must have the shape of x and one common dtype (float32 or bfloat16)")
+    for a in maas:
+        if a.numel() != C:
+            raise RuntimeError(f"mix vectors must hold C={C} values")
+    return B, H, W, C, half
+
+
+def qshift_ddlerp_forward(x, maas, ms, resolution, shift_pixel=1, head_dim=64):
+    """[x + (q_shift_multihead(x) - x) * (maa + m) for maa, m in zip(maas, ms)], one fused pass; m may be None."""
+    given = [m for m in ms if m is not None]
+    dev = _check_inputs([("x", x)] + [(f"maa{i}", a) for i, a in enumerate(maas)])
+    if given:
+        _check_inputs([(f"m{i}", m) for i, m in enumerate(given)], given[0].dtype, dev)
+    B, H, W, C, half = _ddlerp_args(x, maas, ms, resolution, head_dim)
+    outs = [torch.empty_like(x) for _ in maas]
+    if x.numel() == 0:
+        return outs
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        st = lib.vrwkv_qshift_ddlerp_forward_f32(B, H, W, C, head_dim, shift_pixel, len(maas), x.data_ptr(), _ptr_array(maas),
+                                                 _ptr_array_or_null(ms), int(half), _ptr_array(outs),
+                                                 torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_qshift_ddlerp_forward_f32")
+    return outs
+
+
+def qshift_ddlerp_backward(x, maas, ms, gouts, resolution, shift_pixel=1, head_dim=64):
+    """(gx, [gm or None], [gmaa]) of `qshift_ddlerp_forward`."""
+    given = [m for m in ms if m is not None]
+    dev = _check_inputs([("x", x)] + [(f"maa{i}", a) for i, a in enumerate(maas)] + [(f"gout{i}", g) for i, g in enumerate(gouts)])
+    if given:
+        _check_inputs([(f"m{i}", m) for i, m in enumerate(given)], given[0].dtype, dev)
+    B, H, W, C, half = _ddlerp_args(x, maas, ms, resolution, head_dim)
+    gx = torch.empty_like(x)
+    gms = [None if m is None else torch.empty_like(m) for m in ms]
+    gmaas = [torch.zeros(C, device=dev, dtype=torch.float32) for _ in maas]
+    if x.numel() == 0:
+        return gx, gms, gmaas
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.vrwkv_qshift_ddlerp_backward_workspace_bytes(B, H, W, C, len(maas)), dev)
+        st = lib.vrwkv_qshift_ddlerp_backward_f32(B, H, W, C, head_dim, shift_pixel, len(maas), x.data_ptr(), _ptr_array(maas),
+                                                  _ptr_array_or_null(ms), int(half), _ptr_array(gouts), gx.data_ptr(),
+                                                  _ptr_array_or_null(gms), _ptr_array(gmaas), ws.data_ptr(), ws.numel(),
+                                                  torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "vrwkv_qshift_ddlerp_backward_f32")
+    return gx, gms, gmaas
