@@ -721,7 +721,7 @@ def sec_normgate(cx):
 def side_measurements(cx, hl, args):
     """Every secondary measurement by name; one that raises leaves its message in place of its numbers."""
     table = [
-        ("other_pair", lambda: sec_other_pair(cx, hl, args.saved)),
+        ("recompute_pair" if args.saved else "saved_pair", lambda: sec_other_pair(cx, hl, args.saved)),
         ("autograd_surface", lambda: sec_autograd_surface(cx, hl)),
         ("strong_scaling_b64", lambda: sec_strong_scaling(cx, hl, args.strong_batch)),
         ("biwkv_bf16_fwd_bwd", lambda: sec_biwkv_bf16(cx, hl)),
@@ -736,7 +736,7 @@ def side_measurements(cx, hl, args):
         ("qshift_mix_forward", lambda: sec_qshift(cx)),
         ("normgate", lambda: sec_normgate(cx)),
     ]
-    needs_headline = {"other_pair", "autograd_surface", "strong_scaling_b64", "biwkv_bf16_fwd_bwd"}
+    needs_headline = {"saved_pair", "recompute_pair", "autograd_surface", "strong_scaling_b64", "biwkv_bf16_fwd_bwd"}
     out = {"timing": f"each figure: CUDA events around >= {cx.min_ms:.0f} ms of back-to-back calls after warm-up, max over ranks"}
     freed = False
     for name, fn in table:
