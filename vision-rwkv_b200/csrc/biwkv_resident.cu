@@ -181,6 +181,7 @@ __device__ __forceinline__ void st_async1(uint32_t addr, float v, uint32_t bar) 
 // workspace's status block.  Compiled out otherwise.
 #ifdef VRWKV_TIMELINE
 constexpr int kTlCtas = 64, kTlMarks = 32;
+__device__ long long* g_tl_base = nullptr;      // where the marks go; unset: behind the status block
 #define TL_MARK(m)                                                                                         \
     do {                                                                                                   \
         if (tl_slot >= 0 && lane == 0 && (warp == 0 || warp == 5))                                          \
@@ -812,7 +813,7 @@ biwkv_resident_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     c.withhold = c.rank == p.withhold_rank;
 
 #ifdef VRWKV_TIMELINE
-    long long* tl_base = reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.status) + 256);
+    long long* tl_base = g_tl_base ? g_tl_base : reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(p.status) + 256);
     int tl_slot = -1;
     {
         const int mid = (static_cast<int>(gridDim.x) / 2 / p.cluster) * p.cluster;
