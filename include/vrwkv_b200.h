@@ -272,18 +272,19 @@ int vrwkv_qshift_ddlerp_backward_f32(int B, int H, int W, int C, int head_dim, i
  * over rows of C channels; group == C is the LayerNorm + sigmoid gate behind Bi-WKV in the large
  * backbone (key_norm, then sr * x: CLS/vrwkv.py:184-186), group == 64 the per-head GroupNorm + SiLU
  * gate behind WKV6 (ln_x, then x * g: CLS/vrwkv6.py:133, 205-212).  The reference runs them as a
- * normalisation pass and a multiply pass.  `gate` holds the already activated gate, float32 or (with
- * gate_is_bf16 != 0) bfloat16 bit patterns; x, out, gamma, beta float32; mean and rstd receive
+ * normalisation pass and a multiply pass (and an activation pass before them).  `gate` holds, float32 or
+ * (gate_is_bf16 != 0) bfloat16 bit patterns, the gate itself (gate_act 0), or the projection whose sigmoid
+ * (gate_act 1) or SiLU (gate_act 2) is the gate - the backward then returns the gradient of that projection; x, out, gamma, beta float32; mean and rstd receive
  * rows * C / group floats each for the backward.  group must be a multiple of 64, at most 1024, and
  * divide C (else VRWKV_ERR_UNSUPPORTED); pointers 8-byte aligned.  Biased variance, eps inside the
  * square root, as torch.nn.LayerNorm / GroupNorm.  The backward returns gx, ggate (dtype of gate) and
  * ggamma | gbeta as one (2, C) float buffer, summed in a fixed order. */
 int vrwkv_normgate_forward_f32(int rows, int C, int group, float eps, const float* x, const void* gate,
-                               int gate_is_bf16, const float* gamma, const float* beta, float* out,
+                               int gate_is_bf16, int gate_act, const float* gamma, const float* beta, float* out,
                                float* mean, float* rstd, void* stream);
 size_t vrwkv_normgate_backward_workspace_bytes(int rows, int C, int group);
 int vrwkv_normgate_backward_f32(int rows, int C, int group, const float* gout, const float* x, const void* gate,
-                                int gate_is_bf16, const float* gamma, const float* beta, const float* mean,
+                                int gate_is_bf16, int gate_act, const float* gamma, const float* beta, const float* mean,
                                 const float* rstd, float* gx, void* ggate, float* ggamma_gbeta, void* workspace,
                                 size_t workspace_bytes, void* stream);
 

@@ -11,7 +11,11 @@ from __future__ import annotations
 import torch
 
 
-def norm_gate(x, gate, weight, bias, group, eps=1e-5):
+def norm_gate(x, gate, weight, bias, group, eps=1e-5, act=None):
+    if act == "sigmoid":
+        gate = torch.sigmoid(gate)          # sr = torch.sigmoid(r), vrwkv.py:173
+    elif act == "silu":
+        gate = torch.nn.functional.silu(gate)      # g = F.silu(self.gate(xg)), vrwkv6.py:198
     C = x.shape[-1]
     rows = x.reshape(-1, C // group, group)
     mu = rows.mean(dim=-1, keepdim=True)

@@ -35,17 +35,20 @@ CASES = [(2, 196, 1024, 1024), (3, 50, 768, 64), (1, 1, 64, 64), (2, 33, 192, 19
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,T,C,group", CASES)
 @pytest.mark.parametrize("gate_dtype", [torch.float32, torch.bfloat16])
-def test_fused_epilogue_matches_oracle(cuda_device, B, T, C, group, gate_dtype):
+@pytest.mark.parametrize("act", [None, "sigmoid", "silu"])
+def test_fused_epilogue_matches_oracle(cuda_device, B, T, C, group, gate_dtype, act):
     from vision_rwkv_b200.normgate import norm_gate, supported
     assert supported(C, group)
     x, gate, weight, bias, gout = inputs(B, T, C, seed=T + C)
+    if act is not None:
+        gate = torch.logit(gate) * 1.5                               # a projection's output: both signs, a few units wide
     gate = gate.to(gate_dtype).double()                              # the oracle sees the values the kernel sees
     ref_leaves = [t.clone().requires_grad_(True) for t in (x, gate, weight, bias)]
-    ref = O.norm_gate(*ref_leaves, group)
+    ref = O.norm_gate(*ref_leaves, group, act=act)
     ref.backward(gout)
     leaves = [x.float().to(cuda_device).requires_grad_(True), gate.to(gate_dtype).to(cuda_device).requires_grad_(True),
               weight.float().to(cuda_device).requires_grad_(True), bias.float().to(cuda_device).requires_grad_(True)]
-    out = norm_gate(*leaves, group)
+    out = norm_gate(*leaves, group, act=act)
     assert out.dtype == torch.float32
     out.backward(gout.float().to(cuda_device))
     assert rel_err(out, ref) <= 1e-5

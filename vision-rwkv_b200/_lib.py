@@ -47,9 +47,9 @@ SIGNATURES = {
     "vrwkv_qshift_ddlerp_forward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 3 + [_c_int] + [_ptr] * 2),
     "vrwkv_qshift_ddlerp_backward_workspace_bytes": (_c_size_t, [_c_int] * 5),
     "vrwkv_qshift_ddlerp_backward_f32": (_c_int, [_c_int] * 7 + [_ptr] * 3 + [_c_int] + [_ptr] * 4 + [_ptr, _c_size_t, _ptr]),
-    "vrwkv_normgate_forward_f32": (_c_int, [_c_int] * 3 + [ctypes.c_float] + [_ptr] * 2 + [_c_int] + [_ptr] * 5 + [_ptr]),
+    "vrwkv_normgate_forward_f32": (_c_int, [_c_int] * 3 + [ctypes.c_float] + [_ptr] * 2 + [_c_int] * 2 + [_ptr] * 5 + [_ptr]),
     "vrwkv_normgate_backward_workspace_bytes": (_c_size_t, [_c_int] * 3),
-    "vrwkv_normgate_backward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 3 + [_c_int] + [_ptr] * 7 + [_ptr, _c_size_t, _ptr]),
+    "vrwkv_normgate_backward_f32": (_c_int, [_c_int] * 3 + [_ptr] * 3 + [_c_int] * 2 + [_ptr] * 7 + [_ptr, _c_size_t, _ptr]),
 }
 
 _lib = None

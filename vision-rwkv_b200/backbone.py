@@ -56,12 +56,14 @@ class SpatialMix(nn.Module):
         else:
             xk = xv = xr = x
         k, v = self.key(xk), self.value(xv)
-        sr = torch.sigmoid(self.receptance(xr))
+        r = self.receptance(xr)
         y = RUN_CUDA(self.spatial_decay / T, self.spatial_first / T, k, v)
+        if self.key_norm is not None and y.is_cuda and normgate.supported(y.shape[-1], y.shape[-1]):
+            # LayerNorm, sigmoid and gate in one pass over y (normgate.py)
+            return self.output(normgate.norm_gate(y, r, self.key_norm.weight, self.key_norm.bias, y.shape[-1],
+                                                  self.key_norm.eps, act="sigmoid"))
+        sr = torch.sigmoid(r)
         if self.key_norm is not None:
-            if y.is_cuda and normgate.supported(y.shape[-1], y.shape[-1]):
-                # LayerNorm and gate in one pass over y (normgate.py)
-                return self.output(normgate.norm_gate(y, sr, self.key_norm.weight, self.key_norm.bias, y.shape[-1], self.key_norm.eps))
             y = self.key_norm(y)
         return self.output(sr * y.to(sr.dtype))
 

@@ -96,15 +96,16 @@ class SpatialMixV6(nn.Module):
         r = self.receptance(xr)
         k = self.key(xk)
         v = self.value(xv)
-        g = F.silu(self.gate(xg))
+        g_raw = self.gate(xg)
         w = self.time_decay + torch.tanh(xw @ self.time_decay_w1) @ self.time_decay_w2
         y = RUN_CUDA_RWKV6(B, T, C, self.n_head, r.contiguous(), k.contiguous(), v.contiguous(),
                            w.float().contiguous(), self.time_faaaa)
         if self.key_norm is not None:
             y = self.key_norm(y)
         if y.is_cuda and normgate.supported(C, HEAD_SIZE):
-            # per-head GroupNorm and gate in one pass over y (normgate.py)
-            return self.output(normgate.norm_gate(y, g, self.ln_x.weight, self.ln_x.bias, HEAD_SIZE, self.ln_x.eps))
+            # per-head GroupNorm, SiLU and gate in one pass over y (normgate.py)
+            return self.output(normgate.norm_gate(y, g_raw, self.ln_x.weight, self.ln_x.bias, HEAD_SIZE, self.ln_x.eps, act="silu"))
+        g = F.silu(g_raw)
         y = self.ln_x(y.reshape(B * T, C)).view(B, T, C)
         return self.output(y.to(g.dtype) * g)
 

@@ -13,8 +13,9 @@
 // group = C is LayerNorm, group = 64 is the per-head GroupNorm.  One warp per (row, group); a lane
 // holds the channel pairs (64 i + 2 lane, +1) of the group, so a warp reads 256 contiguous bytes per
 // step.  Biased variance in two passes over registers, eps inside the square root, as
-// torch.nn.LayerNorm / GroupNorm compute it.  The gate may be float32 or bfloat16 (the sigmoid or
-// SiLU of a half-precision projection); x, out and the statistics are float32.
+// torch.nn.LayerNorm / GroupNorm compute it.  `gate` may hold the gate itself or the projection it is the
+// sigmoid / SiLU of (then the activation and its derivative are applied here too, one more pass saved), in
+// float32 or bfloat16; x, out and the statistics are float32.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <cstdint>
@@ -30,6 +31,7 @@ constexpr int kMaxGroup = kMaxPairs * 64;
 
 struct Args {
     int rows, C, G, n_groups, pairs;   // pairs = G / 64
+    int act;                           // what `gate` holds: 0 the gate itself, 1 the input of a sigmoid, 2 the input of a SiLU
     float eps;
     const float* x;
     const void* gate;
@@ -54,6 +56,17 @@ template <bool kHalfGate>
 __device__ __forceinline__ void store_gate(void* gate, size_t at, float2 v) {
     if (kHalfGate) *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(gate) + at) = __float22bfloat162_rn(v);
     else *reinterpret_cast<float2*>(static_cast<float*>(gate) + at) = v;
+}
+// the gate from what was loaded (act as in Args), and its derivative with respect to what was loaded
+__device__ __forceinline__ float gate_value(float x, int act) {
+    if (act == 0) return x;
+    const float s = 1.f / (1.f + __expf(-x));
+    return act == 1 ? s : x * s;
+}
+__device__ __forceinline__ float gate_slope(float x, int act) {
+    if (act == 0) return 1.f;
+    const float s = 1.f / (1.f + __expf(-x));
+    return act == 1 ? s * (1.f - s) : s * (1.f + x * (1.f - s));
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -121,10 +134,10 @@ __global__ void __launch_bounds__(kThreads) normgate_forward_kernel(const Args a
                 if (i < a.pairs) {
                     const int c = c0[j] + 64 * i;
                     const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c), be = *reinterpret_cast<const float2*>(a.beta + c);
-                    const float2 gt = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 raw = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
                     float2 o;
-                    o.x = ((v[j][i].x - mu[j]) * rs[j] * ga.x + be.x) * gt.x;
-                    o.y = ((v[j][i].y - mu[j]) * rs[j] * ga.y + be.y) * gt.y;
+                    o.x = ((v[j][i].x - mu[j]) * rs[j] * ga.x + be.x) * gate_value(raw.x, a.act);
+                    o.y = ((v[j][i].y - mu[j]) * rs[j] * ga.y + be.y) * gate_value(raw.y, a.act);
                     *reinterpret_cast<float2*>(a.out + base[j] + 64 * i) = o;
                 }
         }
@@ -167,10 +180,12 @@ __global__ void __launch_bounds__(kThreads) normgate_backward_kernel(const Args 
                 if (i < a.pairs) {
                     const float2 xv = *reinterpret_cast<const float2*>(a.x + base[j] + 64 * i);
                     const float2 go = *reinterpret_cast<const float2*>(a.gout + base[j] + 64 * i);
-                    const float2 gt = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 raw = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 gt = make_float2(gate_value(raw.x, a.act), gate_value(raw.y, a.act));
                     const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c0 + 64 * i), be = *reinterpret_cast<const float2*>(a.beta + c0 + 64 * i);
                     const float nx = (xv.x - mu[j]) * rs[j], ny = (xv.y - mu[j]) * rs[j];
-                    store_gate<kHalfGate>(a.ggate, base[j] + 64 * i, make_float2(go.x * (nx * ga.x + be.x), go.y * (ny * ga.y + be.y)));
+                    store_gate<kHalfGate>(a.ggate, base[j] + 64 * i, make_float2(go.x * (nx * ga.x + be.x) * gate_slope(raw.x, a.act),
+                                                                                  go.y * (ny * ga.y + be.y) * gate_slope(raw.y, a.act)));
                     const float gzx = go.x * gt.x, gzy = go.y * gt.y;
                     ag[i].x += gzx * nx; ag[i].y += gzy * ny;
                     ab[i].x += gzx; ab[i].y += gzy;
@@ -192,7 +207,8 @@ __global__ void __launch_bounds__(kThreads) normgate_backward_kernel(const Args 
                 if (i < a.pairs) {
                     const float2 xv = *reinterpret_cast<const float2*>(a.x + base[j] + 64 * i);
                     const float2 go = *reinterpret_cast<const float2*>(a.gout + base[j] + 64 * i);
-                    const float2 gt = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 raw = load_gate<kHalfGate>(a.gate, base[j] + 64 * i);
+                    const float2 gt = make_float2(gate_value(raw.x, a.act), gate_value(raw.y, a.act));
                     const float2 ga = *reinterpret_cast<const float2*>(a.gamma + c0 + 64 * i);
                     const float nx = (xv.x - mu[j]) * rs[j], ny = (xv.y - mu[j]) * rs[j];
                     float2 o;
@@ -249,16 +265,17 @@ static int backward_blocks(int rows) {
 static inline bool ng_misaligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
 extern "C" int vrwkv_normgate_forward_f32(int rows, int C, int group, float eps, const float* x, const void* gate,
-                                          int gate_is_bf16, const float* gamma, const float* beta, float* out,
+                                          int gate_is_bf16, int gate_act, const float* gamma, const float* beta, float* out,
                                           float* mean, float* rstd, void* stream) {
     using namespace normgate;
     if (int st = check(rows, C, group)) return st;
     if (!x || !gate || !gamma || !beta || !out || !mean || !rstd) return VRWKV_ERR_NULL;
+    if (gate_act < 0 || gate_act > 2) return VRWKV_ERR_SHAPE;
     if (ng_misaligned(x, 8) || ng_misaligned(gate, gate_is_bf16 ? 4 : 8) || ng_misaligned(gamma, 8) || ng_misaligned(beta, 8) ||
         ng_misaligned(out, 8) || ng_misaligned(mean, 4) || ng_misaligned(rstd, 4))
         return VRWKV_ERR_ALIGNMENT;
     Args a{};
-    a.rows = rows; a.C = C; a.G = group; a.n_groups = C / group; a.pairs = group / 64; a.eps = eps;
+    a.rows = rows; a.C = C; a.G = group; a.n_groups = C / group; a.pairs = group / 64; a.eps = eps; a.act = gate_act;
     a.x = x; a.gate = gate; a.gamma = gamma; a.beta = beta; a.out = out; a.mean = mean; a.rstd = rstd;
     const long long items = static_cast<long long>(rows) * a.n_groups;
     const long long want = (items + kWarps - 1) / kWarps;
@@ -285,7 +302,7 @@ extern "C" size_t vrwkv_normgate_backward_workspace_bytes(int rows, int C, int g
 }
 
 extern "C" int vrwkv_normgate_backward_f32(int rows, int C, int group, const float* gout, const float* x, const void* gate,
-                                           int gate_is_bf16, const float* gamma, const float* beta, const float* mean,
+                                           int gate_is_bf16, int gate_act, const float* gamma, const float* beta, const float* mean,
                                            const float* rstd, float* gx, void* ggate, float* ggamma_gbeta, void* workspace,
                                            size_t workspace_bytes, void* stream) {
     using namespace normgate;
@@ -295,8 +312,9 @@ extern "C" int vrwkv_normgate_backward_f32(int rows, int C, int group, const flo
         ng_misaligned(beta, 8) || ng_misaligned(gx, 8) || ng_misaligned(ggate, gate_is_bf16 ? 4 : 8) || ng_misaligned(workspace, 256))
         return VRWKV_ERR_ALIGNMENT;
     if (workspace_bytes < vrwkv_normgate_backward_workspace_bytes(rows, C, group)) return VRWKV_ERR_WORKSPACE;
+    if (gate_act < 0 || gate_act > 2) return VRWKV_ERR_SHAPE;
     Args a{};
-    a.rows = rows; a.C = C; a.G = group; a.n_groups = C / group; a.pairs = group / 64;
+    a.rows = rows; a.C = C; a.G = group; a.n_groups = C / group; a.pairs = group / 64; a.act = gate_act;
     a.x = x; a.gate = gate; a.gamma = gamma; a.beta = beta; a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd);
     a.gout = gout; a.gx = gx; a.ggate = ggate; a.partial = static_cast<float*>(workspace);
     const int blocks = backward_blocks(rows);

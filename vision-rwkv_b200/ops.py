@@ -446,10 +446,14 @@ def qshift_mix_backward(x, mixes, gouts, resolution, shift_pixel=1, gamma=0.25, 
     return gx, gmix
 
 
-def normgate_forward(x, gate, gamma, beta, group, eps=1e-5):
+GATE_ACTIVATIONS = {None: 0, "none": 0, "sigmoid": 1, "silu": 2}
+
+
+def normgate_forward(x, gate, gamma, beta, group, eps=1e-5, act=None):
     """(out, mean, rstd) with out = (normalise(x) * gamma + beta) * gate over groups of `group` channels of
     every row of x (..., C): group = C is LayerNorm, group = 64 a GroupNorm with one group per 64-channel head.
-    x, gamma, beta float32; gate float32 or bfloat16, already activated."""
+    x, gamma, beta float32; gate float32 or bfloat16: the gate itself, or with act = "sigmoid" / "silu" the projection
+    that activation is applied to."""
     dev = _check_inputs((("x", x), ("gamma", gamma), ("beta", beta)))
     _check_inputs((("gate", gate),), gate.dtype if gate.dtype in (torch.float32, torch.bfloat16) else torch.float32, dev)
     C = x.shape[-1]
@@ -465,14 +469,15 @@ def normgate_forward(x, gate, gamma, beta, group, eps=1e-5):
     lib = _lib.load()
     with torch.cuda.device(dev):
         st = lib.vrwkv_normgate_forward_f32(rows, C, group, float(eps), x.data_ptr(), gate.data_ptr(), int(_is_bf16(gate)),
-                                            gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                            GATE_ACTIVATIONS[act], gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                             torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_normgate_forward_f32")
     return out, mean, rstd
 
 
-def normgate_backward(gout, x, gate, gamma, beta, mean, rstd, group):
-    """(gx, ggate, ggamma, gbeta) of `normgate_forward`; ggate has the dtype of gate."""
+def normgate_backward(gout, x, gate, gamma, beta, mean, rstd, group, act=None):
+    """(gx, ggate, ggamma, gbeta) of `normgate_forward`; ggate has the dtype of gate (with `act`: the gradient of the
+    projection the activation is applied to)."""
     dev = _check_inputs((("gout", gout), ("x", x), ("gamma", gamma), ("beta", beta), ("mean", mean), ("rstd", rstd)))
     _check_inputs((("gate", gate),), gate.dtype if gate.dtype in (torch.float32, torch.bfloat16) else torch.float32, dev)
     C = x.shape[-1]
@@ -485,7 +490,7 @@ def normgate_backward(gout, x, gate, gamma, beta, mean, rstd, group):
     with torch.cuda.device(dev):
         ws = _workspace(lib.vrwkv_normgate_backward_workspace_bytes(rows, C, group), dev)
         st = lib.vrwkv_normgate_backward_f32(rows, C, group, gout.data_ptr(), x.data_ptr(), gate.data_ptr(), int(_is_bf16(gate)),
-                                             gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), rstd.data_ptr(), gx.data_ptr(),
+                                             GATE_ACTIVATIONS[act], gamma.data_ptr(), beta.data_ptr(), mean.data_ptr(), rstd.data_ptr(), gx.data_ptr(),
                                              ggate.data_ptr(), gpar.data_ptr(), ws.data_ptr(), ws.numel(),
                                              torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "vrwkv_normgate_backward_f32")
