@@ -124,3 +124,36 @@ def test_config4_wkv6_shape_bf16_inputs(cuda_device, T):
                                 u[h:h + 1].double().cpu(), gy[b:b + 1, :, sl].double().cpu(), 1)
         for x, rf in zip(xs[:4], refg[:4]):
             assert rel_err(x.grad[b:b + 1, :, sl].float(), rf) <= 1e-2
+
+
+def test_second_device_after_the_first(cuda_device):
+    """Per-device set-up (function attributes, cluster-fit cache): a call on another GPU of the same process after
+    one on the first must configure that device too.  Needs two visible GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU visible")
+    from vision_rwkv_b200 import ops
+    from vision_rwkv_b200.vrwkv6 import RUN_CUDA_RWKV6
+    for index in (0, 1, 0):
+        dev = torch.device("cuda", index)
+        w, u, k, v, gy = _biwkv_inputs(2, 300, 64, dev, 9)
+        y = ops.biwkv_forward(w, u, k, v)
+        grads = ops.biwkv_backward(w, u, k, v, gy)
+        y2, logden = ops.biwkv_forward_save(w, u, k, v)
+        assert logden is not None
+        _check_slice(w, u, k, v, gy, y, grads, b=1, cs=slice(60, 64))
+        _check_slice(w, u, k, v, gy, y2, None, b=0, cs=slice(0, 4))
+        kh, vh, gh = k.bfloat16(), v.bfloat16(), gy.bfloat16()
+        yh = ops.biwkv_forward(w, u, kh, vh)
+        ops.biwkv_backward(w, u, kh, vh, gh)
+        assert rel_err(yh.float(), y.double().cpu()) <= 1e-2
+        with torch.cuda.device(dev):
+            H = 1
+            g = torch.Generator(device=dev).manual_seed(3)
+            r6, k6, v6 = (torch.randn(1, 40, 64, device=dev, generator=g).bfloat16() for _ in range(3))
+            w6 = torch.randn(1, 40, 64, device=dev, generator=g) * 0.5 - 0.6
+            u6 = torch.randn(H, 64, device=dev, generator=g) * 0.1
+            leaves = [t.requires_grad_(True) for t in (r6, k6, v6, w6, u6)]
+            y6 = RUN_CUDA_RWKV6(1, 40, 64, H, *leaves)
+            y6.backward(torch.randn_like(y6))
+            assert torch.isfinite(y6).all() and all(torch.isfinite(t.grad).all() for t in leaves)
+        ops.raise_if_failed()
