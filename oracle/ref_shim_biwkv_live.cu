@@ -4,10 +4,9 @@
 // stand-in headers under ref_stubs/ (see build_ref.py); nothing of it is copied here.
 #include REF_SOURCE
 
-extern "C" void ref_biwkv_live_forward(int B, int T, int C, float* w, float* u, float* k, float* v, float* y) {
-    torch::Tensor out = bi_wkv_cuda_forward(torch::wrap(w, C), torch::wrap(u, C), torch::wrap(k, B, T, C), torch::wrap(v, B, T, C));
-    cudaMemcpy(y, out.ptr, sizeof(float) * static_cast<size_t>(B) * T * C, cudaMemcpyDeviceToDevice);
-}
+// Only the gradient kernel is exported.  The file's forward kernel combines its token segments with
+// __shfl_sync(0xffffffff, ...) inside loops whose trip count differs per lane (:71-77, :82-88), which CUDA leaves
+// undefined; it is not run from here.
 extern "C" void ref_biwkv_live_backward(int B, int T, int C, float* w, float* u, float* k, float* v, float* gy,
                                         float* gw, float* gu, float* gk, float* gv) {
     std::vector<torch::Tensor> g = bi_wkv_cuda_backward(torch::wrap(w, C), torch::wrap(u, C), torch::wrap(k, B, T, C),

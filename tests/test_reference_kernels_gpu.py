@@ -95,21 +95,22 @@ def test_biwkv_reference_beyond_32_tokens_follows_its_closed_form(cuda_device):
     assert rel_err(mine, clean) <= 1e-5
 
 
-def run_live_biwkv(lib, dev, w, u, k, v, gy):
-    """The kernel file the four live backbones load (cuda_new/bi_wkv_kernel.cu); gw, gu come back summed over the
-    batch, as its atomicAdd leaves them.  T a multiple of 32 only: every thread's segment is then inside the sequence."""
+def run_live_biwkv_backward(lib, dev, w, u, k, v, gy):
+    """The gradient kernel of the file the four live backbones load (cuda_new/bi_wkv_kernel.cu); gw, gu come back summed
+    over the batch, as its atomicAdd leaves them.  T a multiple of 32 only: every thread's segment is then inside the
+    sequence.  Its forward kernel is not run: it shuffles with a full mask inside loops whose trip count differs per lane
+    (:71-77, :82-88), which CUDA leaves undefined; built for sm_100a it was measured once 1.2e-2 to 2.0e-2 away from the
+    recurrence, from the older copy and from the closed form of the segment updates alike."""
     B, T, C = k.shape
     assert T % 32 == 0 and C >= 32 and (B * C) % 32 == 0
     wd, ud = w.float().to(dev), u.float().to(dev)
     kb, vb, gb = _padded(k, dev), _padded(v, dev), _padded(gy, dev)
-    y = torch.zeros(B + 1, T, C, device=dev)
-    lib.ref_biwkv_live_forward(B, T, C, P(wd), P(ud), P(kb), P(vb), P(y))
     gw, gu = torch.zeros(C, device=dev), torch.zeros(C, device=dev)
     gk = torch.zeros(B + 1, T, C, device=dev)
     gv = torch.zeros(B + 1, T, C, device=dev)
     lib.ref_biwkv_live_backward(B, T, C, P(wd), P(ud), P(kb), P(vb), P(gb), P(gw), P(gu), P(gk), P(gv))
     torch.cuda.synchronize()
-    return y[:B].cpu(), gw.cpu(), gu.cpu(), gk[:B].cpu(), gv[:B].cpu()
+    return gw.cpu(), gu.cpu(), gk[:B].cpu(), gv[:B].cpu()
 
 
 @pytest.mark.parametrize("T", [32, 64, 192])
@@ -119,27 +120,10 @@ def test_live_biwkv_gradient_kernel_is_the_older_copy(cuda_device, T):
     gradients (tests above) holds for the live file too."""
     live, old = _load("libref_biwkv_live.so"), _load("libref_biwkv.so")
     w, u, k, v, gy = BO.make_inputs(2, T, 32, seed=41)
-    a = run_live_biwkv(live, cuda_device, w, u, k, v, gy)
+    gw, gu, gk, gv = run_live_biwkv_backward(live, cuda_device, w, u, k, v, gy)
     b = run_ref_biwkv(old, cuda_device, w, u, k, v, gy)
-    assert torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])
-    assert rel_err(a[1], b[1].double()) < 2e-6 and rel_err(a[2], b[2].double()) < 2e-6
-
-
-@pytest.mark.parametrize("T", [32, 64, 192])
-def test_live_biwkv_forward_kernel_is_not_reproducible_here(cuda_device, T):
-    """The live forward kernel combines its 32 token segments with __shfl_sync(0xffffffff, ...) inside loops whose trip
-    count differs per lane (cuda_new/bi_wkv_kernel.cu:71-77, 82-88): the source lane has left the loop when it is read,
-    which CUDA leaves undefined.  Built for sm_100a it lands 1e-2 to 2e-2 away from the recurrence, from the older copy
-    and from the closed form of the segment updates alike (measured: 2.0e-2, 1.2e-2, 1.5e-2 at T = 32, 64, 192), while
-    the older copy, which does the same sums through shared memory, is on the closed form to 5e-7.  So the forward is
-    pinned by the older copy; here only: finite, and in the neighbourhood."""
-    live, old = _load("libref_biwkv_live.so"), _load("libref_biwkv.so")
-    w, u, k, v, gy = BO.make_inputs(2, T, 32, seed=41)
-    y = run_live_biwkv(live, cuda_device, w, u, k, v, gy)[0]
-    y_old = run_ref_biwkv(old, cuda_device, w, u, k, v, gy)[0]
-    clean = BO.biwkv_scan_forward(w, u, k, v)
-    assert torch.isfinite(y).all() and rel_err(y, clean) < 0.1
-    assert rel_err(y_old, BO.biwkv_reference_quirk_forward(w, u, k, v, token_split=32)) < 5e-5
+    assert torch.equal(gk, b[3]) and torch.equal(gv, b[4])
+    assert rel_err(gw, b[1].double()) < 2e-6 and rel_err(gu, b[2].double()) < 2e-6
 
 
 @pytest.mark.parametrize("B,T,H", [(2, 8, 1), (1, 64, 2), (1, 200, 1), (1, 256, 1)])
