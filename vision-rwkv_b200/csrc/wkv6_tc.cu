@@ -1307,10 +1307,11 @@ __global__ void __launch_bounds__(128) wkv6_bwd_carry_kernel(const FinArgs a) {
     }
 }
 
-// grid (n_seg, H, B), 64 threads: the walk inside a segment, rightward part parked in shared memory
+// grid (n_seg, H, B), 64 threads: the walk inside a segment; the rightward part is parked in gw itself and read back
+// by the leftward walk (32 KB per block, still in L2), which leaves the block without shared memory and the SM
+// with four times the warps
 template <bool kHalfIn>
 __global__ void __launch_bounds__(N) wkv6_bwd_decay_kernel(const FinArgs a) {
-    __shared__ float part[kSeg][N];
     const int seg = blockIdx.x, h = blockIdx.y, b = blockIdx.z, lane = threadIdx.x, c = h * N + lane;
     const int C = a.H * N;
     const int t0 = seg * kSeg, t1 = min(a.T, t0 + kSeg);
@@ -1335,29 +1336,30 @@ __global__ void __launch_bounds__(N) wkv6_bwd_decay_kernel(const FinArgs a) {
 #pragma unroll
         for (int e = 0; e < kU; ++e)
             if (s0 + e < n) {
-                part[s0 + e][lane] = run - p[e];
+                a.gw[i0 + static_cast<size_t>(s0 + e) * C] = run - p[e];
                 run += q[e] - p[e];
             }
     }
     run = a.tot[plane + j];
     for (int s1 = n; s1 > 0; s1 -= kU) {
-        float p[kU], q[kU], ew[kU];
+        float p[kU], q[kU], ew[kU], part[kU];
 #pragma unroll
         for (int e = 0; e < kU; ++e) {
-            p[e] = 0.f; q[e] = 0.f; ew[e] = 0.f;
+            p[e] = 0.f; q[e] = 0.f; ew[e] = 0.f; part[e] = 0.f;
             const int s = s1 - 1 - e;
             if (s >= 0) {
                 const size_t i = i0 + static_cast<size_t>(s) * C;
                 p[e] = in_ld<kHalfIn>(a.r, i) * a.gr_left[i];
                 q[e] = in_ld<kHalfIn>(a.k, i) * a.gk_right[i];
                 ew[e] = -__expf(a.w[i]);
+                part[e] = a.gw[i];
             }
         }
 #pragma unroll
         for (int e = 0; e < kU; ++e) {
             const int s = s1 - 1 - e;
             if (s >= 0) {
-                a.gw[i0 + static_cast<size_t>(s) * C] = (part[s][lane] + run - p[e]) * ew[e];
+                a.gw[i0 + static_cast<size_t>(s) * C] = (part[e] + run - p[e]) * ew[e];
                 run += q[e] - p[e];
             }
         }
